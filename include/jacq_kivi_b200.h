@@ -1,0 +1,231 @@
+/*
+ * jacq_kivi_b200 -- C launch contract of the B200-native int4-KIVI paged KV-cache path.
+ *
+ * One shared library (libjacq_kivi_b200.so) exports two families of entry points:
+ *
+ *  1. The reference's versioned launch contract, ABI v1 (docs/ABI.md of ImpossibleComputing/jacq):
+ *     the exact `extern "C"` symbols the reference's torch-op binding declares
+ *     (integrations/vllm_kivi/source_patch.py:570-658), compiled for the reference lane geometry
+ *     (NH/NKV 40/8 or 20/4 for the `_tp2_local` symbols, head_dim 128, block = group = 32,
+ *     residual 128, at most 124 old pages). They are drop-in: same argument order, same in-place
+ *     mutation, asynchronous on the caller's stream, print-and-exit on a launch error.
+ *
+ *  2. ABI v2: runtime geometry, many sequences per launch, device-resident sequence lengths (no host
+ *     synchronisation, usable under CUDA graph capture once the workspace exists), `int` status
+ *     instead of exit(). The reference has no such call; it loops over requests and tokens in
+ *     Python (integrations/vllm_kivi/source_patch.py:3105-3288).
+ *
+ * Every pointer below is a DEVICE pointer unless it says "host". fp16 tensors are passed as
+ * `kivi_f16*` (raw IEEE binary16 bits). Nothing here allocates device memory unless stated.
+ *
+ * Tensor layout (reference: integrations/vllm_kivi/bindings.py:105-118), for geometry
+ * NH query heads, NKV kv heads, D head_dim, B page tokens, G key group, R residual tokens,
+ * HG = ceil(D / G) value channel groups of width min(G, D):
+ *
+ *   K_CODE_PAGES, V_CODE_PAGES   u8  [num_blocks, NKV, B, D/2]  byte j = channel 2j (low nibble),
+ *                                                               channel 2j+1 (high nibble)
+ *   K_SCALE_PAGES, K_ZERO_PAGES  f16 [num_blocks, NKV, D]       per channel, over the G tokens of
+ *                                                               the group; when G > B the same
+ *                                                               values are stored in every page of
+ *                                                               the group
+ *   V_SCALE_PAGES, V_ZERO_PAGES  f16 [num_blocks, NKV, B, HG]   per token, per channel group
+ *   K/V_RESIDUAL_SCRATCH         f16 [num_slots, NKV, R+G, D]   row 0 = oldest unquantised token
+ *   BLOCK_TABLE                  i32 [>= T_old / B]             logical page -> physical page
+ *   Q f16 [NH, D],  O f32 [NH, D]
+ *
+ *   T_old = floor(max(T - R, 0) / G) * G tokens are quantised; the remaining T - T_old live in
+ *   scratch rows [0, T - T_old).
+ */
+#ifndef JACQ_KIVI_B200_H_
+#define JACQ_KIVI_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#ifndef __CUDA_RUNTIME_H__
+typedef struct CUstream_st* cudaStream_t;
+#endif
+
+typedef uint16_t kivi_f16;
+
+/* Same value as JACQ_KIVI_ABI_VERSION would take after the v2 additions (the reference's rule:
+ * bump on any tensor-shape, launch-order or constant change; integrations/vllm_kivi/abi.py:35-36). */
+#define JACQ_KIVI_B200_ABI_VERSION 2
+
+enum kivi_status {
+    KIVI_OK = 0,
+    KIVI_ERR_NULL_POINTER = 1,     /* a required pointer is NULL */
+    KIVI_ERR_GEOMETRY = 2,         /* unsupported or inconsistent geometry */
+    KIVI_ERR_RANGE = 3,            /* batch / length / count out of range */
+    KIVI_ERR_ALIGNMENT = 4,        /* a tensor base is not 16-byte aligned */
+    KIVI_ERR_WORKSPACE = 5,        /* workspace missing or too small */
+    KIVI_ERR_CUDA = 6,             /* the CUDA runtime reported an error on launch */
+    KIVI_ERR_BLOCK_TABLE = 7       /* block table too narrow for the stated lengths */
+};
+
+/* Runtime geometry. The reference fixes these per translation unit as `static constexpr`
+ * (crates/jac-codegen-cuda/src/variants.rs:2577-2587). */
+typedef struct kivi_geometry {
+    int32_t num_q_heads;   /* NH */
+    int32_t num_kv_heads;  /* NKV; NH % NKV == 0 */
+    int32_t head_dim;      /* D; 64 or 128 on the tensor-core path, any even value otherwise */
+    int32_t block_size;    /* B, tokens per page */
+    int32_t group_size;    /* G, tokens per key group; G % B == 0 */
+    int32_t residual;      /* R, fp16 residual window */
+} kivi_geometry;
+
+/* One layer's page pool and residual scratch slots. */
+typedef struct kivi_cache {
+    uint8_t* k_code_pages;
+    kivi_f16* k_scale_pages;
+    kivi_f16* k_zero_pages;
+    uint8_t* v_code_pages;
+    kivi_f16* v_scale_pages;
+    kivi_f16* v_zero_pages;
+    kivi_f16* k_residual_scratch;
+    kivi_f16* v_residual_scratch;
+    int32_t num_blocks;
+    int32_t num_slots;
+} kivi_cache;
+
+/* ------------------------------------------------------------------ ABI v2 ------------------ */
+
+int kivi_b200_abi_version(void);
+const char* kivi_b200_status_string(int status);
+
+/* KIVI_OK if the geometry is usable at all; *fast_path (may be NULL) receives 1 when the
+ * tensor-core decode kernel covers it, 0 when the generic kernel runs instead. */
+int kivi_b200_validate_geometry(const kivi_geometry* geom, int* fast_path);
+
+/* Cache writer for `batch` sequences in one call. Sequence i appends the rows
+ * new_offsets[i] .. new_offsets[i+1]-1 of NEW_K / NEW_V ([total_new, NKV, D], token-major) to a
+ * cache that held start_seq_lens[i] tokens, ageing out as many key groups as that crosses.
+ * The result equals the reference's single-token writer applied token by token
+ * (integrations/vllm_kivi/source_patch.py:1661-1697; batched form :1737-1775, which needs the
+ * Python planner :504-553 to stay within one age-out per call -- not needed here).
+ *   block_tables   i32 [batch, max_blocks_per_seq]
+ *   start_seq_lens i32 [batch], new_offsets i32 [batch+1]   (device)
+ *   slot_ids       i32 [batch] scratch slot of each sequence, or NULL for slot i = i
+ *   max_new_per_seq  host upper bound of new_offsets[i+1]-new_offsets[i] (sizes the launch)
+ *   max_start_seq_len host upper bound of start_seq_lens (checks the block-table width) */
+int kivi_b200_cache_write(const kivi_geometry* geom, const kivi_cache* cache,
+                          const kivi_f16* new_k, const kivi_f16* new_v,
+                          const int32_t* block_tables, int max_blocks_per_seq,
+                          const int32_t* start_seq_lens, const int32_t* new_offsets,
+                          const int32_t* slot_ids, int batch, int max_new_per_seq,
+                          int max_start_seq_len, cudaStream_t stream);
+
+/* Bytes of caller-owned workspace the decode needs for this batch and longest sequence. */
+size_t kivi_b200_decode_workspace_bytes(const kivi_geometry* geom, int batch, int max_seq_len);
+
+/* Zero the workspace's arrival counters. Call once after allocating (or re-purposing) a
+ * workspace; every decode leaves them zero again. */
+int kivi_b200_decode_workspace_init(void* workspace, size_t workspace_bytes, cudaStream_t stream);
+
+/* Paged decode attention for `batch` independent sequences, one query token each
+ * (the reference's jac_launch applied per sequence: crates/jac-codegen-cuda/src/variants.rs:2441-2509,
+ * :2593-2601). q f16 [batch, NH, D]; out f32 [batch, NH, D]; seq_lens i32 [batch] on the device;
+ * max_seq_len is a host upper bound used to size the launch and check the block-table width. */
+int kivi_b200_decode(const kivi_geometry* geom, const kivi_cache* cache, const kivi_f16* q,
+                     const int32_t* block_tables, int max_blocks_per_seq, const int32_t* seq_lens,
+                     const int32_t* slot_ids, int batch, int max_seq_len, float* out,
+                     void* workspace, size_t workspace_bytes, cudaStream_t stream);
+
+/* fp16 GEMV / skinny GEMM of the generated decode runtime: y[b, o] = sum_i W[o, i] * x[b, i],
+ * W row-major [out_dim, in_dim], fp32 accumulation (reference: gemv(),
+ * crates/jac-codegen-cuda/src/templates/runtime.cu:15-26, a cublasGemmEx call). 1 <= batch <= 64.
+ * in_dim % 8 == 0. Exactly one of y_f16 / y_f32 may be NULL; y_f32 is the kernel-DSL form
+ * (crates/jac-codegen-cuda/src/variants.rs:318-329). */
+int kivi_b200_gemv_f16(const kivi_f16* w, const kivi_f16* x, kivi_f16* y_f16, float* y_f32,
+                       int out_dim, int in_dim, int batch, cudaStream_t stream);
+
+/* ------------------------------------------------------------------ ABI v1 (reference lane) -- */
+
+/* Replaces the emitted `jac_launch` of decode_attention_kivi_paged
+ * (crates/jac-codegen-cuda/src/variants.rs:2593-2601; declared by the binding at
+ * integrations/vllm_kivi/source_patch.py:570-576). One sequence, NH = 40 query heads. */
+void jac_launch(const kivi_f16* Q, const int* BLOCK_TABLE,
+                const unsigned char* K_CODE_PAGES, const kivi_f16* K_SCALE_PAGES, const kivi_f16* K_ZERO_PAGES,
+                const unsigned char* V_CODE_PAGES, const kivi_f16* V_SCALE_PAGES, const kivi_f16* V_ZERO_PAGES,
+                const kivi_f16* K_RESIDUAL_SCRATCH, const kivi_f16* V_RESIDUAL_SCRATCH,
+                int SEQ_LEN, float* O, cudaStream_t stream);
+
+/* TP=2 rank-local clone, NH/NKV 20/4 (integrations/vllm_kivi/dsl_decode.py:267-319;
+ * source_patch.py:578-584). */
+void jac_launch_tp2_local(const kivi_f16* Q, const int* BLOCK_TABLE,
+                          const unsigned char* K_CODE_PAGES, const kivi_f16* K_SCALE_PAGES, const kivi_f16* K_ZERO_PAGES,
+                          const unsigned char* V_CODE_PAGES, const kivi_f16* V_SCALE_PAGES, const kivi_f16* V_ZERO_PAGES,
+                          const kivi_f16* K_RESIDUAL_SCRATCH, const kivi_f16* V_RESIDUAL_SCRATCH,
+                          int SEQ_LEN, float* O, cudaStream_t stream);
+
+/* Replaces `jac_launch_batched` (variants.rs:2891-2896; source_patch.py:609-615): NUM_QUERIES
+ * (<= 160) queries of ONE sequence sharing BLOCK_TABLE and scratch, each with its own SEQ_LENS[i]. */
+void jac_launch_batched(const kivi_f16* Q, const int* SEQ_LENS, const int* BLOCK_TABLE,
+                        const unsigned char* K_CODE_PAGES, const kivi_f16* K_SCALE_PAGES, const kivi_f16* K_ZERO_PAGES,
+                        const unsigned char* V_CODE_PAGES, const kivi_f16* V_SCALE_PAGES, const kivi_f16* V_ZERO_PAGES,
+                        const kivi_f16* K_RESIDUAL_SCRATCH, const kivi_f16* V_RESIDUAL_SCRATCH,
+                        int NUM_QUERIES, float* O, cudaStream_t stream);
+
+void jac_launch_batched_tp2_local(const kivi_f16* Q, const int* SEQ_LENS, const int* BLOCK_TABLE,
+                                  const unsigned char* K_CODE_PAGES, const kivi_f16* K_SCALE_PAGES, const kivi_f16* K_ZERO_PAGES,
+                                  const unsigned char* V_CODE_PAGES, const kivi_f16* V_SCALE_PAGES, const kivi_f16* V_ZERO_PAGES,
+                                  const kivi_f16* K_RESIDUAL_SCRATCH, const kivi_f16* V_RESIDUAL_SCRATCH,
+                                  int NUM_QUERIES, float* O, cudaStream_t stream);
+
+/* Replaces `jac_launch_sparse_retained` (variants.rs:2737-2742; source_patch.py:590-596): scans
+ * NUM_RETAINED_PAGES pages of a compact table; the residual bound still comes from SEQ_LEN. */
+void jac_launch_sparse_retained(const kivi_f16* Q, const int* RETAINED_BLOCK_TABLE,
+                                const unsigned char* K_CODE_PAGES, const kivi_f16* K_SCALE_PAGES, const kivi_f16* K_ZERO_PAGES,
+                                const unsigned char* V_CODE_PAGES, const kivi_f16* V_SCALE_PAGES, const kivi_f16* V_ZERO_PAGES,
+                                const kivi_f16* K_RESIDUAL_SCRATCH, const kivi_f16* V_RESIDUAL_SCRATCH,
+                                int SEQ_LEN, int NUM_RETAINED_PAGES, float* O, cudaStream_t stream);
+
+void jac_launch_sparse_retained_tp2_local(const kivi_f16* Q, const int* RETAINED_BLOCK_TABLE,
+                                          const unsigned char* K_CODE_PAGES, const kivi_f16* K_SCALE_PAGES, const kivi_f16* K_ZERO_PAGES,
+                                          const unsigned char* V_CODE_PAGES, const kivi_f16* V_SCALE_PAGES, const kivi_f16* V_ZERO_PAGES,
+                                          const kivi_f16* K_RESIDUAL_SCRATCH, const kivi_f16* V_RESIDUAL_SCRATCH,
+                                          int SEQ_LEN, int NUM_RETAINED_PAGES, float* O, cudaStream_t stream);
+
+/* Replaces `jac_launch_cache_write` (variants.rs:3226-3253; source_patch.py:645-650). SEQ_LEN is
+ * the length after the new token. NKV = 8. */
+void jac_launch_cache_write(unsigned char* K_CODE_PAGES, kivi_f16* K_SCALE_PAGES, kivi_f16* K_ZERO_PAGES,
+                            unsigned char* V_CODE_PAGES, kivi_f16* V_SCALE_PAGES, kivi_f16* V_ZERO_PAGES,
+                            kivi_f16* K_RESIDUAL_SCRATCH, kivi_f16* V_RESIDUAL_SCRATCH,
+                            const kivi_f16* NEW_K, const kivi_f16* NEW_V,
+                            const int* BLOCK_TABLE, int SEQ_LEN, cudaStream_t stream);
+
+/* Replaces `jac_launch_cache_write_batched` (variants.rs:3135-3167; source_patch.py:655-660).
+ * NUM_NEW outside [1, 160] prints and exits like the reference; unlike the reference a chunk that
+ * crosses several age-out boundaries is handled in the one call. */
+void jac_launch_cache_write_batched(unsigned char* K_CODE_PAGES, kivi_f16* K_SCALE_PAGES, kivi_f16* K_ZERO_PAGES,
+                                    unsigned char* V_CODE_PAGES, kivi_f16* V_SCALE_PAGES, kivi_f16* V_ZERO_PAGES,
+                                    kivi_f16* K_RESIDUAL_SCRATCH, kivi_f16* V_RESIDUAL_SCRATCH,
+                                    const kivi_f16* NEW_K, const kivi_f16* NEW_V,
+                                    const int* BLOCK_TABLE, int START_SEQ_LEN, int NUM_NEW, cudaStream_t stream);
+
+/* C-callable forms of the reference's C++-linkage hand-CUDA writer
+ * (kivi_cache_write_launch / kivi_cache_write_batched_launch, source_patch.py:624-637,
+ * :1661-1666, :1737-1742). The library also exports those two names with C++ linkage and the
+ * reference's exact parameter lists, so the reference's binding links against it unchanged.
+ * NKV_RUNTIME is 8 or 4; SLOT_MAPPING is accepted and ignored, as in the reference. */
+void kivi_b200_cache_write_launch(unsigned char* K_CODE_PAGES, kivi_f16* K_SCALE_PAGES, kivi_f16* K_ZERO_PAGES,
+                                  unsigned char* V_CODE_PAGES, kivi_f16* V_SCALE_PAGES, kivi_f16* V_ZERO_PAGES,
+                                  kivi_f16* K_RESIDUAL_SCRATCH, kivi_f16* V_RESIDUAL_SCRATCH,
+                                  const kivi_f16* NEW_K, const kivi_f16* NEW_V, const int64_t* SLOT_MAPPING,
+                                  const int* BLOCK_TABLE, int seq_len, int NKV_RUNTIME, cudaStream_t stream);
+
+void kivi_b200_cache_write_batched_launch(unsigned char* K_CODE_PAGES, kivi_f16* K_SCALE_PAGES, kivi_f16* K_ZERO_PAGES,
+                                          unsigned char* V_CODE_PAGES, kivi_f16* V_SCALE_PAGES, kivi_f16* V_ZERO_PAGES,
+                                          kivi_f16* K_RESIDUAL_SCRATCH, kivi_f16* V_RESIDUAL_SCRATCH,
+                                          const kivi_f16* NEW_K, const kivi_f16* NEW_V, const int64_t* SLOT_MAPPING,
+                                          const int* BLOCK_TABLE, int START_SEQ_LEN, int NUM_NEW, int NKV_RUNTIME,
+                                          cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* JACQ_KIVI_B200_H_ */

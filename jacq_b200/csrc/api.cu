@@ -1,0 +1,416 @@
+// C launch contract of libjacq_kivi_b200.so: argument validation, launch planning and the
+// reference-lane (ABI v1) symbols. Declarations and the reference lines each entry point
+// replaces are in include/jacq_kivi_b200.h.
+#include <cstdio>
+#include <cstdlib>
+
+#include "kivi_common.cuh"
+
+namespace kivi {
+namespace {
+
+constexpr int kSmCount = 148;       // B200
+constexpr int kMinChunkTokens = 256;
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int check_geometry(const kivi_geometry* s) {
+    if (!s) return KIVI_ERR_NULL_POINTER;
+    if (s->num_q_heads <= 0 || s->num_kv_heads <= 0 || s->head_dim <= 0 || s->block_size <= 0 ||
+        s->group_size <= 0 || s->residual < 0)
+        return KIVI_ERR_GEOMETRY;
+    if (s->num_q_heads % s->num_kv_heads) return KIVI_ERR_GEOMETRY;
+    if (s->head_dim % 8 || s->head_dim > 256) return KIVI_ERR_GEOMETRY;  // 16-byte rows, <= 4 bytes per lane
+    if (s->group_size % s->block_size) return KIVI_ERR_GEOMETRY;
+    const int vg = s->group_size < s->head_dim ? s->group_size : s->head_dim;
+    if (s->head_dim % vg || vg % 8) return KIVI_ERR_GEOMETRY;
+    return KIVI_OK;
+}
+
+int check_cache(const kivi_cache* c) {
+    if (!c) return KIVI_ERR_NULL_POINTER;
+    const void* ptrs[] = {c->k_code_pages, c->k_scale_pages, c->k_zero_pages, c->v_code_pages,
+                          c->v_scale_pages, c->v_zero_pages, c->k_residual_scratch, c->v_residual_scratch};
+    for (const void* p : ptrs) {
+        if (!p) return KIVI_ERR_NULL_POINTER;
+        if (!aligned16(p)) return KIVI_ERR_ALIGNMENT;
+    }
+    if (c->num_blocks < 0 || c->num_slots <= 0) return KIVI_ERR_RANGE;
+    return KIVI_OK;
+}
+
+CachePtrs cache_ptrs(const kivi_cache& c) {
+    CachePtrs o;
+    o.k_code = c.k_code_pages;
+    o.k_scale = reinterpret_cast<__half*>(c.k_scale_pages);
+    o.k_zero = reinterpret_cast<__half*>(c.k_zero_pages);
+    o.v_code = c.v_code_pages;
+    o.v_scale = reinterpret_cast<__half*>(c.v_scale_pages);
+    o.v_zero = reinterpret_cast<__half*>(c.v_zero_pages);
+    o.k_scratch = reinterpret_cast<__half*>(c.k_residual_scratch);
+    o.v_scratch = reinterpret_cast<__half*>(c.v_residual_scratch);
+    return o;
+}
+
+// Split of the context over CTAs. Work units are (sequence, kv head); when there are fewer of
+// them than about two per SM, each unit's quantised tokens are cut into equal chunks (a multiple
+// of the key group, at least kMinChunkTokens) so that the grid still fills the machine.
+struct SplitPlan { int chunk_tokens; int max_chunks; };
+
+SplitPlan plan_split(const Geom& g, int n, int max_old_tokens) {
+    SplitPlan sp;
+    const long long units = (long long)n * g.nkv;
+    long long want = (2LL * kSmCount + units - 1) / units;
+    if (want < 1) want = 1;
+    long long chunk = (max_old_tokens + want - 1) / want;
+    if (chunk < kMinChunkTokens) chunk = kMinChunkTokens;
+    const int gran = g.g > 64 ? g.g : ((64 + g.g - 1) / g.g) * g.g;  // multiple of the group, >= 64
+    chunk = ((chunk + gran - 1) / gran) * gran;
+    sp.chunk_tokens = (int)chunk;
+    sp.max_chunks = max_old_tokens > 0 ? (int)((max_old_tokens + chunk - 1) / chunk) : 1;
+    return sp;
+}
+
+constexpr size_t kWsAlign = 256;
+size_t align_up(size_t x) { return (x + kWsAlign - 1) / kWsAlign * kWsAlign; }
+
+struct WsLayout { size_t count_off, ml_off, o_off, total; };
+WsLayout ws_layout(const Geom& g, int n, const SplitPlan& sp) {
+    WsLayout w;
+    const size_t units = (size_t)n * g.nkv;
+    w.count_off = 0;
+    w.ml_off = align_up(units * sizeof(unsigned int));
+    const size_t parts = sp.max_chunks > 1 ? units * sp.max_chunks * g.qpk : 0;
+    w.o_off = w.ml_off + align_up(parts * 2 * sizeof(float));
+    w.total = w.o_off + align_up(parts * g.d * sizeof(float));
+    return w;
+}
+
+int run_decode(const Geom& g, const CachePtrs& cache, const SeqAddressing& seq, const __half* q, float* out, int n,
+               int max_old_cap, int max_old_tokens, int retained_pages, void* ws, size_t ws_bytes,
+               cudaStream_t stream) {
+    DecodeParams p;
+    p.geom = g; p.cache = cache; p.seq = seq; p.q = q; p.out = out; p.n = n;
+    p.max_old = max_old_cap; p.retained_pages = retained_pages; p.status = nullptr;
+    const SplitPlan sp = plan_split(g, n, max_old_tokens);
+    const WsLayout wl = ws_layout(g, n, sp);
+    p.chunk_tokens = sp.chunk_tokens;
+    p.max_chunks = sp.max_chunks;
+    if (sp.max_chunks > 1) {
+        if (!ws || ws_bytes < wl.total) return KIVI_ERR_WORKSPACE;
+        if (!aligned16(ws)) return KIVI_ERR_ALIGNMENT;
+    }
+    unsigned char* base = static_cast<unsigned char*>(ws);
+    p.ws_count = base ? reinterpret_cast<unsigned int*>(base + wl.count_off) : nullptr;
+    p.ws_ml = base ? reinterpret_cast<float*>(base + wl.ml_off) : nullptr;
+    p.ws_o = base ? reinterpret_cast<float*>(base + wl.o_off) : nullptr;
+    cudaError_t e = decode_mma_supports(g, retained_pages) ? launch_decode_mma(p, stream)
+                                                           : launch_decode_generic(p, stream);
+    return e == cudaSuccess ? KIVI_OK : KIVI_ERR_CUDA;
+}
+
+// ------------------------------------------------------------------ reference lane (ABI v1) --
+
+// Constants of the reference artefacts (snapshot decode_attention_kivi_paged_library_flash.cu:14-25;
+// integrations/vllm_kivi/source_patch.py:661-672).
+constexpr int kRefD = 128, kRefB = 32, kRefG = 32, kRefR = 128;
+constexpr int kRefOldBlocks = 124, kRefLQ = kRefOldBlocks * kRefB, kRefMaxQueries = 160;
+constexpr int kRefMaxNew = kRefR + kRefB;
+
+Geom ref_geom(int nh, int nkv) {
+    kivi_geometry s = {nh, nkv, kRefD, kRefB, kRefG, kRefR};
+    return make_geom(s);
+}
+
+[[noreturn]] void die(const char* what, cudaError_t e) {
+    fprintf(stderr, "CUDA error %s in %s\n", cudaGetErrorString(e), what);
+    exit(1);
+}
+
+// Workspace of the v1 decode symbols. Their signatures carry no workspace, so the library keeps
+// one per device, sized for the largest v1 launch (160 queries) and allocated with cudaMalloc on
+// the first v1 decode call on that device (that first call must not be inside a stream capture).
+constexpr int kMaxDevices = 64;
+void* g_ref_ws[kMaxDevices];
+size_t g_ref_ws_bytes[kMaxDevices];
+
+void* ref_workspace(const Geom& g, int n, size_t* bytes, cudaStream_t stream) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) die("cudaGetDevice", e);
+    if (dev < 0 || dev >= kMaxDevices) { fprintf(stderr, "device index %d out of range\n", dev); exit(1); }
+    (void)g; (void)n;
+    if (!g_ref_ws[dev]) {
+        size_t need = 0;
+        const Geom lanes[2] = {ref_geom(40, 8), ref_geom(20, 4)};
+        for (const Geom& lane : lanes)
+            for (int q = 1; q <= kRefMaxQueries; ++q) {
+                size_t t = ws_layout(lane, q, plan_split(lane, q, kRefLQ)).total;
+                if (t > need) need = t;
+            }
+        e = cudaMalloc(&g_ref_ws[dev], need);
+        if (e != cudaSuccess) die("cudaMalloc(v1 decode workspace)", e);
+        e = cudaMemsetAsync(g_ref_ws[dev], 0, need, stream);
+        if (e != cudaSuccess) die("cudaMemsetAsync(v1 decode workspace)", e);
+        g_ref_ws_bytes[dev] = need;
+    }
+    *bytes = g_ref_ws_bytes[dev];
+    return g_ref_ws[dev];
+}
+
+CachePtrs ref_cache(const unsigned char* kc, const kivi_f16* ks, const kivi_f16* kz, const unsigned char* vc,
+                    const kivi_f16* vs, const kivi_f16* vz, const kivi_f16* kr, const kivi_f16* vr) {
+    CachePtrs c;
+    c.k_code = const_cast<unsigned char*>(kc);
+    c.k_scale = reinterpret_cast<__half*>(const_cast<kivi_f16*>(ks));
+    c.k_zero = reinterpret_cast<__half*>(const_cast<kivi_f16*>(kz));
+    c.v_code = const_cast<unsigned char*>(vc);
+    c.v_scale = reinterpret_cast<__half*>(const_cast<kivi_f16*>(vs));
+    c.v_zero = reinterpret_cast<__half*>(const_cast<kivi_f16*>(vz));
+    c.k_scratch = reinterpret_cast<__half*>(const_cast<kivi_f16*>(kr));
+    c.v_scratch = reinterpret_cast<__half*>(const_cast<kivi_f16*>(vr));
+    return c;
+}
+
+void ref_decode(int nh, int nkv, const kivi_f16* Q, const int* seq_lens, int seq_len, const int* bt,
+                const CachePtrs& cache, int n, int retained, float* O, cudaStream_t stream) {
+    if (n <= 0) return;
+    const Geom g = ref_geom(nh, nkv);
+    SeqAddressing a;
+    a.seq_lens = seq_lens; a.seq_len_scalar = seq_len;
+    a.block_tables = bt; a.bt_stride = 0; a.bt_width = kRefOldBlocks;
+    a.slot_ids = nullptr; a.slot_shared = 1;
+    size_t ws_bytes = 0;
+    void* ws = ref_workspace(g, n, &ws_bytes, stream);
+    int rc = run_decode(g, cache, a, reinterpret_cast<const __half*>(Q), O, n, kRefLQ, kRefLQ, retained, ws, ws_bytes,
+                        stream);
+    if (rc != KIVI_OK) { fprintf(stderr, "jac_launch: %s\n", kivi_b200_status_string(rc)); exit(1); }
+}
+
+void ref_write(int nkv, const CachePtrs& cache, const kivi_f16* new_k, const kivi_f16* new_v, const int* bt,
+               int start_seq_len, int num_new, cudaStream_t stream) {
+    WriteParams p;
+    p.geom = ref_geom(nkv * 5, nkv);
+    p.cache = cache;
+    p.seq.seq_lens = nullptr; p.seq.seq_len_scalar = start_seq_len;
+    p.seq.block_tables = bt; p.seq.bt_stride = 0; p.seq.bt_width = kRefOldBlocks;
+    p.seq.slot_ids = nullptr; p.seq.slot_shared = 1;
+    p.new_k = reinterpret_cast<const __half*>(new_k);
+    p.new_v = reinterpret_cast<const __half*>(new_v);
+    p.new_offsets = nullptr; p.num_new_scalar = num_new; p.n = 1;
+    cudaError_t e = launch_cache_write(p, num_new, stream);
+    if (e != cudaSuccess) die("KIVI cache write", e);
+}
+
+}  // namespace
+}  // namespace kivi
+
+using namespace kivi;
+
+// ------------------------------------------------------------------ ABI v2 -------------------
+
+extern "C" int kivi_b200_abi_version(void) { return JACQ_KIVI_B200_ABI_VERSION; }
+
+extern "C" const char* kivi_b200_status_string(int status) {
+    switch (status) {
+        case KIVI_OK: return "ok";
+        case KIVI_ERR_NULL_POINTER: return "a required pointer is NULL";
+        case KIVI_ERR_GEOMETRY: return "unsupported or inconsistent KIVI geometry";
+        case KIVI_ERR_RANGE: return "batch, length or count out of range";
+        case KIVI_ERR_ALIGNMENT: return "a tensor base is not 16-byte aligned";
+        case KIVI_ERR_WORKSPACE: return "decode workspace missing or too small";
+        case KIVI_ERR_CUDA: return "the CUDA runtime reported an error on launch";
+        case KIVI_ERR_BLOCK_TABLE: return "block table too narrow for the stated sequence lengths";
+        default: return "unknown status";
+    }
+}
+
+extern "C" int kivi_b200_validate_geometry(const kivi_geometry* geom, int* fast_path) {
+    int rc = check_geometry(geom);
+    if (rc != KIVI_OK) return rc;
+    if (fast_path) *fast_path = decode_mma_supports(make_geom(*geom), -1) ? 1 : 0;
+    return KIVI_OK;
+}
+
+extern "C" int kivi_b200_cache_write(const kivi_geometry* geom, const kivi_cache* cache, const kivi_f16* new_k,
+                                     const kivi_f16* new_v, const int32_t* block_tables, int max_blocks_per_seq,
+                                     const int32_t* start_seq_lens, const int32_t* new_offsets,
+                                     const int32_t* slot_ids, int batch, int max_new_per_seq, int max_start_seq_len,
+                                     cudaStream_t stream) {
+    int rc = check_geometry(geom);
+    if (rc != KIVI_OK) return rc;
+    rc = check_cache(cache);
+    if (rc != KIVI_OK) return rc;
+    if (!new_k || !new_v || !block_tables || !start_seq_lens || !new_offsets) return KIVI_ERR_NULL_POINTER;
+    if (!aligned16(new_k) || !aligned16(new_v)) return KIVI_ERR_ALIGNMENT;
+    if (batch < 0 || max_new_per_seq < 0 || max_start_seq_len < 0 || max_blocks_per_seq < 0) return KIVI_ERR_RANGE;
+    if (batch == 0 || max_new_per_seq == 0) return KIVI_OK;
+    if (!slot_ids && batch > cache->num_slots) return KIVI_ERR_RANGE;
+    const Geom g = make_geom(*geom);
+    const long long max_end = (long long)max_start_seq_len + max_new_per_seq;
+    if (max_end > 0x3fffffff) return KIVI_ERR_RANGE;
+    if ((long long)split_old((int)max_end, g.r, g.g) > (long long)max_blocks_per_seq * g.b) return KIVI_ERR_BLOCK_TABLE;
+    WriteParams p;
+    p.geom = g;
+    p.cache = cache_ptrs(*cache);
+    p.seq.seq_lens = start_seq_lens; p.seq.seq_len_scalar = 0;
+    p.seq.block_tables = block_tables; p.seq.bt_stride = max_blocks_per_seq; p.seq.bt_width = max_blocks_per_seq;
+    p.seq.slot_ids = slot_ids; p.seq.slot_shared = 0;
+    p.new_k = reinterpret_cast<const __half*>(new_k);
+    p.new_v = reinterpret_cast<const __half*>(new_v);
+    p.new_offsets = new_offsets; p.num_new_scalar = 0; p.n = batch;
+    return launch_cache_write(p, max_new_per_seq, stream) == cudaSuccess ? KIVI_OK : KIVI_ERR_CUDA;
+}
+
+extern "C" size_t kivi_b200_decode_workspace_bytes(const kivi_geometry* geom, int batch, int max_seq_len) {
+    if (check_geometry(geom) != KIVI_OK || batch <= 0 || max_seq_len < 0) return 0;
+    const Geom g = make_geom(*geom);
+    return ws_layout(g, batch, plan_split(g, batch, split_old(max_seq_len, g.r, g.g))).total;
+}
+
+extern "C" int kivi_b200_decode_workspace_init(void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+    if (!workspace) return workspace_bytes ? KIVI_ERR_NULL_POINTER : KIVI_OK;
+    return cudaMemsetAsync(workspace, 0, workspace_bytes, stream) == cudaSuccess ? KIVI_OK : KIVI_ERR_CUDA;
+}
+
+extern "C" int kivi_b200_decode(const kivi_geometry* geom, const kivi_cache* cache, const kivi_f16* q,
+                                const int32_t* block_tables, int max_blocks_per_seq, const int32_t* seq_lens,
+                                const int32_t* slot_ids, int batch, int max_seq_len, float* out, void* workspace,
+                                size_t workspace_bytes, cudaStream_t stream) {
+    int rc = check_geometry(geom);
+    if (rc != KIVI_OK) return rc;
+    rc = check_cache(cache);
+    if (rc != KIVI_OK) return rc;
+    if (!q || !block_tables || !seq_lens || !out) return KIVI_ERR_NULL_POINTER;
+    if (!aligned16(q) || !aligned16(out)) return KIVI_ERR_ALIGNMENT;
+    if (batch < 0 || max_seq_len < 0 || max_seq_len > 0x3fffffff || max_blocks_per_seq < 0) return KIVI_ERR_RANGE;
+    if (batch == 0) return KIVI_OK;
+    if (!slot_ids && batch > cache->num_slots) return KIVI_ERR_RANGE;
+    const Geom g = make_geom(*geom);
+    const int max_old = split_old(max_seq_len, g.r, g.g);
+    if ((long long)max_old > (long long)max_blocks_per_seq * g.b) return KIVI_ERR_BLOCK_TABLE;
+    SeqAddressing a;
+    a.seq_lens = seq_lens; a.seq_len_scalar = 0;
+    a.block_tables = block_tables; a.bt_stride = max_blocks_per_seq; a.bt_width = max_blocks_per_seq;
+    a.slot_ids = slot_ids; a.slot_shared = 0;
+    // max_old also caps what a sequence longer than the stated bound may walk, so the launch plan
+    // and the workspace stay valid whatever the device-side lengths say.
+    return run_decode(g, cache_ptrs(*cache), a, reinterpret_cast<const __half*>(q), out, batch, max_old, max_old, -1,
+                      workspace, workspace_bytes, stream);
+}
+
+extern "C" int kivi_b200_gemv_f16(const kivi_f16* w, const kivi_f16* x, kivi_f16* y_f16, float* y_f32, int out_dim,
+                                  int in_dim, int batch, cudaStream_t stream) {
+    if (!w || !x || (!y_f16 && !y_f32)) return KIVI_ERR_NULL_POINTER;
+    if (out_dim <= 0 || in_dim <= 0 || batch < 1 || batch > 64 || in_dim % 8) return KIVI_ERR_RANGE;
+    if (!aligned16(w) || !aligned16(x)) return KIVI_ERR_ALIGNMENT;
+    return launch_gemv(reinterpret_cast<const __half*>(w), reinterpret_cast<const __half*>(x),
+                       reinterpret_cast<__half*>(y_f16), y_f32, out_dim, in_dim, batch, stream) == cudaSuccess
+               ? KIVI_OK : KIVI_ERR_CUDA;
+}
+
+// ------------------------------------------------------------------ ABI v1 symbols -----------
+
+#define KIVI_V1_CACHE_ARGS                                                                              \
+    const unsigned char* K_CODE_PAGES, const kivi_f16* K_SCALE_PAGES, const kivi_f16* K_ZERO_PAGES,      \
+    const unsigned char* V_CODE_PAGES, const kivi_f16* V_SCALE_PAGES, const kivi_f16* V_ZERO_PAGES,      \
+    const kivi_f16* K_RESIDUAL_SCRATCH, const kivi_f16* V_RESIDUAL_SCRATCH
+#define KIVI_V1_CACHE                                                                                    \
+    ref_cache(K_CODE_PAGES, K_SCALE_PAGES, K_ZERO_PAGES, V_CODE_PAGES, V_SCALE_PAGES, V_ZERO_PAGES,      \
+              K_RESIDUAL_SCRATCH, V_RESIDUAL_SCRATCH)
+
+extern "C" void jac_launch(const kivi_f16* Q, const int* BLOCK_TABLE, KIVI_V1_CACHE_ARGS, int SEQ_LEN, float* O,
+                           cudaStream_t stream) {
+    ref_decode(40, 8, Q, nullptr, SEQ_LEN, BLOCK_TABLE, KIVI_V1_CACHE, 1, -1, O, stream);
+}
+extern "C" void jac_launch_tp2_local(const kivi_f16* Q, const int* BLOCK_TABLE, KIVI_V1_CACHE_ARGS, int SEQ_LEN,
+                                     float* O, cudaStream_t stream) {
+    ref_decode(20, 4, Q, nullptr, SEQ_LEN, BLOCK_TABLE, KIVI_V1_CACHE, 1, -1, O, stream);
+}
+extern "C" void jac_launch_batched(const kivi_f16* Q, const int* SEQ_LENS, const int* BLOCK_TABLE, KIVI_V1_CACHE_ARGS,
+                                   int NUM_QUERIES, float* O, cudaStream_t stream) {
+    if (NUM_QUERIES > kRefMaxQueries) { fprintf(stderr, "NUM_QUERIES out of range for jac_launch_batched: %d\n", NUM_QUERIES); exit(1); }
+    ref_decode(40, 8, Q, SEQ_LENS, 0, BLOCK_TABLE, KIVI_V1_CACHE, NUM_QUERIES, -1, O, stream);
+}
+extern "C" void jac_launch_batched_tp2_local(const kivi_f16* Q, const int* SEQ_LENS, const int* BLOCK_TABLE,
+                                             KIVI_V1_CACHE_ARGS, int NUM_QUERIES, float* O, cudaStream_t stream) {
+    if (NUM_QUERIES > kRefMaxQueries) { fprintf(stderr, "NUM_QUERIES out of range for jac_launch_batched_tp2_local: %d\n", NUM_QUERIES); exit(1); }
+    ref_decode(20, 4, Q, SEQ_LENS, 0, BLOCK_TABLE, KIVI_V1_CACHE, NUM_QUERIES, -1, O, stream);
+}
+extern "C" void jac_launch_sparse_retained(const kivi_f16* Q, const int* RETAINED_BLOCK_TABLE, KIVI_V1_CACHE_ARGS,
+                                           int SEQ_LEN, int NUM_RETAINED_PAGES, float* O, cudaStream_t stream) {
+    ref_decode(40, 8, Q, nullptr, SEQ_LEN, RETAINED_BLOCK_TABLE, KIVI_V1_CACHE, 1,
+               NUM_RETAINED_PAGES < 0 ? 0 : NUM_RETAINED_PAGES, O, stream);
+}
+extern "C" void jac_launch_sparse_retained_tp2_local(const kivi_f16* Q, const int* RETAINED_BLOCK_TABLE,
+                                                     KIVI_V1_CACHE_ARGS, int SEQ_LEN, int NUM_RETAINED_PAGES, float* O,
+                                                     cudaStream_t stream) {
+    ref_decode(20, 4, Q, nullptr, SEQ_LEN, RETAINED_BLOCK_TABLE, KIVI_V1_CACHE, 1,
+               NUM_RETAINED_PAGES < 0 ? 0 : NUM_RETAINED_PAGES, O, stream);
+}
+
+extern "C" void jac_launch_cache_write(unsigned char* K_CODE_PAGES, kivi_f16* K_SCALE_PAGES, kivi_f16* K_ZERO_PAGES,
+                                       unsigned char* V_CODE_PAGES, kivi_f16* V_SCALE_PAGES, kivi_f16* V_ZERO_PAGES,
+                                       kivi_f16* K_RESIDUAL_SCRATCH, kivi_f16* V_RESIDUAL_SCRATCH,
+                                       const kivi_f16* NEW_K, const kivi_f16* NEW_V, const int* BLOCK_TABLE,
+                                       int SEQ_LEN, cudaStream_t stream) {
+    ref_write(8, KIVI_V1_CACHE, NEW_K, NEW_V, BLOCK_TABLE, SEQ_LEN - 1, 1, stream);
+}
+extern "C" void jac_launch_cache_write_batched(unsigned char* K_CODE_PAGES, kivi_f16* K_SCALE_PAGES,
+                                               kivi_f16* K_ZERO_PAGES, unsigned char* V_CODE_PAGES,
+                                               kivi_f16* V_SCALE_PAGES, kivi_f16* V_ZERO_PAGES,
+                                               kivi_f16* K_RESIDUAL_SCRATCH, kivi_f16* V_RESIDUAL_SCRATCH,
+                                               const kivi_f16* NEW_K, const kivi_f16* NEW_V, const int* BLOCK_TABLE,
+                                               int START_SEQ_LEN, int NUM_NEW, cudaStream_t stream) {
+    if (NUM_NEW < 1 || NUM_NEW > kRefMaxNew) {
+        fprintf(stderr, "NUM_NEW out of range for jac_launch_cache_write_batched: %d\n", NUM_NEW);
+        exit(1);
+    }
+    ref_write(8, KIVI_V1_CACHE, NEW_K, NEW_V, BLOCK_TABLE, START_SEQ_LEN, NUM_NEW, stream);
+}
+
+extern "C" void kivi_b200_cache_write_launch(unsigned char* K_CODE_PAGES, kivi_f16* K_SCALE_PAGES,
+                                             kivi_f16* K_ZERO_PAGES, unsigned char* V_CODE_PAGES,
+                                             kivi_f16* V_SCALE_PAGES, kivi_f16* V_ZERO_PAGES,
+                                             kivi_f16* K_RESIDUAL_SCRATCH, kivi_f16* V_RESIDUAL_SCRATCH,
+                                             const kivi_f16* NEW_K, const kivi_f16* NEW_V, const int64_t* SLOT_MAPPING,
+                                             const int* BLOCK_TABLE, int seq_len, int NKV_RUNTIME, cudaStream_t stream) {
+    (void)SLOT_MAPPING;  // validated by the caller, never used for addressing (source_patch.py:1675)
+    ref_write(NKV_RUNTIME, KIVI_V1_CACHE, NEW_K, NEW_V, BLOCK_TABLE, seq_len - 1, 1, stream);
+}
+extern "C" void kivi_b200_cache_write_batched_launch(unsigned char* K_CODE_PAGES, kivi_f16* K_SCALE_PAGES,
+                                                     kivi_f16* K_ZERO_PAGES, unsigned char* V_CODE_PAGES,
+                                                     kivi_f16* V_SCALE_PAGES, kivi_f16* V_ZERO_PAGES,
+                                                     kivi_f16* K_RESIDUAL_SCRATCH, kivi_f16* V_RESIDUAL_SCRATCH,
+                                                     const kivi_f16* NEW_K, const kivi_f16* NEW_V,
+                                                     const int64_t* SLOT_MAPPING, const int* BLOCK_TABLE,
+                                                     int START_SEQ_LEN, int NUM_NEW, int NKV_RUNTIME,
+                                                     cudaStream_t stream) {
+    (void)SLOT_MAPPING;
+    if (NUM_NEW < 1) return;
+    ref_write(NKV_RUNTIME, KIVI_V1_CACHE, NEW_K, NEW_V, BLOCK_TABLE, START_SEQ_LEN, NUM_NEW, stream);
+}
+
+// The reference's binding declares the hand-CUDA writer with C++ linkage and __half pointers
+// (integrations/vllm_kivi/source_patch.py:624-637); export those exact names too.
+void kivi_cache_write_launch(unsigned char* K_CODE_PAGES, __half* K_SCALE_PAGES, __half* K_ZERO_PAGES,
+                             unsigned char* V_CODE_PAGES, __half* V_SCALE_PAGES, __half* V_ZERO_PAGES,
+                             __half* K_RESIDUAL_SCRATCH, __half* V_RESIDUAL_SCRATCH, const __half* NEW_K,
+                             const __half* NEW_V, const int64_t* SLOT_MAPPING, const int* BLOCK_TABLE, int seq_len,
+                             int NKV_RUNTIME, cudaStream_t stream) {
+    kivi_b200_cache_write_launch(K_CODE_PAGES, (kivi_f16*)K_SCALE_PAGES, (kivi_f16*)K_ZERO_PAGES, V_CODE_PAGES,
+                                 (kivi_f16*)V_SCALE_PAGES, (kivi_f16*)V_ZERO_PAGES, (kivi_f16*)K_RESIDUAL_SCRATCH,
+                                 (kivi_f16*)V_RESIDUAL_SCRATCH, (const kivi_f16*)NEW_K, (const kivi_f16*)NEW_V,
+                                 SLOT_MAPPING, BLOCK_TABLE, seq_len, NKV_RUNTIME, stream);
+}
+void kivi_cache_write_batched_launch(unsigned char* K_CODE_PAGES, __half* K_SCALE_PAGES, __half* K_ZERO_PAGES,
+                                     unsigned char* V_CODE_PAGES, __half* V_SCALE_PAGES, __half* V_ZERO_PAGES,
+                                     __half* K_RESIDUAL_SCRATCH, __half* V_RESIDUAL_SCRATCH, const __half* NEW_K,
+                                     const __half* NEW_V, const int64_t* SLOT_MAPPING, const int* BLOCK_TABLE,
+                                     int START_SEQ_LEN, int NUM_NEW, int NKV_RUNTIME, cudaStream_t stream) {
+    kivi_b200_cache_write_batched_launch(K_CODE_PAGES, (kivi_f16*)K_SCALE_PAGES, (kivi_f16*)K_ZERO_PAGES, V_CODE_PAGES,
+                                         (kivi_f16*)V_SCALE_PAGES, (kivi_f16*)V_ZERO_PAGES,
+                                         (kivi_f16*)K_RESIDUAL_SCRATCH, (kivi_f16*)V_RESIDUAL_SCRATCH,
+                                         (const kivi_f16*)NEW_K, (const kivi_f16*)NEW_V, SLOT_MAPPING, BLOCK_TABLE,
+                                         START_SEQ_LEN, NUM_NEW, NKV_RUNTIME, stream);
+}

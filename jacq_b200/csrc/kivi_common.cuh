@@ -1,0 +1,208 @@
+// Shared definitions of the B200 KIVI kernels: launch-parameter blocks, geometry helpers and the
+// few PTX wrappers (mbarrier, bulk async copy, mma, movmatrix) the kernels use.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/jacq_kivi_b200.h"
+
+namespace kivi {
+
+// Geometry as the kernels see it (all derived values precomputed on the host).
+struct Geom {
+    int nh, nkv, d, b, g, r;
+    int qpk;           // query heads per kv head
+    int hg;            // value channel groups, ceil(D / G)
+    int vg;            // value channel-group width, min(G, D)
+    int scratch_rows;  // R + G
+    int pages_per_group;
+};
+
+inline Geom make_geom(const kivi_geometry& s) {
+    Geom g;
+    g.nh = s.num_q_heads; g.nkv = s.num_kv_heads; g.d = s.head_dim;
+    g.b = s.block_size; g.g = s.group_size; g.r = s.residual;
+    g.qpk = g.nh / g.nkv;
+    g.hg = (g.d + g.g - 1) / g.g;
+    g.vg = g.g < g.d ? g.g : g.d;
+    g.scratch_rows = g.r + g.g;
+    g.pages_per_group = g.g / g.b;
+    return g;
+}
+
+// split_old_tokens of the reference (integrations/vllm_kivi/source_patch.py:1655-1659) with the
+// key group as the age-out unit.
+__host__ __device__ inline int split_old(int seq_len, int residual, int group) {
+    int q = seq_len - residual;
+    if (q < 0) return 0;
+    return (q / group) * group;
+}
+
+struct CachePtrs {
+    uint8_t* k_code; __half* k_scale; __half* k_zero;
+    uint8_t* v_code; __half* v_scale; __half* v_zero;
+    __half* k_scratch; __half* v_scratch;
+};
+
+// How a launch finds each sequence's length, block-table row and scratch slot. The v1 symbols
+// pass host scalars and one shared table; the v2 calls pass device arrays.
+struct SeqAddressing {
+    const int* seq_lens;      // device [n] or nullptr -> seq_len_scalar
+    int seq_len_scalar;
+    const int* block_tables;  // device
+    int bt_stride;            // elements between rows; 0 = one shared table
+    int bt_width;             // entries readable per row
+    const int* slot_ids;      // device [n] or nullptr
+    int slot_shared;          // with slot_ids == nullptr: 1 -> slot 0 for all, 0 -> slot i
+};
+
+__device__ __forceinline__ int seq_len_of(const SeqAddressing& a, int i) {
+    return a.seq_lens ? a.seq_lens[i] : a.seq_len_scalar;
+}
+__device__ __forceinline__ int slot_of(const SeqAddressing& a, int i) {
+    return a.slot_ids ? a.slot_ids[i] : (a.slot_shared ? 0 : i);
+}
+
+// Decode bounds of the reference kernel (crates/jac-codegen-cuda/src/variants.rs:2486-2495) for a
+// runtime geometry: quantised tokens scanned and residual rows read. max_old < 0 = no cap.
+struct DecodeBounds { int old_valid; int res_valid; };
+__host__ __device__ inline DecodeBounds decode_bounds(int seq_len, int residual, int group, int max_old,
+                                                      int bt_width, int block) {
+    int bounded = seq_len < 0 ? 0 : seq_len;
+    if (max_old >= 0 && bounded > max_old + residual) bounded = max_old + residual;
+    int ov = split_old(bounded, residual, group);
+    if (max_old >= 0 && ov > max_old) ov = max_old;
+    // never walk past the block table the caller gave us
+    long long cover = (long long)bt_width * block;
+    if (ov > cover) ov = (int)((cover / group) * group);
+    int rv = bounded - ov;
+    if (rv < 0) rv = 0;
+    if (rv > residual + group) rv = residual + group;
+    DecodeBounds b; b.old_valid = ov; b.res_valid = rv;
+    return b;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Decode launch parameters shared by the generic and the tensor-core kernels.
+struct DecodeParams {
+    Geom geom;
+    CachePtrs cache;
+    SeqAddressing seq;
+    const __half* q;      // [n, NH, D]
+    float* out;           // [n, NH, D]
+    int n;                // queries (sequences) in this launch
+    int max_old;          // reference LQ cap, or -1
+    int retained_pages;   // sparse-retained: pages to scan from the compact table, else -1
+    // split over the context: each CTA takes `chunk_tokens` quantised tokens; the residual rides
+    // with the last chunk. Partials go to the workspace, the last CTA to arrive merges.
+    int chunk_tokens;
+    int max_chunks;
+    float* ws_o;          // [n, NKV, max_chunks, QPK, D]
+    float* ws_ml;         // [n, NKV, max_chunks, QPK, 2]  (running max in log2 units, sum)
+    unsigned int* ws_count;  // [n, NKV] arrival counters, zero between launches
+    int* status;          // device status word (0 = ok), may be nullptr
+};
+
+// Writer launch parameters.
+struct WriteParams {
+    Geom geom;
+    CachePtrs cache;
+    SeqAddressing seq;        // seq_lens = length BEFORE the new tokens
+    const __half* new_k;      // [total_new, NKV, D]
+    const __half* new_v;
+    const int* new_offsets;   // device [n+1] or nullptr -> sequence i owns rows [i*num_new_scalar, ...)
+    int num_new_scalar;
+    int n;
+};
+
+// ---------------------------------------------------------------------------------------------
+// PTX helpers.
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after ~2^22 polls (each poll itself blocks for a hardware-defined time)
+// and reports failure instead of spinning forever.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    for (int it = 0; it < (1 << 22); ++it)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void fence_barrier_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+// 1-D bulk asynchronous copy global -> shared (the TMA engine, no tensor map, no multicast).
+// dst, src 16-byte aligned; bytes a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(smem_u32(dst_smem)), "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+// D(16x8, f32) += A(16x16, f16, row) * B(16x8, f16, col)
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Transpose an 8x8 tile of 16-bit elements held one 32-bit register per lane (row lane/4,
+// columns 2*(lane%4), +1).
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+    uint32_t y;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+    return y;
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_row) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(smem_row)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_row) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(smem_row)));
+}
+
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Host-side launchers implemented in the .cu files.
+cudaError_t launch_cache_write(const WriteParams& p, int max_new_per_seq, cudaStream_t stream);
+cudaError_t launch_decode_generic(const DecodeParams& p, cudaStream_t stream);
+cudaError_t launch_decode_mma(const DecodeParams& p, cudaStream_t stream);
+bool decode_mma_supports(const Geom& g, int retained_pages);
+cudaError_t launch_gemv(const __half* w, const __half* x, __half* y16, float* y32, int out_dim, int in_dim,
+                        int batch, cudaStream_t stream);
+
+}  // namespace kivi
