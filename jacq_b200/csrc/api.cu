@@ -87,11 +87,11 @@ WsLayout ws_layout(const Geom& g, int n, const SplitPlan& sp) {
 }
 
 int run_decode(const Geom& g, const CachePtrs& cache, const SeqAddressing& seq, const __half* q, float* out, int n,
-               int max_old_cap, int max_old_tokens, int retained_pages, void* ws, size_t ws_bytes,
+               int max_seq_cap, int max_old_tokens, int retained_pages, void* ws, size_t ws_bytes,
                cudaStream_t stream) {
     DecodeParams p;
     p.geom = g; p.cache = cache; p.seq = seq; p.q = q; p.out = out; p.n = n;
-    p.max_old = max_old_cap; p.retained_pages = retained_pages; p.status = nullptr;
+    p.max_seq = max_seq_cap; p.retained_pages = retained_pages; p.status = nullptr;
     const SplitPlan sp = plan_split(g, n, max_old_tokens);
     const WsLayout wl = ws_layout(g, n, sp);
     p.chunk_tokens = sp.chunk_tokens;
@@ -182,7 +182,7 @@ void ref_decode(int nh, int nkv, const kivi_f16* Q, const int* seq_lens, int seq
     a.slot_ids = nullptr; a.slot_shared = 1;
     size_t ws_bytes = 0;
     void* ws = ref_workspace(g, n, &ws_bytes, stream);
-    int rc = run_decode(g, cache, a, reinterpret_cast<const __half*>(Q), O, n, kRefLQ, kRefLQ, retained, ws, ws_bytes,
+    int rc = run_decode(g, cache, a, reinterpret_cast<const __half*>(Q), O, n, kRefLQ + kRefR, kRefLQ, retained, ws, ws_bytes,
                         stream);
     if (rc != KIVI_OK) { fprintf(stderr, "jac_launch: %s\n", kivi_b200_status_string(rc)); exit(1); }
 }
@@ -293,9 +293,9 @@ extern "C" int kivi_b200_decode(const kivi_geometry* geom, const kivi_cache* cac
     a.seq_lens = seq_lens; a.seq_len_scalar = 0;
     a.block_tables = block_tables; a.bt_stride = max_blocks_per_seq; a.bt_width = max_blocks_per_seq;
     a.slot_ids = slot_ids; a.slot_shared = 0;
-    // max_old also caps what a sequence longer than the stated bound may walk, so the launch plan
-    // and the workspace stay valid whatever the device-side lengths say.
-    return run_decode(g, cache_ptrs(*cache), a, reinterpret_cast<const __half*>(q), out, batch, max_old, max_old, -1,
+    // max_seq_len also clamps a device-side length beyond the stated bound, so the launch plan and
+    // the workspace stay valid whatever seq_lens holds.
+    return run_decode(g, cache_ptrs(*cache), a, reinterpret_cast<const __half*>(q), out, batch, max_seq_len, max_old, -1,
                       workspace, workspace_bytes, stream);
 }
 

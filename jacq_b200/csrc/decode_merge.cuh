@@ -12,7 +12,7 @@ namespace kivi {
 __device__ __forceinline__ DecodeBounds effective_bounds(const DecodeParams& p, int seq_len) {
     const Geom& g = p.geom;
     const bool sparse = p.retained_pages >= 0;
-    DecodeBounds b = decode_bounds(seq_len, g.r, g.g, p.max_old, sparse ? 0x3fffffff / g.b : p.seq.bt_width, g.b);
+    DecodeBounds b = decode_bounds(seq_len, g.r, g.g, p.max_seq, sparse ? 0x3fffffff / g.b : p.seq.bt_width, g.b);
     if (sparse) {
         int dense_pages = b.old_valid / g.b;
         int rp = p.retained_pages < dense_pages ? p.retained_pages : dense_pages;

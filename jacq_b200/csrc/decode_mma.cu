@@ -1,5 +1,541 @@
+// Paged int4-KIVI decode attention for B200: TMA-staged pages, in-register int4 unpack,
+// tensor-core QK^T and PV over the GQA query group, warp-shuffle softmax, split over the context.
+//
+// What it computes is the reference kernel's recurrence (crates/jac-codegen-cuda/src/variants.rs:
+// 2359-2431, prologue/epilogue :2463-2502): softmax(q . dequant(K) / sqrt(D)) . dequant(V) over the
+// quantised pages named by the block table, then over the fp16 residual rows. The reference runs
+// one warp per query head and re-reads every K/V byte once per query head of the group; here one
+// CTA serves all query heads of a kv head, so each byte is read once.
+//
+// Work split: grid (context chunk, kv head, sequence). A CTA's items are the key groups of its
+// chunk (G tokens = G/B pages each) followed, on the last chunk, by 16-row tiles of the residual.
+// Items go round-robin to 8 warps; each warp keeps its own online-softmax state and the states
+// are merged in shared memory at the end (and across chunks by the last CTA to arrive).
+//
+// Data movement: a ring of shared-memory stages, one item each, filled by 1-D bulk asynchronous
+// copies (cp.async.bulk, the TMA engine without a tensor map: pages are contiguous per kv head)
+// that complete on an mbarrier per stage. The warp that finishes item k issues the copies of item
+// k + stages into the slot it just drained, so no "empty" barrier is needed and 100+ KB stay in
+// flight per SM with no registers spent on it.
+//
+// Arithmetic on codes: a 32-bit word holds 8 channels of one token. Masking a word with
+// 0x000f000f / 0x00f000f0 leaves two nibbles in fp16 *subnormal* position: the pair (n_i, n_i+4)
+// scaled by 2^-24, or (n_i+1, n_i+5) scaled by 2^-20 -- exact fp16 values the tensor core
+// multiplies as they are. So unpacking costs 5 integer ops per 8 codes and no conversion:
+//   QK^T:  sum_c q_c (s_c n_c + z_c) = sum_c (q_c s_c) n_c + sum_c q_c z_c. Per key group the
+//          query fragment is pre-multiplied by the channel scales (odd channels by a further 2^-4
+//          to even out the two nibble positions) and the zero-point term is one extra MMA set.
+//          Channels are contracted, so the odd pairing (i, i+4) only permutes the contraction.
+//   PV:    sum_s p_s (vs_s n_sd + vz_s) = sum_s (p_s vs_s) n_sd + sum_s p_s vz_s. Tokens are
+//          contracted, so a byte-permute first interleaves the same word of two tokens; the
+//          2^-24 / 2^-20 factors land on output channels and are undone in the epilogue.
+// MMA shape m16n8k16 (fp16 in, fp32 accumulate): M = 16 tokens (QK^T) or 16 channels (PV),
+// N = 8 query heads of the group (up to 8 used), so the tensor work wasted on padding is at most
+// 2x for a group of 4. The score tile comes out token-major and is turned head-major for PV by
+// movmatrix. tcgen05 does not fit: its M >= 64 would need the dequantised operand in shared memory
+// or TMEM, i.e. a 4x expanded fp16 copy of every code written by CUDA cores.
+//
+// Rows of a 16-token tile are assigned to MMA rows through a fixed permutation (pair swap on
+// odd pairs) and value words are fetched in a lane-dependent order so that the 16-byte key loads
+// and the 4-byte value loads are shared-memory bank-conflict free for head_dim 128.
 #include "kivi_common.cuh"
+#include "decode_merge.cuh"
+
 namespace kivi {
-bool decode_mma_supports(const Geom&, int) { return false; }
-cudaError_t launch_decode_mma(const DecodeParams&, cudaStream_t) { return cudaErrorNotSupported; }
+namespace {
+
+constexpr int kWarps = 8;
+constexpr int kThreads = kWarps * 32;
+constexpr int kResTile = 16;
+constexpr int kBarBytes = 512;          // room for up to 64 mbarriers
+constexpr int kMaxStages = 24;
+constexpr float kLog2e = 1.4426950408889634f;
+
+template <int D, int G>
+struct Cfg {
+    static constexpr int VG = G < D ? G : D;   // value channel-group width
+    static constexpr int HG = D / VG;          // value channel groups
+    static constexpr int WPR = D / 8;          // 32-bit code words per token row
+    static constexpr int KW = D / 32;          // key words per lane per token
+    static constexpr int NMMA = D / 16;        // MMAs per 16-token tile, QK^T and PV each
+    static constexpr int TILES = G / 16;
+    static constexpr bool HALF = (VG == 32);   // a lane uses half a value word per channel group
+    static constexpr int UNITS = HALF ? HG : WPR / 8;   // value words per lane per token
+    static constexpr int MPU = HALF ? 2 : 4;   // PV MMAs fed by one unit
+    // stage layout (bytes)
+    static constexpr int KC = 0;
+    static constexpr int VC = KC + G * D / 2;
+    static constexpr int KS = VC + G * D / 2;
+    static constexpr int KZ = KS + D * 2;
+    static constexpr int VS = KZ + D * 2;
+    static constexpr int VZ = VS + G * HG * 2;
+    static constexpr int QUANT_BYTES = VZ + G * HG * 2;
+    static constexpr int RES_STRIDE = 2 * D + 16;  // padded fp16 row: ldmatrix rows hit distinct banks
+    static constexpr int RES_V = kResTile * RES_STRIDE;
+    static constexpr int RES_BYTES = 2 * kResTile * RES_STRIDE;
+    static constexpr int STAGE = ((QUANT_BYTES > RES_BYTES ? QUANT_BYTES : RES_BYTES) + 127) / 128 * 128;
+    static constexpr int STATE_FLOATS = 8 * D + 16;  // per warp: O[8][D], m[8], l[8]
+    static_assert(UNITS == 1 || UNITS == 2 || UNITS == 4, "unexpected value-word count");
+    static_assert(NMMA == UNITS * MPU, "value MMA bookkeeping");
+};
+
+// MMA row rho (0..7) of a 16-token tile holds token rho ^ ((rho >> 1) & 1); rows 8..15 add 8.
+__device__ __forceinline__ int row_token(int rho) { return rho ^ ((rho >> 1) & 1); }
+
+__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
+    __half2 r = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
 }
+// (x0,x1),(x2,x3),(x4,x5),(x6,x7) -> (x0,x4),(x1,x5),(x2,x6),(x3,x7): the pairing the nibble masks give.
+__device__ __forceinline__ void pair_by_four(const uint4& v, uint32_t (&o)[4]) {
+    o[0] = __byte_perm(v.x, v.z, 0x5410);
+    o[1] = __byte_perm(v.x, v.z, 0x7632);
+    o[2] = __byte_perm(v.y, v.w, 0x5410);
+    o[3] = __byte_perm(v.y, v.w, 0x7632);
+}
+
+template <int D, int G>
+__global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const DecodeParams p, int nstages) {
+    using C = Cfg<D, G>;
+    extern __shared__ __align__(128) unsigned char smem[];
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem);
+    unsigned char* ring = smem + kBarBytes;
+
+    const Geom& g = p.geom;
+    const int i = blockIdx.z, kv = blockIdx.y, chunk = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = lane >> 2, t = lane & 3;
+    const int swz = (t >> 1) & 1;
+
+    const int seq_len = seq_len_of(p.seq, i);
+    const DecodeBounds bnd = effective_bounds(p, seq_len);
+    const int nchunks = chunks_of(p, bnd.old_valid);
+    if (chunk >= nchunks) return;
+    const int tok0 = chunk * p.chunk_tokens;
+    const int tok1 = min(bnd.old_valid, tok0 + p.chunk_tokens);
+    const int ngroups = (tok1 - tok0) / G;
+    const int nres = (chunk == nchunks - 1) ? (bnd.res_valid + kResTile - 1) / kResTile : 0;
+    const int nitems = ngroups + nres;
+
+    const int* bt = p.seq.block_tables + (size_t)i * p.seq.bt_stride;
+    const int slot = slot_of(p.seq, i);
+    const int B = g.b;
+    const int ppg = G / B;
+    const size_t page_code_bytes = (size_t)B * (D / 2);
+    const size_t page_vparam_elems = (size_t)B * C::HG;
+    const __half* k_res = p.cache.k_scratch + ((size_t)slot * g.nkv + kv) * g.scratch_rows * D;
+    const __half* v_res = p.cache.v_scratch + ((size_t)slot * g.nkv + kv) * g.scratch_rows * D;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < nstages; ++s) mbar_init(&full[s], 1);
+        fence_barrier_init();
+    }
+    __syncthreads();
+
+    // Issue the copies of item k into its ring slot (whole warp; every lane may issue copies).
+    auto issue = [&](int k) {
+        const int s = k % nstages;
+        unsigned char* st = ring + (size_t)s * C::STAGE;
+        uint64_t* bar = &full[s];
+        fence_proxy_async();
+        if (k < ngroups) {
+            if (lane == 0) mbar_expect_tx(bar, (uint32_t)C::QUANT_BYTES);
+            __syncwarp();
+            const int lp0 = (tok0 + k * G) / B;
+            if (lane < ppg) {
+                const size_t head = (size_t)bt[lp0 + lane] * g.nkv + kv;
+                bulk_g2s(st + C::KC + lane * page_code_bytes, p.cache.k_code + head * page_code_bytes,
+                         (uint32_t)page_code_bytes, bar);
+                bulk_g2s(st + C::VC + lane * page_code_bytes, p.cache.v_code + head * page_code_bytes,
+                         (uint32_t)page_code_bytes, bar);
+                bulk_g2s(st + C::VS + lane * page_vparam_elems * 2, p.cache.v_scale + head * page_vparam_elems,
+                         (uint32_t)(page_vparam_elems * 2), bar);
+                bulk_g2s(st + C::VZ + lane * page_vparam_elems * 2, p.cache.v_zero + head * page_vparam_elems,
+                         (uint32_t)(page_vparam_elems * 2), bar);
+                if (lane == 0) {
+                    bulk_g2s(st + C::KS, p.cache.k_scale + head * D, D * 2, bar);
+                    bulk_g2s(st + C::KZ, p.cache.k_zero + head * D, D * 2, bar);
+                }
+            }
+        } else {
+            const int row0 = (k - ngroups) * kResTile;
+            const int rows = min(kResTile, bnd.res_valid - row0);
+            if (lane == 0) mbar_expect_tx(bar, (uint32_t)(rows * 2 * D * 2));
+            __syncwarp();
+            const int rr = lane & 15;
+            if (rr < rows) {
+                const __half* src = (lane < 16 ? k_res : v_res) + (size_t)(row0 + rr) * D;
+                bulk_g2s(st + (lane < 16 ? 0 : C::RES_V) + rr * C::RES_STRIDE, src, D * 2, bar);
+            }
+        }
+    };
+
+    for (int k = warp; k < nitems && k < nstages; k += kWarps) issue(k);
+
+    // ---- per-lane query fragments -----------------------------------------------------------
+    // Lane (r, t): head r of the group (zero when r >= heads per group), channels [D/4*t, D/4*(t+1)).
+    const bool head_on = r < g.qpk;
+    const __half* qrow = p.q + ((size_t)i * g.nh + (size_t)kv * g.qpk + (head_on ? r : 0)) * D;
+    uint32_t qp[4 * C::KW];   // permuted pairs; odd channels carry a 2^-4 factor
+    uint32_t qs[4 * C::KW];   // qp times the key scales of the current group (later: natural pairs)
+    {
+        const uint32_t sixteenth = 0x2C002C00u;  // half2(1/16, 1/16)
+#pragma unroll
+        for (int j = 0; j < C::KW; ++j) {
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (head_on) v = *reinterpret_cast<const uint4*>(qrow + (D / 4) * t + 8 * j);
+            uint32_t o[4];
+            pair_by_four(v, o);
+            qp[4 * j + 0] = o[0];
+            qp[4 * j + 1] = hmul2_u32(o[1], sixteenth);
+            qp[4 * j + 2] = o[2];
+            qp[4 * j + 3] = hmul2_u32(o[3], sixteenth);
+        }
+    }
+
+    const float scale_log2 = rsqrtf((float)D) * kLog2e;
+    const float sc_code = scale_log2 * 16777216.0f;   // undo the 2^-24 of the subnormal codes
+    float m0 = -1.0e30f, m1 = -1.0e30f, l0 = 0.0f, l1 = 0.0f;
+    float zacc[C::HG][2];
+#pragma unroll
+    for (int cg = 0; cg < C::HG; ++cg) zacc[cg][0] = zacc[cg][1] = 0.0f;
+    float o[C::NMMA][4];
+#pragma unroll
+    for (int m = 0; m < C::NMMA; ++m) o[m][0] = o[m][1] = o[m][2] = o[m][3] = 0.0f;
+    bool true_scale = false;  // accumulators still carry the 2^-24 / 2^-20 code factors
+    bool failed = false;
+
+    // Online-softmax update shared by both phases: scores s[4] (log2 units) of tokens (rowA: s0,s1;
+    // rowB: s2,s3) for heads (2t, 2t+1) -> probabilities in s[], state rescaled.
+    auto softmax_step = [&](float (&s)[4]) {
+        float mx0 = fmaxf(s[0], s[2]), mx1 = fmaxf(s[1], s[3]);
+#pragma unroll
+        for (int off = 4; off < 32; off <<= 1) {
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+        }
+        const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+        if (__any_sync(0xffffffffu, n0 > m0 || n1 > m1)) {
+            const float c0 = fast_exp2(m0 - n0), c1 = fast_exp2(m1 - n1);
+            l0 *= c0; l1 *= c1;
+#pragma unroll
+            for (int cg = 0; cg < C::HG; ++cg) { zacc[cg][0] *= c0; zacc[cg][1] *= c1; }
+#pragma unroll
+            for (int m = 0; m < C::NMMA; ++m) { o[m][0] *= c0; o[m][1] *= c1; o[m][2] *= c0; o[m][3] *= c1; }
+            m0 = n0; m1 = n1;
+        }
+        s[0] = fast_exp2(s[0] - m0); s[1] = fast_exp2(s[1] - m1);
+        s[2] = fast_exp2(s[2] - m0); s[3] = fast_exp2(s[3] - m1);
+        l0 += s[0] + s[2];
+        l1 += s[1] + s[3];
+    };
+
+    for (int k = warp; k < nitems; k += kWarps) {
+        const int s_idx = k % nstages;
+        unsigned char* st = ring + (size_t)s_idx * C::STAGE;
+        if (!mbar_wait(&full[s_idx], (uint32_t)((k / nstages) & 1))) { failed = true; break; }
+
+        if (k < ngroups) {
+            // ================= one key group of int4 pages =================
+            float bias0, bias1;
+            {
+                float cb[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                const uint32_t sixteenth = 0x2C002C00u;
+#pragma unroll
+                for (int j = 0; j < C::KW; ++j) {
+                    const uint4 sv = *reinterpret_cast<const uint4*>(st + C::KS + ((D / 4) * t + 8 * j) * 2);
+                    const uint4 zv = *reinterpret_cast<const uint4*>(st + C::KZ + ((D / 4) * t + 8 * j) * 2);
+                    uint32_t sp[4], zp[4];
+                    pair_by_four(sv, sp);
+                    pair_by_four(zv, zp);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) qs[4 * j + e] = hmul2_u32(qp[4 * j + e], sp[e]);
+                    // zero-point term: rows all equal, even channels scaled 2^-4 to match qp's odd 2^-4
+                    const uint32_t z0 = hmul2_u32(zp[0], sixteenth), z2 = hmul2_u32(zp[2], sixteenth);
+                    mma16816(cb, z0, z0, zp[1], zp[1], qp[4 * j + 0], qp[4 * j + 1]);
+                    mma16816(cb, z2, z2, zp[3], zp[3], qp[4 * j + 2], qp[4 * j + 3]);
+                }
+                bias0 = cb[0] * 16.0f * scale_log2;
+                bias1 = cb[1] * 16.0f * scale_log2;
+            }
+
+#pragma unroll 1
+            for (int tile = 0; tile < C::TILES; ++tile) {
+                const int tb = tile * 16;
+                const int rowA = tb + row_token(r);
+                // ---- QK^T: S^T[token, head] ----
+                float sc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                {
+                    uint32_t ka[C::KW], kb[C::KW];
+                    const unsigned char* kpa = st + C::KC + rowA * (D / 2) + (D / 8) * t;
+                    const unsigned char* kpb = kpa + 8 * (D / 2);
+                    if constexpr (C::KW == 4) {
+                        const uint4 a = *reinterpret_cast<const uint4*>(kpa);
+                        const uint4 b = *reinterpret_cast<const uint4*>(kpb);
+                        ka[0] = a.x; ka[1] = a.y; ka[2] = a.z; ka[3] = a.w;
+                        kb[0] = b.x; kb[1] = b.y; kb[2] = b.z; kb[3] = b.w;
+                    } else {
+                        const uint2 a = *reinterpret_cast<const uint2*>(kpa);
+                        const uint2 b = *reinterpret_cast<const uint2*>(kpb);
+                        ka[0] = a.x; ka[1] = a.y;
+                        kb[0] = b.x; kb[1] = b.y;
+                    }
+#pragma unroll
+                    for (int j = 0; j < C::KW; ++j) {
+                        const uint32_t wa = ka[j], wb = kb[j], wa8 = wa >> 8, wb8 = wb >> 8;
+                        mma16816(sc, wa & 0x000f000fu, wb & 0x000f000fu, wa & 0x00f000f0u, wb & 0x00f000f0u,
+                                 qs[4 * j + 0], qs[4 * j + 1]);
+                        mma16816(sc, wa8 & 0x000f000fu, wb8 & 0x000f000fu, wa8 & 0x00f000f0u, wb8 & 0x00f000f0u,
+                                 qs[4 * j + 2], qs[4 * j + 3]);
+                    }
+                }
+                sc[0] = fmaf(sc[0], sc_code, bias0); sc[1] = fmaf(sc[1], sc_code, bias1);
+                sc[2] = fmaf(sc[2], sc_code, bias0); sc[3] = fmaf(sc[3], sc_code, bias1);
+                softmax_step(sc);
+
+                // ---- P' = p * value scale (per channel group), token-major -> head-major ----
+                uint32_t pb01[C::HG], pb23[C::HG];
+                {
+                    const __half* vs = reinterpret_cast<const __half*>(st + C::VS);
+                    const __half* vz = reinterpret_cast<const __half*>(st + C::VZ);
+#pragma unroll
+                    for (int cg = 0; cg < C::HG; ++cg) {
+                        const float sa = __half2float(vs[rowA * C::HG + cg]), sb = __half2float(vs[(rowA + 8) * C::HG + cg]);
+                        const float za = __half2float(vz[rowA * C::HG + cg]), zb = __half2float(vz[(rowA + 8) * C::HG + cg]);
+                        pb01[cg] = movmatrix_trans(pack_half2(sc[0] * sa, sc[1] * sa));
+                        pb23[cg] = movmatrix_trans(pack_half2(sc[2] * sb, sc[3] * sb));
+                        zacc[cg][0] = fmaf(sc[0], za, fmaf(sc[2], zb, zacc[cg][0]));
+                        zacc[cg][1] = fmaf(sc[1], za, fmaf(sc[3], zb, zacc[cg][1]));
+                    }
+                }
+
+                // ---- PV: O^T[channel, head] += V^T[channel, token] P'[token, head] ----
+                {
+                    // k-slots (2t, 2t+1, 2t+8, 2t+9) of this lane are tokens tA, tB, tA+8, tB+8.
+                    const int tA = tb + 2 * t + (t & 1), tB = tb + 2 * t + ((t & 1) ^ 1);
+                    const uint32_t* vw = reinterpret_cast<const uint32_t*>(st + C::VC);
+                    uint32_t wA[C::UNITS], wB[C::UNITS], wA8[C::UNITS], wB8[C::UNITS];
+#pragma unroll
+                    for (int s = 0; s < C::UNITS; ++s) {
+                        // the instruction in slot s fetches unit s ^ swz: lanes that would collide on a
+                        // bank read different words instead
+                        const int u = C::UNITS > 1 ? (s ^ swz) : s;
+                        const int widx = C::HALF ? (4 * u + (r & 3)) : (8 * u + r);
+                        wA[s] = vw[tA * C::WPR + widx];
+                        wB[s] = vw[tB * C::WPR + widx];
+                        wA8[s] = vw[(tA + 8) * C::WPR + widx];
+                        wB8[s] = vw[(tB + 8) * C::WPR + widx];
+                    }
+                    if constexpr (C::UNITS > 1) {
+#pragma unroll
+                        for (int s = 0; s < C::UNITS; s += 2) {
+                            if (swz) {
+                                uint32_t x;
+                                x = wA[s]; wA[s] = wA[s + 1]; wA[s + 1] = x;
+                                x = wB[s]; wB[s] = wB[s + 1]; wB[s + 1] = x;
+                                x = wA8[s]; wA8[s] = wA8[s + 1]; wA8[s + 1] = x;
+                                x = wB8[s]; wB8[s] = wB8[s + 1]; wB8[s + 1] = x;
+                            }
+                        }
+                    }
+                    const uint32_t sel_lo = C::HALF ? ((r >> 2) ? 0x7632u : 0x5410u) : 0x5410u;
+#pragma unroll
+                    for (int u = 0; u < C::UNITS; ++u) {
+                        const int cg = C::HALF ? u : (64 * u) / C::VG;
+                        {
+                            const uint32_t xl = __byte_perm(wA[u], wB[u], sel_lo), xh = __byte_perm(wA8[u], wB8[u], sel_lo);
+                            const uint32_t xl8 = xl >> 8, xh8 = xh >> 8;
+                            mma16816(o[u * C::MPU + 0], xl & 0x000f000fu, xl & 0x00f000f0u, xh & 0x000f000fu,
+                                     xh & 0x00f000f0u, pb01[cg], pb23[cg]);
+                            mma16816(o[u * C::MPU + 1], xl8 & 0x000f000fu, xl8 & 0x00f000f0u, xh8 & 0x000f000fu,
+                                     xh8 & 0x00f000f0u, pb01[cg], pb23[cg]);
+                        }
+                        if constexpr (!C::HALF) {
+                            const uint32_t xl = __byte_perm(wA[u], wB[u], 0x7632), xh = __byte_perm(wA8[u], wB8[u], 0x7632);
+                            const uint32_t xl8 = xl >> 8, xh8 = xh >> 8;
+                            mma16816(o[u * C::MPU + 2], xl & 0x000f000fu, xl & 0x00f000f0u, xh & 0x000f000fu,
+                                     xh & 0x00f000f0u, pb01[cg], pb23[cg]);
+                            mma16816(o[u * C::MPU + 3], xl8 & 0x000f000fu, xl8 & 0x00f000f0u, xh8 & 0x000f000fu,
+                                     xh8 & 0x00f000f0u, pb01[cg], pb23[cg]);
+                        }
+                    }
+                }
+            }
+        } else {
+            // ================= one 16-row tile of the fp16 residual =================
+            if (!true_scale) {
+                true_scale = true;
+#pragma unroll
+                for (int m = 0; m < C::NMMA; ++m) {
+                    o[m][0] *= 16777216.0f; o[m][1] *= 16777216.0f;
+                    o[m][2] *= 1048576.0f;  o[m][3] *= 1048576.0f;
+                }
+                // natural channel pairs of q for this phase: (16m+2t, +1) and (16m+2t+8, +9)
+#pragma unroll
+                for (int m = 0; m < C::NMMA; ++m) {
+                    qs[2 * m] = head_on ? *reinterpret_cast<const uint32_t*>(qrow + 16 * m + 2 * t) : 0u;
+                    qs[2 * m + 1] = head_on ? *reinterpret_cast<const uint32_t*>(qrow + 16 * m + 2 * t + 8) : 0u;
+                }
+            }
+            const int row0 = (k - ngroups) * kResTile;
+            const int rows = min(kResTile, bnd.res_valid - row0);
+            const int rA = row_token(r);
+            float sc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            {
+                // ldmatrix: lanes 0-7 / 8-15 / 16-23 / 24-31 give the row addresses of the four
+                // 8x8 blocks (rows 0-7 | 8-15) x (channels +0 | +8).
+                const int lrow = row_token(lane & 7) + 8 * ((lane >> 3) & 1);
+                const unsigned char* base = st + lrow * C::RES_STRIDE + 16 * (lane >> 4);
+#pragma unroll
+                for (int m = 0; m < C::NMMA; ++m) {
+                    uint32_t a[4];
+                    ldmatrix_x4(a, base + 32 * m);
+                    mma16816(sc, a[0], a[1], a[2], a[3], qs[2 * m], qs[2 * m + 1]);
+                }
+            }
+            const bool onA = rA < rows, onB = rA + 8 < rows;
+            sc[0] = onA ? sc[0] * scale_log2 : -1.0e30f; sc[1] = onA ? sc[1] * scale_log2 : -1.0e30f;
+            sc[2] = onB ? sc[2] * scale_log2 : -1.0e30f; sc[3] = onB ? sc[3] * scale_log2 : -1.0e30f;
+            softmax_step(sc);
+            if (!onA) { sc[0] = 0.0f; sc[1] = 0.0f; }
+            if (!onB) { sc[2] = 0.0f; sc[3] = 0.0f; }
+            const uint32_t pb01 = movmatrix_trans(pack_half2(sc[0], sc[1]));
+            const uint32_t pb23 = movmatrix_trans(pack_half2(sc[2], sc[3]));
+            {
+                const int tA = 2 * t + (t & 1), tB = 2 * t + ((t & 1) ^ 1);
+                const unsigned char* vb = st + C::RES_V;
+                const bool vA = tA < rows, vB = tB < rows, vA8 = tA + 8 < rows, vB8 = tB + 8 < rows;
+#pragma unroll
+                for (int u = 0; u < C::UNITS; ++u) {
+                    // same channel-to-row assignment as the int4 path: rows (r, r+8) of MMA q are
+                    // channels (c0 + 2q, c0 + 2q + 1)
+                    const int c0 = C::HALF ? (C::VG * u + 8 * (r & 3) + 4 * (r >> 2)) : (64 * u + 8 * r);
+                    uint32_t xa[C::MPU], xb[C::MPU], xa8[C::MPU], xb8[C::MPU];
+                    auto load = [&](int tok, bool on, uint32_t (&x)[C::MPU]) {
+                        if constexpr (C::HALF) {
+                            uint2 v = *reinterpret_cast<const uint2*>(vb + tok * C::RES_STRIDE + c0 * 2);
+                            x[0] = on ? v.x : 0u; x[1] = on ? v.y : 0u;
+                        } else {
+                            uint4 v = *reinterpret_cast<const uint4*>(vb + tok * C::RES_STRIDE + c0 * 2);
+                            x[0] = on ? v.x : 0u; x[1] = on ? v.y : 0u; x[2] = on ? v.z : 0u; x[3] = on ? v.w : 0u;
+                        }
+                    };
+                    load(tA, vA, xa); load(tB, vB, xb); load(tA + 8, vA8, xa8); load(tB + 8, vB8, xb8);
+#pragma unroll
+                    for (int q = 0; q < C::MPU; ++q)
+                        mma16816(o[u * C::MPU + q], __byte_perm(xa[q], xb[q], 0x5410), __byte_perm(xa[q], xb[q], 0x7632),
+                                 __byte_perm(xa8[q], xb8[q], 0x5410), __byte_perm(xa8[q], xb8[q], 0x7632), pb01, pb23);
+                }
+            }
+        }
+        __syncwarp();
+        if (k + nstages < nitems) issue(k + nstages);
+    }
+
+    if (failed && p.status && lane == 0) atomicExch(p.status, 1);
+
+    // ---- finish the lane-partial sums and bring the accumulators to true scale ----
+    if (!true_scale) {
+#pragma unroll
+        for (int m = 0; m < C::NMMA; ++m) {
+            o[m][0] *= 16777216.0f; o[m][1] *= 16777216.0f;
+            o[m][2] *= 1048576.0f;  o[m][3] *= 1048576.0f;
+        }
+    }
+#pragma unroll
+    for (int off = 4; off < 32; off <<= 1) {
+        l0 += __shfl_xor_sync(0xffffffffu, l0, off);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, off);
+#pragma unroll
+        for (int cg = 0; cg < C::HG; ++cg) {
+            zacc[cg][0] += __shfl_xor_sync(0xffffffffu, zacc[cg][0], off);
+            zacc[cg][1] += __shfl_xor_sync(0xffffffffu, zacc[cg][1], off);
+        }
+    }
+
+    __syncthreads();  // every stage has been consumed: the ring can hold the warp states
+    float* state = reinterpret_cast<float*>(ring) + (size_t)warp * C::STATE_FLOATS;
+#pragma unroll
+    for (int u = 0; u < C::UNITS; ++u) {
+        const int c0 = C::HALF ? (C::VG * u + 8 * (r & 3) + 4 * (r >> 2)) : (64 * u + 8 * r);
+        const int cg = C::HALF ? u : (64 * u) / C::VG;
+#pragma unroll
+        for (int q = 0; q < C::MPU; ++q) {
+            const float* acc = o[u * C::MPU + q];
+            state[(2 * t) * D + c0 + 2 * q] = acc[0] + zacc[cg][0];
+            state[(2 * t + 1) * D + c0 + 2 * q] = acc[1] + zacc[cg][1];
+            state[(2 * t) * D + c0 + 2 * q + 1] = acc[2] + zacc[cg][0];
+            state[(2 * t + 1) * D + c0 + 2 * q + 1] = acc[3] + zacc[cg][1];
+        }
+    }
+    if (r == 0) {
+        state[8 * D + 2 * t] = m0; state[8 * D + 2 * t + 1] = m1;
+        state[8 * D + 8 + 2 * t] = l0; state[8 * D + 8 + 2 * t + 1] = l1;
+    }
+    __syncthreads();
+
+    const float* all = reinterpret_cast<const float*>(ring);
+    for (int idx = threadIdx.x; idx < g.qpk * D; idx += kThreads) {
+        const int hq = idx / D, d = idx - hq * D;
+        float mx = -1.0e30f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) mx = fmaxf(mx, all[w * C::STATE_FLOATS + 8 * D + hq]);
+        float l = 0.0f, acc = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+            const float* sw = all + w * C::STATE_FLOATS;
+            const float wt = fast_exp2(sw[8 * D + hq] - mx);
+            l += wt * sw[8 * D + 8 + hq];
+            acc += wt * sw[hq * D + d];
+        }
+        if (nchunks == 1) {
+            p.out[((size_t)i * g.nh + (size_t)kv * g.qpk + hq) * D + d] = acc / fmaxf(l, 1.0e-30f);
+        } else {
+            const size_t part = (((size_t)i * g.nkv + kv) * p.max_chunks + chunk) * g.qpk + hq;
+            p.ws_o[part * D + d] = acc;
+            if (d == 0) { p.ws_ml[part * 2] = mx; p.ws_ml[part * 2 + 1] = l; }
+        }
+    }
+    if (nchunks > 1) merge_when_last(p, i, kv, nchunks);
+}
+
+template <int D, int G>
+cudaError_t launch(const DecodeParams& p, cudaStream_t stream) {
+    using C = Cfg<D, G>;
+    constexpr int kBudget = 226 * 1024;   // of the 227 KB a CTA may opt into
+    int nstages = (kBudget - kBarBytes) / C::STAGE;
+    if (nstages > kMaxStages) nstages = kMaxStages;
+    const int state_bytes = kWarps * C::STATE_FLOATS * (int)sizeof(float);
+    while (nstages * C::STAGE < state_bytes) ++nstages;
+    const int smem = kBarBytes + nstages * C::STAGE;
+    cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<D, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    decode_mma_kernel<D, G><<<dim3(p.max_chunks, p.geom.nkv, p.n), kThreads, smem, stream>>>(p, nstages);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+bool decode_mma_supports(const Geom& g, int retained_pages) {
+    if (g.d != 64 && g.d != 128) return false;
+    if (g.g != 32 && g.g != 64 && g.g != 128) return false;
+    if (g.qpk > 8) return false;
+    if (g.pages_per_group > 32) return false;
+    if ((g.b * g.hg * 2) % 16 || (g.b * g.d / 2) % 16) return false;  // bulk copies move 16-byte multiples
+    if (retained_pages >= 0 && g.g != g.b) return false;  // a compact table breaks groups that span pages
+    return true;
+}
+
+cudaError_t launch_decode_mma(const DecodeParams& p, cudaStream_t stream) {
+    if (p.n <= 0) return cudaSuccess;
+    const int d = p.geom.d, g = p.geom.g;
+    if (d == 128 && g == 128) return launch<128, 128>(p, stream);
+    if (d == 128 && g == 64) return launch<128, 64>(p, stream);
+    if (d == 128 && g == 32) return launch<128, 32>(p, stream);
+    if (d == 64 && g == 128) return launch<64, 128>(p, stream);
+    if (d == 64 && g == 64) return launch<64, 64>(p, stream);
+    if (d == 64 && g == 32) return launch<64, 32>(p, stream);
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace kivi

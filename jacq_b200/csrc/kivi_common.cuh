@@ -66,14 +66,15 @@ __device__ __forceinline__ int slot_of(const SeqAddressing& a, int i) {
 }
 
 // Decode bounds of the reference kernel (crates/jac-codegen-cuda/src/variants.rs:2486-2495) for a
-// runtime geometry: quantised tokens scanned and residual rows read. max_old < 0 = no cap.
+// runtime geometry: quantised tokens scanned and residual rows read. max_seq is the longest
+// sequence the launch was planned for (the reference's LQ + RESIDUAL); longer lengths are clamped
+// to it, as the reference does. max_seq < 0 = no cap.
 struct DecodeBounds { int old_valid; int res_valid; };
-__host__ __device__ inline DecodeBounds decode_bounds(int seq_len, int residual, int group, int max_old,
+__host__ __device__ inline DecodeBounds decode_bounds(int seq_len, int residual, int group, int max_seq,
                                                       int bt_width, int block) {
     int bounded = seq_len < 0 ? 0 : seq_len;
-    if (max_old >= 0 && bounded > max_old + residual) bounded = max_old + residual;
+    if (max_seq >= 0 && bounded > max_seq) bounded = max_seq;
     int ov = split_old(bounded, residual, group);
-    if (max_old >= 0 && ov > max_old) ov = max_old;
     // never walk past the block table the caller gave us
     long long cover = (long long)bt_width * block;
     if (ov > cover) ov = (int)((cover / group) * group);
@@ -93,7 +94,7 @@ struct DecodeParams {
     const __half* q;      // [n, NH, D]
     float* out;           // [n, NH, D]
     int n;                // queries (sequences) in this launch
-    int max_old;          // reference LQ cap, or -1
+    int max_seq;          // longest sequence the launch is planned for (reference: LQ + RESIDUAL), or -1
     int retained_pages;   // sparse-retained: pages to scan from the compact table, else -1
     // split over the context: each CTA takes `chunk_tokens` quantised tokens; the residual rides
     // with the last chunk. Partials go to the workspace, the last CTA to arrive merges.
