@@ -1,0 +1,417 @@
+"""Benchmark of the int4-KIVI paged decode attention on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--workload NAME]
+
+A step is ONE pass of the paged decode attention over one batch of sequences for one layer (the
+library's kivi_b200_decode: one kernel launch). Workload at one GPU: the Mistral-7B decode shape
+(32 q / 8 kv heads, head_dim 128, batch 128, context 8192, block 16, group 128, residual 128) on
+seeded synthetic q/K/V (fp16 N(0,1), 3 of 128 key channels per head x10); the cache is built on
+the device by the library's own writer. With N GPUs every rank holds its own 128 sequences
+(independent sequences, no collective: weak scaling); the value is the aggregate over ranks.
+
+metric / value  achieved HBM GB/s = algorithmic bytes of the step / device time, inputs resident
+                in HBM; tokens/s rides along as `tokens_per_s`
+e2e             the same bytes over the time of a full serving step through the public API with
+                HOST buffers: pinned q and the step's new K/V rows copied host->device, cache write,
+                decode, output copied device->host
+roofline        achieved = algorithmic bytes per launch / mean CUDA-event time of the decode launch,
+                against the measured HBM copy bandwidth in MEASURED_PEAKS.json
+cpu_baseline    the scalar CPU oracle (test infrastructure, a port of the reference's kernel math)
+                timed on the host cores on a bounded sample of the same workload
+--impl reference  times that CPU port with all host threads (the reference's own implementation of
+                this path is CUDA-only and cannot express this geometry)
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOADS = {
+    # name: (case key in tests.helpers.CONFIGS, batch, context)
+    "mistral7b_decode_attn_b128_t8192": ("mistral7b", 128, 8192),
+    "qwen05b_decode_attn_b64_t4096": ("qwen05b", 64, 4096),
+    "tinyllama_decode_attn_b4_t512": ("tinyllama", 4, 512),
+    "reflane_decode_attn_b64_t4096": ("reflane", 64, 4096),
+    # same kernel and geometry as the default, a quarter of the batch: 373 MB of pages, still 3x the L2;
+    # sized for `ncu --set full` captures
+    "mistral7b_decode_attn_b32_t8192": ("mistral7b", 32, 8192),
+}
+DEFAULT_WORKLOAD = "mistral7b_decode_attn_b128_t8192"
+METRIC = "KIVI decode-attn achieved HBM GB/s"
+
+
+def _peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def _dist_env():
+    return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+
+
+# ------------------------------------------------------------------------------------------------
+# synthetic cache, built on the device with the library's writer
+
+def build_cache(case, batch, context, device, spare_tokens=0, seed=20261125):
+    import torch
+    from jacq_b200.cache import KiviCache
+    from tests import helpers
+    lay = helpers.layout_of(case)
+    pages = lay.old_pages(context + spare_tokens) + 1
+    cache = KiviCache(lay, batch * pages, batch, pages, device)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+    cache.set_block_tables(torch.randperm(batch * pages, device=device, generator=gen).to(torch.int32)
+                           .reshape(batch, pages))
+    outl = torch.from_numpy(helpers.outlier_channels(case, seed)).to(device)      # [NKV, n]
+    kscale = torch.ones((case.nkv, case.d), device=device, dtype=torch.float16)
+    kscale.scatter_(1, outl.long(), 10.0)
+    chunk, write_ms, write_bytes = 512, [], 0
+    for start in range(0, context, chunk):
+        n = min(chunk, context - start)
+        k = torch.randn((batch * n, case.nkv, case.d), device=device, dtype=torch.float16, generator=gen) * kscale
+        v = torch.randn((batch * n, case.nkv, case.d), device=device, dtype=torch.float16, generator=gen)
+        offs = torch.arange(batch + 1, device=device, dtype=torch.int32) * n
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        cache.write(k, v, offs, max_new_per_seq=n, max_start_seq_len=start)
+        e1.record()
+        torch.cuda.synchronize(device)
+        write_ms.append(e0.elapsed_time(e1))
+        write_bytes = k.numel() * 2 * 2
+    q = torch.randn((batch, case.nh, case.d), device=device, dtype=torch.float16, generator=gen)
+    writer = {"ms_per_512_token_chunk": statistics.median(write_ms),
+              "input_gbs": write_bytes / statistics.median(write_ms) / 1e6}
+    return cache, q, writer
+
+
+def sample_to_oracle(cache, case, seqs):
+    """Host copy (OracleCache) of the chosen sequences, pages renumbered densely."""
+    import torch
+    from oracle import kivi_oracle as ko
+    from tests import helpers
+    geom = helpers.oracle_geometry(case)
+    pages = cache.max_blocks_per_seq
+    idx = cache.block_tables[seqs].reshape(-1).long()
+    oc = ko.OracleCache(geom, len(seqs) * pages, len(seqs))
+    t = cache.tensors
+    for name in ("K_CODE_PAGES", "K_SCALE_PAGES", "K_ZERO_PAGES", "V_CODE_PAGES", "V_SCALE_PAGES", "V_ZERO_PAGES"):
+        src = getattr(t, name).index_select(0, idx)
+        getattr(oc, helpers.ORACLE_FIELD[name])[...] = helpers.to_bits(src)
+    sel = torch.tensor(seqs, device=cache.device)
+    oc.k_scratch[...] = helpers.to_bits(t.K_RESIDUAL_SCRATCH.index_select(0, sel))
+    oc.v_scratch[...] = helpers.to_bits(t.V_RESIDUAL_SCRATCH.index_select(0, sel))
+    tables = np.arange(len(seqs) * pages, dtype=np.int32).reshape(len(seqs), pages)
+    return oc, tables
+
+
+def cpu_baseline(cache, q, case, context, nthreads, target_seconds=12.0):
+    """Time the CPU oracle on a bounded sample of the workload; also checks the GPU output."""
+    from oracle import kivi_oracle as ko
+    from tests import helpers
+    lay = helpers.layout_of(case)
+    batch = q.shape[0]
+    n = min(batch, 2)
+    oc, tables = sample_to_oracle(cache, case, list(range(n)))
+    qh = helpers.to_bits(q[:n])
+    lens = np.full(n, context, np.int32)
+    t0 = time.perf_counter()
+    ko.decode_batch(oc, qh, tables, lens, mode=0, nthreads=nthreads)
+    probe = time.perf_counter() - t0
+    n = int(max(1, min(batch, round(n * target_seconds / max(probe, 1e-6)))))
+    n = max(n, min(batch, nthreads // max(1, case.nh) + 1))
+    oc, tables = sample_to_oracle(cache, case, list(range(n)))
+    qh = helpers.to_bits(q[:n])
+    lens = np.full(n, context, np.int32)
+    t0 = time.perf_counter()
+    want = ko.decode_batch(oc, qh, tables, lens, mode=0, nthreads=nthreads)
+    secs = time.perf_counter() - t0
+    sample_bytes = lay.decode_algorithmic_bytes(context) * n
+    return {"value": sample_bytes / secs / 1e9, "unit": "GB/s", "cores": nthreads, "kind": "port",
+            "sample": f"{n} of {batch} sequences of the workload, all heads, {secs:.1f} s",
+            "tokens_per_s": n / secs}, want, n
+
+
+# ------------------------------------------------------------------------------------------------
+# clocks
+
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.proc = None
+        self.gpu_index = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu_index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------------------------
+
+def run_b200(args):
+    import torch
+    import torch.distributed as dist
+    from tests import helpers
+    from jacq_b200 import _native
+    _native.lib()   # fail loudly when the CUDA library is missing: there is no other path
+
+    rank, local_rank, world = _dist_env()
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
+    device = torch.device(f"cuda:{local_rank}")
+    torch.cuda.set_device(device)
+
+    key, batch, context = WORKLOADS[args.workload]
+    case = helpers.CONFIGS[key]
+    lay = helpers.layout_of(case)
+    e2e_steps = args.steps
+    cache, q, writer = build_cache(case, batch, context, device, spare_tokens=e2e_steps + args.warmup + 8,
+                                   seed=20261125 + rank)
+    out = torch.empty((batch, case.nh, case.d), dtype=torch.float32, device=device)
+    step_bytes = lay.decode_algorithmic_bytes(context) * batch
+
+    if args.profile_only:
+        # a handful of launches and nothing else: the command line ncu wraps
+        for _ in range(args.warmup + args.steps):
+            cache.decode(q, out, max_seq_len=context)
+        torch.cuda.synchronize(device)
+        print(json.dumps({"profile_only": True, "workload": args.workload, "launches": args.warmup + args.steps,
+                          "algorithmic_bytes_per_launch": step_bytes}))
+        return
+
+    # ---- kernel-resident measurement: `value` and `roofline` --------------------------------
+    for _ in range(max(3, args.warmup)):
+        cache.decode(q, out, max_seq_len=context)
+    torch.cuda.synchronize(device)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(device)
+    events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    # keep the GPU busy long enough for clock samples: repeat the K timed steps in rounds
+    rounds = max(1, int(0.6 / max(1e-4, args.steps * 4e-4)))
+    per_step_ms = []
+    for rnd in range(rounds):
+        for e0, e1 in events:
+            e0.record()
+            cache.decode(q, out, max_seq_len=context)
+            e1.record()
+        torch.cuda.synchronize(device)
+        if rnd == rounds - 1:
+            per_step_ms = [e0.elapsed_time(e1) for e0, e1 in events]
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(device)
+    clocks = sampler.stop() if rank == 0 else None
+    total_ms = float(sum(per_step_ms))
+    if world > 1:
+        t = torch.tensor([total_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+    value = step_bytes * world / (ms_per_step * 1e-3) / 1e9
+
+    # ---- CPU baseline on a bounded sample (rank 0, one GPU only); doubles as a parity check ------
+    base, parity = None, None
+    if args.cpu_baseline and rank == 0:
+        nthreads = os.cpu_count() or 1
+        base, want, n = cpu_baseline(cache, q, case, context, nthreads)
+        got = out[:n].cpu().numpy()
+        err = float(np.abs(got - want).max())
+        parity = {"sequences": n, "max_abs_err": err, "within_1e-2": bool((np.abs(got - want) <= 1e-2 + 1e-2 * np.abs(want)).all())}
+
+    # ---- end to end through the public API with host buffers ---------------------------------
+    q_host = q.cpu().pin_memory()
+    out_host = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+    gen = torch.Generator().manual_seed(7 + rank)
+    nk_host = torch.randn((batch, case.nkv, case.d), generator=gen).to(torch.float16).pin_memory()
+    nv_host = torch.randn((batch, case.nkv, case.d), generator=gen).to(torch.float16).pin_memory()
+    q_dev, nk_dev, nv_dev = torch.empty_like(q), torch.empty_like(nk_host, device=device), torch.empty_like(nv_host, device=device)
+    offs = torch.arange(batch + 1, device=device, dtype=torch.int32)
+    cur = context
+
+    def serving_step(cur_len):
+        q_dev.copy_(q_host, non_blocking=True)
+        nk_dev.copy_(nk_host, non_blocking=True)
+        nv_dev.copy_(nv_host, non_blocking=True)
+        cache.write(nk_dev, nv_dev, offs, max_new_per_seq=1, max_start_seq_len=cur_len)
+        cache.decode(q_dev, out, max_seq_len=cur_len + 1)
+        out_host.copy_(out, non_blocking=True)
+        torch.cuda.synchronize(device)
+
+    for _ in range(max(3, args.warmup)):
+        serving_step(cur)
+        cur += 1
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(device)
+    e2e_bytes = 0
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        serving_step(cur)
+        cur += 1
+        e2e_bytes += lay.decode_algorithmic_bytes(cur) * batch
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e_value = e2e_bytes * world / e2e_s / 1e9
+    h2d = q_host.numel() * 2 + nk_host.numel() * 2 * 2
+    d2h = out_host.numel() * 4
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    peak, peak_kind = _peaks()
+    kernel_ms = statistics.mean(per_step_ms)
+    achieved = step_bytes / (kernel_ms * 1e-3) / 1e9
+    line = {
+        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "u4 codes, f16 params/residual, f32 accumulate", "data": "synthetic",
+        "config": {"workload": args.workload, "geometry": {"nh": case.nh, "nkv": case.nkv, "head_dim": case.d,
+                                                            "block": case.b, "group": case.g, "residual": case.r},
+                   "batch_per_gpu": batch, "context": context, "algorithmic_bytes_per_step_per_gpu": step_bytes,
+                   "l2": "inputs (1.49 GB of pages per GPU) exceed the 126 MB L2; no flush between iterations",
+                   "parallelism": f"sequences sharded over {world} GPU(s), no collective"},
+        "tokens_per_s": batch * world / (ms_per_step * 1e-3),
+        "pct_of_8TBs_nominal": 100.0 * value / world / 8000.0,
+        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": e2e_s / e2e_steps * 1e3, "tokens_per_s": batch * world / (e2e_s / e2e_steps),
+                "what": "pinned q + new K/V rows H2D, cache write (1 token/sequence), decode, O D2H"},
+        "gpu_launches": args.steps,
+        "clocks": clocks,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_source": f"{peak_kind} HBM copy bandwidth",
+                     "kernel": "decode_mma_kernel", "ms_per_launch": kernel_ms},
+        "writer": writer,
+    }
+    line["cpu_baseline"] = base
+    line["parity_vs_cpu_port"] = parity
+    if world > 1:
+        dist.destroy_process_group()
+    print(json.dumps(line))
+
+
+def run_reference(args):
+    """Reference arm: the CPU port of the reference's writer + decode math, all host threads, no GPU."""
+    rank, local_rank, world = _dist_env()
+    if rank != 0:
+        return
+    from tests import helpers
+    from oracle import kivi_oracle as ko
+    key, batch, context = WORKLOADS[args.workload]
+    case = helpers.CONFIGS[key]
+    geom = helpers.oracle_geometry(case)
+    lay = helpers.layout_of(case)
+    nthreads = os.cpu_count() or 1
+    n = min(batch, max(1, nthreads // 8))
+    pages = lay.old_pages(context) + 1
+    tables = helpers.shuffled_block_tables(n, pages, n * pages)
+    oc = ko.OracleCache(geom, n * pages, n)
+    kv = [helpers.make_kv(case, context, stream=i) for i in range(n)]
+    ko.write_batch(oc, np.concatenate([k for k, _ in kv]), np.concatenate([v for _, v in kv]), tables,
+                   np.zeros(n, np.int32), np.arange(n + 1, dtype=np.int32) * context, nthreads=nthreads)
+    qh = helpers.make_q(case, n)
+    lens = np.full(n, context, np.int32)
+    step_bytes = lay.decode_algorithmic_bytes(context) * n
+    warm = min(args.warmup, 1)
+    for _ in range(warm):
+        ko.decode_batch(oc, qh, tables, lens, mode=0, nthreads=nthreads)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        ko.decode_batch(oc, qh, tables, lens, mode=0, nthreads=nthreads)
+    secs = (time.perf_counter() - t0) / args.steps
+    value = step_bytes / secs / 1e9
+    sample = f"each step = {n} of {batch} sequences of the workload, all heads"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": warm, "ms_per_step": secs * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32 scalar", "data": "synthetic",
+        "config": {"workload": args.workload, "note": "the reference's own implementation of this path is CUDA "
+                   "only and is compiled for block = group = 32 / head_dim 128 / context <= 4096, so it cannot run "
+                   "this geometry; this arm times the CPU port of its kernel math (oracle/) on the host cores"},
+        "tokens_per_s": n / secs,
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": nthreads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
+    ap.add_argument("--profile-only", action="store_true",
+                    help="build the cache, run warmup+steps decode launches and exit (for ncu)")
+    args = ap.parse_args()
+    _, _, world = _dist_env()
+    if args.gpus != world and world == 1 and args.gpus > 1:
+        # launched without torchrun: spawn the ranks ourselves
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", "29571", __file__] + sys.argv[1:]
+        raise SystemExit(subprocess.call(cmd))
+    if world > 1:
+        args.cpu_baseline = False   # rank 0 at N = 1 only
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -22,6 +22,10 @@ NVCC_FLAGS = [
 ]
 
 
+# compile-time tunables that may be overridden from the environment when experimenting
+TUNABLES = ("KIVI_DECODE_WARPS",)
+
+
 def sources() -> list[Path]:
     return sorted(CSRC.glob("*.cu"))
 
@@ -41,9 +45,10 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     LIB_DIR.mkdir(exist_ok=True)
     objs = []
     procs = []
+    extra = [f"-D{name}={os.environ[name]}" for name in TUNABLES if name in os.environ]
     for src in sources():
         obj = LIB_DIR / (src.stem + ".o")
-        cmd = [nvcc, *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+        cmd = [nvcc, *NVCC_FLAGS, *extra, "-c", str(src), "-o", str(obj)]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))

@@ -1,4 +1,4 @@
-// Paged int4-KIVI decode attention for B200: TMA-staged pages, in-register int4 unpack,
+// Paged int4-KIVI decode attention for B200: asynchronously staged pages, in-register int4 unpack,
 // tensor-core QK^T and PV over the GQA query group, warp-shuffle softmax, split over the context.
 //
 // What it computes is the reference kernel's recurrence (crates/jac-codegen-cuda/src/variants.rs:
@@ -7,16 +7,20 @@
 // one warp per query head and re-reads every K/V byte once per query head of the group; here one
 // CTA serves all query heads of a kv head, so each byte is read once.
 //
-// Work split: grid (context chunk, kv head, sequence). A CTA's items are the key groups of its
-// chunk (G tokens = G/B pages each) followed, on the last chunk, by 16-row tiles of the residual.
-// Items go round-robin to 8 warps; each warp keeps its own online-softmax state and the states
-// are merged in shared memory at the end (and across chunks by the last CTA to arrive).
+// Work split: grid (context chunk, kv head, sequence). A CTA's key groups go round-robin to its
+// warps; each warp keeps its own online-softmax state, the states are merged in shared memory at
+// the end, and across chunks by the last CTA to arrive. The last chunk also takes the residual
+// rows, in 16-row tiles.
 //
-// Data movement: a ring of shared-memory stages, one item each, filled by 1-D bulk asynchronous
-// copies (cp.async.bulk, the TMA engine without a tensor map: pages are contiguous per kv head)
-// that complete on an mbarrier per stage. The warp that finishes item k issues the copies of item
-// k + stages into the slot it just drained, so no "empty" barrier is needed and 100+ KB stay in
-// flight per SM with no registers spent on it.
+// Data movement: every warp owns a small ring of shared-memory slots of 32 tokens each (codes of
+// K and V, the value scale/zero of those tokens, and with the first slot of a group its key
+// scale/zero). Code pages arrive by 1-D bulk asynchronous copies (cp.async.bulk, the TMA engine
+// without a tensor map: a page is contiguous per kv head); the small parameter arrays and the fp16
+// residual rows arrive by 16-byte cp.async, one warp instruction for a whole slot. Both complete on
+// the slot's mbarrier. A warp fills its own slots and is the only one to wait on them: after
+// draining a slot it issues the copies of the slot-count-th next one into it, so there is no
+// "empty" barrier and no cross-warp synchronisation until the final merge, every warp keeps
+// several slots in flight, and no registers are spent on staging.
 //
 // Arithmetic on codes: a 32-bit word holds 8 channels of one token. Masking a word with
 // 0x000f000f / 0x00f000f0 leaves two nibbles in fp16 *subnormal* position: the pair (n_i, n_i+4)
@@ -35,21 +39,22 @@
 // movmatrix. tcgen05 does not fit: its M >= 64 would need the dequantised operand in shared memory
 // or TMEM, i.e. a 4x expanded fp16 copy of every code written by CUDA cores.
 //
-// Rows of a 16-token tile are assigned to MMA rows through a fixed permutation (pair swap on
-// odd pairs) and value words are fetched in a lane-dependent order so that the 16-byte key loads
-// and the 4-byte value loads are shared-memory bank-conflict free for head_dim 128.
+// The running maximum is only raised (and the accumulators rescaled) when a tile exceeds it by
+// more than 2^8: probabilities then stay below 256, far inside fp16/fp32 range, and the 36
+// multiplies of a rescale are paid a handful of times per sequence instead of on every new maximum.
 #include "kivi_common.cuh"
 #include "decode_merge.cuh"
 
 namespace kivi {
 namespace {
 
-constexpr int kWarps = 8;
-constexpr int kThreads = kWarps * 32;
 constexpr int kResTile = 16;
-constexpr int kBarBytes = 512;          // room for up to 64 mbarriers
-constexpr int kMaxStages = 24;
+constexpr int kSub = 32;                 // tokens per ring slot
+constexpr int kBarBytes = 512;           // room for 64 mbarriers
+constexpr int kMaxSlotsPerWarp = 4;
+constexpr int kBarArrivals = 33;         // lane 0's expect_tx arrive + one cp.async arrive per lane
 constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kRescaleSlack = 8.0f;    // log2 units
 
 template <int D, int G>
 struct Cfg {
@@ -58,28 +63,31 @@ struct Cfg {
     static constexpr int WPR = D / 8;          // 32-bit code words per token row
     static constexpr int KW = D / 32;          // key words per lane per token
     static constexpr int NMMA = D / 16;        // MMAs per 16-token tile, QK^T and PV each
-    static constexpr int TILES = G / 16;
+    static constexpr int SUBS = G / kSub;      // ring slots per key group
     static constexpr bool HALF = (VG == 32);   // a lane uses half a value word per channel group
     static constexpr int UNITS = HALF ? HG : WPR / 8;   // value words per lane per token
     static constexpr int MPU = HALF ? 2 : 4;   // PV MMAs fed by one unit
-    // stage layout (bytes)
+    // slot layout (bytes)
     static constexpr int KC = 0;
-    static constexpr int VC = KC + G * D / 2;
-    static constexpr int KS = VC + G * D / 2;
+    static constexpr int VC = KC + kSub * D / 2;
+    static constexpr int VS = VC + kSub * D / 2;
+    static constexpr int VZ = VS + kSub * HG * 2;
+    static constexpr int KS = VZ + kSub * HG * 2;
     static constexpr int KZ = KS + D * 2;
-    static constexpr int VS = KZ + D * 2;
-    static constexpr int VZ = VS + G * HG * 2;
-    static constexpr int QUANT_BYTES = VZ + G * HG * 2;
-    static constexpr int RES_STRIDE = 2 * D + 16;  // padded fp16 row: ldmatrix rows hit distinct banks
-    static constexpr int RES_V = kResTile * RES_STRIDE;
-    static constexpr int RES_BYTES = 2 * kResTile * RES_STRIDE;
-    static constexpr int STAGE = ((QUANT_BYTES > RES_BYTES ? QUANT_BYTES : RES_BYTES) + 127) / 128 * 128;
-    static constexpr int STATE_FLOATS = 8 * D + 16;  // per warp: O[8][D], m[8], l[8]
+    static constexpr int QUANT_BYTES = KZ + D * 2;
+    static constexpr int CODE_BYTES = kSub * D;        // K + V codes of one slot
+    static constexpr int RES_STRIDE = 2 * D + 16;      // padded fp16 row: ldmatrix rows hit distinct banks
+    static constexpr int RES_BYTES = kResTile * RES_STRIDE;   // 16 key rows OR 16 value rows
+    static constexpr int SLOT = ((QUANT_BYTES > RES_BYTES ? QUANT_BYTES : RES_BYTES) + 127) / 128 * 128;
+    static constexpr int Q_BYTES = KW * 32 * 16;       // permuted query fragments of all lanes
+    static constexpr int STATE_FLOATS = 8 * D + 16;    // per warp: O[8][D], m[8], l[8]
+    static_assert(G % kSub == 0, "a key group must be whole slots");
     static_assert(UNITS == 1 || UNITS == 2 || UNITS == 4, "unexpected value-word count");
     static_assert(NMMA == UNITS * MPU, "value MMA bookkeeping");
 };
 
 // MMA row rho (0..7) of a 16-token tile holds token rho ^ ((rho >> 1) & 1); rows 8..15 add 8.
+// With this pair swap the 16-byte key loads of a quarter warp touch rows of both parities.
 __device__ __forceinline__ int row_token(int rho) { return rho ^ ((rho >> 1) & 1); }
 
 __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
@@ -94,18 +102,18 @@ __device__ __forceinline__ void pair_by_four(const uint4& v, uint32_t (&o)[4]) {
     o[3] = __byte_perm(v.y, v.w, 0x7632);
 }
 
-template <int D, int G>
-__global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const DecodeParams p, int nstages) {
+template <int D, int G, int W>
+__global__ void __launch_bounds__(W * 32, 1) decode_mma_kernel(const DecodeParams p, int per_warp) {
     using C = Cfg<D, G>;
     extern __shared__ __align__(128) unsigned char smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
-    unsigned char* ring = smem + kBarBytes;
+    uint4* qsm = reinterpret_cast<uint4*>(smem + kBarBytes);
+    unsigned char* ring = smem + kBarBytes + C::Q_BYTES;
 
     const Geom& g = p.geom;
     const int i = blockIdx.z, kv = blockIdx.y, chunk = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = lane >> 2, t = lane & 3;
-    const int swz = (t >> 1) & 1;
 
     const int seq_len = seq_len_of(p.seq, i);
     const DecodeBounds bnd = effective_bounds(p, seq_len);
@@ -115,86 +123,127 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const DecodePar
     const int tok1 = min(bnd.old_valid, tok0 + p.chunk_tokens);
     const int ngroups = (tok1 - tok0) / G;
     const int nres = (chunk == nchunks - 1) ? (bnd.res_valid + kResTile - 1) / kResTile : 0;
-    const int nitems = ngroups + nres;
 
     const int* bt = p.seq.block_tables + (size_t)i * p.seq.bt_stride;
     const int slot = slot_of(p.seq, i);
     const int B = g.b;
-    const int ppg = G / B;
     const size_t page_code_bytes = (size_t)B * (D / 2);
-    const size_t page_vparam_elems = (size_t)B * C::HG;
+    const size_t page_stride = (size_t)g.nkv * page_code_bytes;
+    const uint8_t* kc_head = p.cache.k_code + (size_t)kv * page_code_bytes;
+    const uint8_t* vc_head = p.cache.v_code + (size_t)kv * page_code_bytes;
     const __half* k_res = p.cache.k_scratch + ((size_t)slot * g.nkv + kv) * g.scratch_rows * D;
     const __half* v_res = p.cache.v_scratch + ((size_t)slot * g.nkv + kv) * g.scratch_rows * D;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < nstages; ++s) mbar_init(&full[s], 1);
+        for (int s = 0; s < per_warp * W; ++s) mbar_init(&full[s], kBarArrivals);
         fence_barrier_init();
     }
-    __syncthreads();
 
-    // Issue the copies of item k into its ring slot (whole warp; every lane may issue copies).
-    auto issue = [&](int k) {
-        const int s = k % nstages;
-        unsigned char* st = ring + (size_t)s * C::STAGE;
-        uint64_t* bar = &full[s];
-        fence_proxy_async();
-        if (k < ngroups) {
-            if (lane == 0) mbar_expect_tx(bar, (uint32_t)C::QUANT_BYTES);
-            __syncwarp();
-            const int lp0 = (tok0 + k * G) / B;
-            if (lane < ppg) {
-                const size_t head = (size_t)bt[lp0 + lane] * g.nkv + kv;
-                bulk_g2s(st + C::KC + lane * page_code_bytes, p.cache.k_code + head * page_code_bytes,
-                         (uint32_t)page_code_bytes, bar);
-                bulk_g2s(st + C::VC + lane * page_code_bytes, p.cache.v_code + head * page_code_bytes,
-                         (uint32_t)page_code_bytes, bar);
-                bulk_g2s(st + C::VS + lane * page_vparam_elems * 2, p.cache.v_scale + head * page_vparam_elems,
-                         (uint32_t)(page_vparam_elems * 2), bar);
-                bulk_g2s(st + C::VZ + lane * page_vparam_elems * 2, p.cache.v_zero + head * page_vparam_elems,
-                         (uint32_t)(page_vparam_elems * 2), bar);
-                if (lane == 0) {
-                    bulk_g2s(st + C::KS, p.cache.k_scale + head * D, D * 2, bar);
-                    bulk_g2s(st + C::KZ, p.cache.k_zero + head * D, D * 2, bar);
-                }
-            }
-        } else {
-            const int row0 = (k - ngroups) * kResTile;
-            const int rows = min(kResTile, bnd.res_valid - row0);
-            if (lane == 0) mbar_expect_tx(bar, (uint32_t)(rows * 2 * D * 2));
-            __syncwarp();
-            const int rr = lane & 15;
-            if (rr < rows) {
-                const __half* src = (lane < 16 ? k_res : v_res) + (size_t)(row0 + rr) * D;
-                bulk_g2s(st + (lane < 16 ? 0 : C::RES_V) + rr * C::RES_STRIDE, src, D * 2, bar);
-            }
-        }
-    };
-
-    for (int k = warp; k < nitems && k < nstages; k += kWarps) issue(k);
-
-    // ---- per-lane query fragments -----------------------------------------------------------
-    // Lane (r, t): head r of the group (zero when r >= heads per group), channels [D/4*t, D/4*(t+1)).
+    // ---- query fragments, shared by all warps ------------------------------------------------
+    // Lane (r, t): head r of the group (zero when r >= heads per group), channels [D/4*t, D/4*(t+1)),
+    // as the pairs the nibble masks produce; odd channels carry a 2^-4 factor.
     const bool head_on = r < g.qpk;
     const __half* qrow = p.q + ((size_t)i * g.nh + (size_t)kv * g.qpk + (head_on ? r : 0)) * D;
-    uint32_t qp[4 * C::KW];   // permuted pairs; odd channels carry a 2^-4 factor
-    uint32_t qs[4 * C::KW];   // qp times the key scales of the current group (later: natural pairs)
-    {
+    if (warp == 0) {
         const uint32_t sixteenth = 0x2C002C00u;  // half2(1/16, 1/16)
 #pragma unroll
         for (int j = 0; j < C::KW; ++j) {
             uint4 v = make_uint4(0, 0, 0, 0);
             if (head_on) v = *reinterpret_cast<const uint4*>(qrow + (D / 4) * t + 8 * j);
-            uint32_t o[4];
-            pair_by_four(v, o);
-            qp[4 * j + 0] = o[0];
-            qp[4 * j + 1] = hmul2_u32(o[1], sixteenth);
-            qp[4 * j + 2] = o[2];
-            qp[4 * j + 3] = hmul2_u32(o[3], sixteenth);
+            uint32_t o4[4];
+            pair_by_four(v, o4);
+            qsm[j * 32 + lane] = make_uint4(o4[0], hmul2_u32(o4[1], sixteenth), o4[2], hmul2_u32(o4[3], sixteenth));
         }
     }
+    __syncthreads();
 
+    // ---- staging -------------------------------------------------------------------------------
+    // Every warp owns `per_warp` ring slots and the mbarriers that go with them, fills them itself
+    // and is the only one to wait on them: its items are, in order, the slots of its key groups
+    // (group warp, warp + W, ...) and then its residual tiles (key rows, then value rows). After
+    // draining an item it issues the one `per_warp` items ahead into the slot it just freed.
+    unsigned char* my_ring = ring + (size_t)warp * per_warp * C::SLOT;
+    uint64_t* my_bars = full + warp * per_warp;
+    const int my_groups = ngroups > warp ? (ngroups - warp + W - 1) / W : 0;
+    const int my_quant = my_groups * C::SUBS;
+    const int res_first = ((warp - ngroups) % W + W) % W;   // residual tiles go to the least loaded warps first
+    const int my_res = nres > res_first ? (nres - res_first + W - 1) / W : 0;
+    const int my_items = my_quant + 2 * my_res;
+    const int logb = g.log2b, bmask = B - 1;
+
+    // per-lane constants of the 16-byte parameter copies
+    constexpr int CH = 4 * C::HG;          // chunks per value-parameter array per slot
+    const bool vp_on = lane < 2 * CH;
+    const int vp_c = lane < CH ? lane : lane - CH;
+    const int vp_tok = (vp_c * 8) / C::HG;
+    const __half* vp_base = (lane < CH ? p.cache.v_scale : p.cache.v_zero) + (size_t)kv * B * C::HG;
+    const int vp_dst = (lane < CH ? C::VS : C::VZ) + vp_c * 16;
+    const size_t vp_page_stride = (size_t)g.nkv * B * C::HG;
+    constexpr int CK = D / 8;              // chunks per key-parameter array
+    const bool kp_on = lane < 2 * CK;
+    const int kp_c = lane < CK ? lane : lane - CK;
+    const __half* kp_base = (lane < CK ? p.cache.k_scale : p.cache.k_zero) + (size_t)kv * D + kp_c * 8;
+    const int kp_dst = (lane < CK ? C::KS : C::KZ) + kp_c * 16;
+    const size_t kp_page_stride = (size_t)g.nkv * D;
+    static_assert(2 * CK <= 32 && 2 * CH <= 32, "parameter copies must fit one warp instruction");
+
+    int i_item = 0, i_slot = 0, i_grp = warp, i_sub = 0, i_tile = res_first, i_isv = 0;
+    auto issue_next = [&]() {
+        if (i_item >= my_items) return;
+        unsigned char* st = my_ring + (size_t)i_slot * C::SLOT;
+        uint64_t* bar = my_bars + i_slot;
+        fence_proxy_async();
+        if (i_item < my_quant) {
+            const int tokbase = tok0 + i_grp * G + i_sub * kSub;
+            const int lp = tokbase >> logb;
+            if (lane == 0) {
+                mbar_expect_tx(bar, (uint32_t)C::CODE_BYTES);
+                if (B >= kSub) {
+                    const size_t off = (size_t)bt[lp] * page_stride + (size_t)(tokbase & bmask) * (D / 2);
+                    bulk_g2s(st + C::KC, kc_head + off, kSub * (D / 2), bar);
+                    bulk_g2s(st + C::VC, vc_head + off, kSub * (D / 2), bar);
+                } else {
+                    for (int j = 0; j < (kSub >> logb); ++j) {
+                        const size_t off = (size_t)bt[lp + j] * page_stride;
+                        bulk_g2s(st + C::KC + j * page_code_bytes, kc_head + off, (uint32_t)page_code_bytes, bar);
+                        bulk_g2s(st + C::VC + j * page_code_bytes, vc_head + off, (uint32_t)page_code_bytes, bar);
+                    }
+                }
+            }
+            if (vp_on) {   // value scale / zero of the slot's 32 tokens
+                const int at = tokbase + vp_tok;
+                cp_async16(st + vp_dst, vp_base + (size_t)bt[at >> logb] * vp_page_stride + (size_t)(at & bmask) * C::HG);
+            }
+            if (i_sub == 0 && kp_on)   // key scale / zero of the group, from its first page
+                cp_async16(st + kp_dst, kp_base + (size_t)bt[lp] * kp_page_stride);
+            if (++i_sub == C::SUBS) { i_sub = 0; i_grp += W; }
+        } else {
+            const int row0 = i_tile * kResTile;
+            const int rows = min(kResTile, bnd.res_valid - row0);
+            if (lane == 0) mbar_expect_tx(bar, 0u);
+            const __half* src = (i_isv ? v_res : k_res) + (size_t)row0 * D;
+            constexpr int CPR = D / 8;
+            for (int c = lane; c < rows * CPR; c += 32) {
+                const int rr = c / CPR, cc = c - rr * CPR;
+                cp_async16(st + rr * C::RES_STRIDE + cc * 16, src + (size_t)rr * D + cc * 8);
+            }
+            if (i_isv) { i_isv = 0; i_tile += W; } else i_isv = 1;
+        }
+        cp_async_arrive_noinc(bar);
+        ++i_item;
+        if (++i_slot == per_warp) i_slot = 0;
+    };
+    int c_slot = 0;
+    uint32_t c_phase = 0;
+    auto advance_consumer = [&]() { if (++c_slot == per_warp) { c_slot = 0; c_phase ^= 1u; } };
+
+    for (int s = 0; s < per_warp; ++s) issue_next();
+
+    // ---- per-warp state --------------------------------------------------------------------------
+    uint32_t qs[4 * C::KW];   // query fragment times the key scales of the current group (residual: natural pairs)
     const float scale_log2 = rsqrtf((float)D) * kLog2e;
     const float sc_code = scale_log2 * 16777216.0f;   // undo the 2^-24 of the subnormal codes
+    float bias0 = 0.0f, bias1 = 0.0f;
     float m0 = -1.0e30f, m1 = -1.0e30f, l0 = 0.0f, l1 = 0.0f;
     float zacc[C::HG][2];
 #pragma unroll
@@ -202,11 +251,10 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const DecodePar
     float o[C::NMMA][4];
 #pragma unroll
     for (int m = 0; m < C::NMMA; ++m) o[m][0] = o[m][1] = o[m][2] = o[m][3] = 0.0f;
-    bool true_scale = false;  // accumulators still carry the 2^-24 / 2^-20 code factors
     bool failed = false;
 
     // Online-softmax update shared by both phases: scores s[4] (log2 units) of tokens (rowA: s0,s1;
-    // rowB: s2,s3) for heads (2t, 2t+1) -> probabilities in s[], state rescaled.
+    // rowB: s2,s3) for heads (2t, 2t+1) -> probabilities in s[], state rescaled when needed.
     auto softmax_step = [&](float (&s)[4]) {
         float mx0 = fmaxf(s[0], s[2]), mx1 = fmaxf(s[1], s[3]);
 #pragma unroll
@@ -214,8 +262,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const DecodePar
             mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
             mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
         }
-        const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
-        if (__any_sync(0xffffffffu, n0 > m0 || n1 > m1)) {
+        if (__any_sync(0xffffffffu, mx0 > m0 + kRescaleSlack || mx1 > m1 + kRescaleSlack)) {
+            const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
             const float c0 = fast_exp2(m0 - n0), c1 = fast_exp2(m1 - n1);
             l0 *= c0; l1 *= c1;
 #pragma unroll
@@ -230,41 +278,43 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const DecodePar
         l1 += s[1] + s[3];
     };
 
-    for (int k = warp; k < nitems; k += kWarps) {
-        const int s_idx = k % nstages;
-        unsigned char* st = ring + (size_t)s_idx * C::STAGE;
-        if (!mbar_wait(&full[s_idx], (uint32_t)((k / nstages) & 1))) { failed = true; break; }
+    // ================= key groups of int4 pages =================
+    for (int gi = 0; gi < my_groups && !failed; ++gi) {
+#pragma unroll 1
+        for (int sub = 0; sub < C::SUBS; ++sub) {
+            const unsigned char* st = my_ring + (size_t)c_slot * C::SLOT;
+            if (!mbar_wait(my_bars + c_slot, c_phase)) { failed = true; break; }
 
-        if (k < ngroups) {
-            // ================= one key group of int4 pages =================
-            float bias0, bias1;
-            {
-                float cb[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            if (sub == 0) {
+                float ca[4] = {0.0f, 0.0f, 0.0f, 0.0f}, cb[4] = {0.0f, 0.0f, 0.0f, 0.0f};
                 const uint32_t sixteenth = 0x2C002C00u;
 #pragma unroll
                 for (int j = 0; j < C::KW; ++j) {
+                    const uint4 qv = qsm[j * 32 + lane];
                     const uint4 sv = *reinterpret_cast<const uint4*>(st + C::KS + ((D / 4) * t + 8 * j) * 2);
                     const uint4 zv = *reinterpret_cast<const uint4*>(st + C::KZ + ((D / 4) * t + 8 * j) * 2);
                     uint32_t sp[4], zp[4];
                     pair_by_four(sv, sp);
                     pair_by_four(zv, zp);
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) qs[4 * j + e] = hmul2_u32(qp[4 * j + e], sp[e]);
-                    // zero-point term: rows all equal, even channels scaled 2^-4 to match qp's odd 2^-4
+                    qs[4 * j + 0] = hmul2_u32(qv.x, sp[0]);
+                    qs[4 * j + 1] = hmul2_u32(qv.y, sp[1]);
+                    qs[4 * j + 2] = hmul2_u32(qv.z, sp[2]);
+                    qs[4 * j + 3] = hmul2_u32(qv.w, sp[3]);
+                    // zero-point term: all rows equal; even channels scaled 2^-4 to match the odd 2^-4 of q
                     const uint32_t z0 = hmul2_u32(zp[0], sixteenth), z2 = hmul2_u32(zp[2], sixteenth);
-                    mma16816(cb, z0, z0, zp[1], zp[1], qp[4 * j + 0], qp[4 * j + 1]);
-                    mma16816(cb, z2, z2, zp[3], zp[3], qp[4 * j + 2], qp[4 * j + 3]);
+                    mma16816(ca, z0, z0, zp[1], zp[1], qv.x, qv.y);
+                    mma16816(cb, z2, z2, zp[3], zp[3], qv.z, qv.w);
                 }
-                bias0 = cb[0] * 16.0f * scale_log2;
-                bias1 = cb[1] * 16.0f * scale_log2;
+                bias0 = (ca[0] + cb[0]) * 16.0f * scale_log2;
+                bias1 = (ca[1] + cb[1]) * 16.0f * scale_log2;
             }
 
-#pragma unroll 1
-            for (int tile = 0; tile < C::TILES; ++tile) {
+#pragma unroll
+            for (int tile = 0; tile < kSub / 16; ++tile) {
                 const int tb = tile * 16;
                 const int rowA = tb + row_token(r);
-                // ---- QK^T: S^T[token, head] ----
-                float sc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                // ---- QK^T: S^T[token, head]; two accumulators halve the dependent MMA chain ----
+                float sc[4] = {0.0f, 0.0f, 0.0f, 0.0f}, sd[4] = {0.0f, 0.0f, 0.0f, 0.0f};
                 {
                     uint32_t ka[C::KW], kb[C::KW];
                     const unsigned char* kpa = st + C::KC + rowA * (D / 2) + (D / 8) * t;
@@ -285,12 +335,12 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const DecodePar
                         const uint32_t wa = ka[j], wb = kb[j], wa8 = wa >> 8, wb8 = wb >> 8;
                         mma16816(sc, wa & 0x000f000fu, wb & 0x000f000fu, wa & 0x00f000f0u, wb & 0x00f000f0u,
                                  qs[4 * j + 0], qs[4 * j + 1]);
-                        mma16816(sc, wa8 & 0x000f000fu, wb8 & 0x000f000fu, wa8 & 0x00f000f0u, wb8 & 0x00f000f0u,
+                        mma16816(sd, wa8 & 0x000f000fu, wb8 & 0x000f000fu, wa8 & 0x00f000f0u, wb8 & 0x00f000f0u,
                                  qs[4 * j + 2], qs[4 * j + 3]);
                     }
                 }
-                sc[0] = fmaf(sc[0], sc_code, bias0); sc[1] = fmaf(sc[1], sc_code, bias1);
-                sc[2] = fmaf(sc[2], sc_code, bias0); sc[3] = fmaf(sc[3], sc_code, bias1);
+                sc[0] = fmaf(sc[0] + sd[0], sc_code, bias0); sc[1] = fmaf(sc[1] + sd[1], sc_code, bias1);
+                sc[2] = fmaf(sc[2] + sd[2], sc_code, bias0); sc[3] = fmaf(sc[3] + sd[3], sc_code, bias1);
                 softmax_step(sc);
 
                 // ---- P' = p * value scale (per channel group), token-major -> head-major ----
@@ -314,36 +364,15 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const DecodePar
                     // k-slots (2t, 2t+1, 2t+8, 2t+9) of this lane are tokens tA, tB, tA+8, tB+8.
                     const int tA = tb + 2 * t + (t & 1), tB = tb + 2 * t + ((t & 1) ^ 1);
                     const uint32_t* vw = reinterpret_cast<const uint32_t*>(st + C::VC);
-                    uint32_t wA[C::UNITS], wB[C::UNITS], wA8[C::UNITS], wB8[C::UNITS];
-#pragma unroll
-                    for (int s = 0; s < C::UNITS; ++s) {
-                        // the instruction in slot s fetches unit s ^ swz: lanes that would collide on a
-                        // bank read different words instead
-                        const int u = C::UNITS > 1 ? (s ^ swz) : s;
-                        const int widx = C::HALF ? (4 * u + (r & 3)) : (8 * u + r);
-                        wA[s] = vw[tA * C::WPR + widx];
-                        wB[s] = vw[tB * C::WPR + widx];
-                        wA8[s] = vw[(tA + 8) * C::WPR + widx];
-                        wB8[s] = vw[(tB + 8) * C::WPR + widx];
-                    }
-                    if constexpr (C::UNITS > 1) {
-#pragma unroll
-                        for (int s = 0; s < C::UNITS; s += 2) {
-                            if (swz) {
-                                uint32_t x;
-                                x = wA[s]; wA[s] = wA[s + 1]; wA[s + 1] = x;
-                                x = wB[s]; wB[s] = wB[s + 1]; wB[s + 1] = x;
-                                x = wA8[s]; wA8[s] = wA8[s + 1]; wA8[s + 1] = x;
-                                x = wB8[s]; wB8[s] = wB8[s + 1]; wB8[s + 1] = x;
-                            }
-                        }
-                    }
                     const uint32_t sel_lo = C::HALF ? ((r >> 2) ? 0x7632u : 0x5410u) : 0x5410u;
 #pragma unroll
                     for (int u = 0; u < C::UNITS; ++u) {
+                        const int widx = C::HALF ? (4 * u + (r & 3)) : (8 * u + r);
                         const int cg = C::HALF ? u : (64 * u) / C::VG;
+                        const uint32_t wA = vw[tA * C::WPR + widx], wB = vw[tB * C::WPR + widx];
+                        const uint32_t wA8 = vw[(tA + 8) * C::WPR + widx], wB8 = vw[(tB + 8) * C::WPR + widx];
                         {
-                            const uint32_t xl = __byte_perm(wA[u], wB[u], sel_lo), xh = __byte_perm(wA8[u], wB8[u], sel_lo);
+                            const uint32_t xl = __byte_perm(wA, wB, sel_lo), xh = __byte_perm(wA8, wB8, sel_lo);
                             const uint32_t xl8 = xl >> 8, xh8 = xh >> 8;
                             mma16816(o[u * C::MPU + 0], xl & 0x000f000fu, xl & 0x00f000f0u, xh & 0x000f000fu,
                                      xh & 0x00f000f0u, pb01[cg], pb23[cg]);
@@ -351,7 +380,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const DecodePar
                                      xh8 & 0x00f000f0u, pb01[cg], pb23[cg]);
                         }
                         if constexpr (!C::HALF) {
-                            const uint32_t xl = __byte_perm(wA[u], wB[u], 0x7632), xh = __byte_perm(wA8[u], wB8[u], 0x7632);
+                            const uint32_t xl = __byte_perm(wA, wB, 0x7632), xh = __byte_perm(wA8, wB8, 0x7632);
                             const uint32_t xl8 = xl >> 8, xh8 = xh >> 8;
                             mma16816(o[u * C::MPU + 2], xl & 0x000f000fu, xl & 0x00f000f0u, xh & 0x000f000fu,
                                      xh & 0x00f000f0u, pb01[cg], pb23[cg]);
@@ -361,41 +390,54 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const DecodePar
                     }
                 }
             }
-        } else {
-            // ================= one 16-row tile of the fp16 residual =================
-            if (!true_scale) {
-                true_scale = true;
+            __syncwarp();
+            advance_consumer();
+            issue_next();
+        }
+    }
+
+    // accumulators leave the code scale: channels masked at bits 0-3 carry 2^-24, at bits 4-7 2^-20
 #pragma unroll
-                for (int m = 0; m < C::NMMA; ++m) {
-                    o[m][0] *= 16777216.0f; o[m][1] *= 16777216.0f;
-                    o[m][2] *= 1048576.0f;  o[m][3] *= 1048576.0f;
-                }
-                // natural channel pairs of q for this phase: (16m+2t, +1) and (16m+2t+8, +9)
+    for (int m = 0; m < C::NMMA; ++m) {
+        o[m][0] *= 16777216.0f; o[m][1] *= 16777216.0f;
+        o[m][2] *= 1048576.0f;  o[m][3] *= 1048576.0f;
+    }
+
+    // ================= 16-row tiles of the fp16 residual =================
+    if (my_res > 0 && !failed) {
+        // natural channel pairs of q: (16m+2t, +1) and (16m+2t+8, +9)
 #pragma unroll
-                for (int m = 0; m < C::NMMA; ++m) {
-                    qs[2 * m] = head_on ? *reinterpret_cast<const uint32_t*>(qrow + 16 * m + 2 * t) : 0u;
-                    qs[2 * m + 1] = head_on ? *reinterpret_cast<const uint32_t*>(qrow + 16 * m + 2 * t + 8) : 0u;
-                }
-            }
-            const int row0 = (k - ngroups) * kResTile;
-            const int rows = min(kResTile, bnd.res_valid - row0);
+        for (int m = 0; m < C::NMMA; ++m) {
+            qs[2 * m] = head_on ? *reinterpret_cast<const uint32_t*>(qrow + 16 * m + 2 * t) : 0u;
+            qs[2 * m + 1] = head_on ? *reinterpret_cast<const uint32_t*>(qrow + 16 * m + 2 * t + 8) : 0u;
+        }
+        for (int tile = res_first; tile < nres; tile += W) {
+            const unsigned char* stk = my_ring + (size_t)c_slot * C::SLOT;
+            if (!mbar_wait(my_bars + c_slot, c_phase)) { failed = true; break; }
+            advance_consumer();
+            const unsigned char* stv = my_ring + (size_t)c_slot * C::SLOT;
+            if (!mbar_wait(my_bars + c_slot, c_phase)) { failed = true; break; }
+            advance_consumer();
+            const int rows = min(kResTile, bnd.res_valid - tile * kResTile);
             const int rA = row_token(r);
-            float sc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            float sc[4] = {0.0f, 0.0f, 0.0f, 0.0f}, sd[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             {
                 // ldmatrix: lanes 0-7 / 8-15 / 16-23 / 24-31 give the row addresses of the four
                 // 8x8 blocks (rows 0-7 | 8-15) x (channels +0 | +8).
                 const int lrow = row_token(lane & 7) + 8 * ((lane >> 3) & 1);
-                const unsigned char* base = st + lrow * C::RES_STRIDE + 16 * (lane >> 4);
+                const unsigned char* base = stk + lrow * C::RES_STRIDE + 16 * (lane >> 4);
 #pragma unroll
-                for (int m = 0; m < C::NMMA; ++m) {
-                    uint32_t a[4];
+                for (int m = 0; m < C::NMMA; m += 2) {
+                    uint32_t a[4], b[4];
                     ldmatrix_x4(a, base + 32 * m);
+                    ldmatrix_x4(b, base + 32 * (m + 1));
                     mma16816(sc, a[0], a[1], a[2], a[3], qs[2 * m], qs[2 * m + 1]);
+                    mma16816(sd, b[0], b[1], b[2], b[3], qs[2 * m + 2], qs[2 * m + 3]);
                 }
             }
             const bool onA = rA < rows, onB = rA + 8 < rows;
-            sc[0] = onA ? sc[0] * scale_log2 : -1.0e30f; sc[1] = onA ? sc[1] * scale_log2 : -1.0e30f;
-            sc[2] = onB ? sc[2] * scale_log2 : -1.0e30f; sc[3] = onB ? sc[3] * scale_log2 : -1.0e30f;
+            sc[0] = onA ? (sc[0] + sd[0]) * scale_log2 : -1.0e30f; sc[1] = onA ? (sc[1] + sd[1]) * scale_log2 : -1.0e30f;
+            sc[2] = onB ? (sc[2] + sd[2]) * scale_log2 : -1.0e30f; sc[3] = onB ? (sc[3] + sd[3]) * scale_log2 : -1.0e30f;
             softmax_step(sc);
             if (!onA) { sc[0] = 0.0f; sc[1] = 0.0f; }
             if (!onB) { sc[2] = 0.0f; sc[3] = 0.0f; }
@@ -403,7 +445,6 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const DecodePar
             const uint32_t pb23 = movmatrix_trans(pack_half2(sc[2], sc[3]));
             {
                 const int tA = 2 * t + (t & 1), tB = 2 * t + ((t & 1) ^ 1);
-                const unsigned char* vb = st + C::RES_V;
                 const bool vA = tA < rows, vB = tB < rows, vA8 = tA + 8 < rows, vB8 = tB + 8 < rows;
 #pragma unroll
                 for (int u = 0; u < C::UNITS; ++u) {
@@ -413,10 +454,10 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const DecodePar
                     uint32_t xa[C::MPU], xb[C::MPU], xa8[C::MPU], xb8[C::MPU];
                     auto load = [&](int tok, bool on, uint32_t (&x)[C::MPU]) {
                         if constexpr (C::HALF) {
-                            uint2 v = *reinterpret_cast<const uint2*>(vb + tok * C::RES_STRIDE + c0 * 2);
+                            uint2 v = *reinterpret_cast<const uint2*>(stv + tok * C::RES_STRIDE + c0 * 2);
                             x[0] = on ? v.x : 0u; x[1] = on ? v.y : 0u;
                         } else {
-                            uint4 v = *reinterpret_cast<const uint4*>(vb + tok * C::RES_STRIDE + c0 * 2);
+                            uint4 v = *reinterpret_cast<const uint4*>(stv + tok * C::RES_STRIDE + c0 * 2);
                             x[0] = on ? v.x : 0u; x[1] = on ? v.y : 0u; x[2] = on ? v.z : 0u; x[3] = on ? v.w : 0u;
                         }
                     };
@@ -427,21 +468,15 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const DecodePar
                                  __byte_perm(xa8[q], xb8[q], 0x5410), __byte_perm(xa8[q], xb8[q], 0x7632), pb01, pb23);
                 }
             }
+            __syncwarp();
+            issue_next();
+            issue_next();
         }
-        __syncwarp();
-        if (k + nstages < nitems) issue(k + nstages);
     }
 
     if (failed && p.status && lane == 0) atomicExch(p.status, 1);
 
-    // ---- finish the lane-partial sums and bring the accumulators to true scale ----
-    if (!true_scale) {
-#pragma unroll
-        for (int m = 0; m < C::NMMA; ++m) {
-            o[m][0] *= 16777216.0f; o[m][1] *= 16777216.0f;
-            o[m][2] *= 1048576.0f;  o[m][3] *= 1048576.0f;
-        }
-    }
+    // ---- finish the lane-partial sums ----
 #pragma unroll
     for (int off = 4; off < 32; off <<= 1) {
         l0 += __shfl_xor_sync(0xffffffffu, l0, off);
@@ -453,7 +488,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const DecodePar
         }
     }
 
-    __syncthreads();  // every stage has been consumed: the ring can hold the warp states
+    __syncthreads();  // every slot has been consumed: the ring can hold the warp states
     float* state = reinterpret_cast<float*>(ring) + (size_t)warp * C::STATE_FLOATS;
 #pragma unroll
     for (int u = 0; u < C::UNITS; ++u) {
@@ -475,14 +510,14 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const DecodePar
     __syncthreads();
 
     const float* all = reinterpret_cast<const float*>(ring);
-    for (int idx = threadIdx.x; idx < g.qpk * D; idx += kThreads) {
+    for (int idx = threadIdx.x; idx < g.qpk * D; idx += W * 32) {
         const int hq = idx / D, d = idx - hq * D;
         float mx = -1.0e30f;
 #pragma unroll
-        for (int w = 0; w < kWarps; ++w) mx = fmaxf(mx, all[w * C::STATE_FLOATS + 8 * D + hq]);
+        for (int w = 0; w < W; ++w) mx = fmaxf(mx, all[w * C::STATE_FLOATS + 8 * D + hq]);
         float l = 0.0f, acc = 0.0f;
 #pragma unroll
-        for (int w = 0; w < kWarps; ++w) {
+        for (int w = 0; w < W; ++w) {
             const float* sw = all + w * C::STATE_FLOATS;
             const float wt = fast_exp2(sw[8 * D + hq] - mx);
             l += wt * sw[8 * D + 8 + hq];
@@ -499,20 +534,27 @@ __global__ void __launch_bounds__(kThreads, 1) decode_mma_kernel(const DecodePar
     if (nchunks > 1) merge_when_last(p, i, kv, nchunks);
 }
 
-template <int D, int G>
+template <int D, int G, int W>
 cudaError_t launch(const DecodeParams& p, cudaStream_t stream) {
     using C = Cfg<D, G>;
     constexpr int kBudget = 226 * 1024;   // of the 227 KB a CTA may opt into
-    int nstages = (kBudget - kBarBytes) / C::STAGE;
-    if (nstages > kMaxStages) nstages = kMaxStages;
-    const int state_bytes = kWarps * C::STATE_FLOATS * (int)sizeof(float);
-    while (nstages * C::STAGE < state_bytes) ++nstages;
-    const int smem = kBarBytes + nstages * C::STAGE;
-    cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<D, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    int per_warp = (kBudget - kBarBytes - C::Q_BYTES) / (C::SLOT * W);
+    if (per_warp > kMaxSlotsPerWarp) per_warp = kMaxSlotsPerWarp;
+    if (per_warp * W > 64) per_warp = 64 / W;
+    const int state_bytes = W * C::STATE_FLOATS * (int)sizeof(float);
+    while (per_warp * W * C::SLOT < state_bytes) ++per_warp;
+    if (per_warp < 2) return cudaErrorInvalidConfiguration;
+    const int smem = kBarBytes + C::Q_BYTES + per_warp * W * C::SLOT;
+    cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<D, G, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    decode_mma_kernel<D, G><<<dim3(p.max_chunks, p.geom.nkv, p.n), kThreads, smem, stream>>>(p, nstages);
+    decode_mma_kernel<D, G, W><<<dim3(p.max_chunks, p.geom.nkv, p.n), W * 32, smem, stream>>>(p, per_warp);
     return cudaGetLastError();
 }
+
+#ifndef KIVI_DECODE_WARPS
+#define KIVI_DECODE_WARPS 16
+#endif
+constexpr int kWarps = KIVI_DECODE_WARPS;
 
 }  // namespace
 
@@ -520,8 +562,8 @@ bool decode_mma_supports(const Geom& g, int retained_pages) {
     if (g.d != 64 && g.d != 128) return false;
     if (g.g != 32 && g.g != 64 && g.g != 128) return false;
     if (g.qpk > 8) return false;
-    if (g.pages_per_group > 32) return false;
-    if ((g.b * g.hg * 2) % 16 || (g.b * g.d / 2) % 16) return false;  // bulk copies move 16-byte multiples
+    if (g.log2b < 3) return false;                                     // power-of-two pages of at least 8 tokens
+    if ((g.b * g.hg * 2) % 16 || (g.b * g.d / 2) % 16) return false;   // async copies move 16-byte multiples
     if (retained_pages >= 0 && g.g != g.b) return false;  // a compact table breaks groups that span pages
     return true;
 }
@@ -529,12 +571,12 @@ bool decode_mma_supports(const Geom& g, int retained_pages) {
 cudaError_t launch_decode_mma(const DecodeParams& p, cudaStream_t stream) {
     if (p.n <= 0) return cudaSuccess;
     const int d = p.geom.d, g = p.geom.g;
-    if (d == 128 && g == 128) return launch<128, 128>(p, stream);
-    if (d == 128 && g == 64) return launch<128, 64>(p, stream);
-    if (d == 128 && g == 32) return launch<128, 32>(p, stream);
-    if (d == 64 && g == 128) return launch<64, 128>(p, stream);
-    if (d == 64 && g == 64) return launch<64, 64>(p, stream);
-    if (d == 64 && g == 32) return launch<64, 32>(p, stream);
+    if (d == 128 && g == 128) return launch<128, 128, kWarps>(p, stream);
+    if (d == 128 && g == 64) return launch<128, 64, kWarps>(p, stream);
+    if (d == 128 && g == 32) return launch<128, 32, kWarps>(p, stream);
+    if (d == 64 && g == 128) return launch<64, 128, kWarps>(p, stream);
+    if (d == 64 && g == 64) return launch<64, 64, kWarps>(p, stream);
+    if (d == 64 && g == 32) return launch<64, 32, kWarps>(p, stream);
     return cudaErrorInvalidValue;
 }
 

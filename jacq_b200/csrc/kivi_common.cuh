@@ -18,6 +18,7 @@ struct Geom {
     int vg;            // value channel-group width, min(G, D)
     int scratch_rows;  // R + G
     int pages_per_group;
+    int log2b;         // log2(block) when the block size is a power of two, else -1
 };
 
 inline Geom make_geom(const kivi_geometry& s) {
@@ -29,6 +30,8 @@ inline Geom make_geom(const kivi_geometry& s) {
     g.vg = g.g < g.d ? g.g : g.d;
     g.scratch_rows = g.r + g.g;
     g.pages_per_group = g.g / g.b;
+    g.log2b = -1;
+    for (int sh = 0; sh < 16; ++sh) if ((1 << sh) == g.b) g.log2b = sh;
     return g;
 }
 
@@ -160,6 +163,15 @@ __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, u
     asm volatile(
         "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
         ::"r"(smem_u32(dst_smem)), "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+// 16-byte asynchronous copy global -> shared (per-thread cp.async), and the arrive that lets an
+// mbarrier track every cp.async this thread issued before it (.noinc: the arrival was counted at init).
+__device__ __forceinline__ void cp_async16(void* dst_smem, const void* src_gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src_gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_arrive_noinc(uint64_t* bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
 // D(16x8, f32) += A(16x16, f16, row) * B(16x8, f16, col)

@@ -124,12 +124,12 @@ def _check_cache_shapes(cache: Mapping[str, Any]) -> tuple[int, str]:
     return nkv, _GEOMETRIES[(nkv * 5, nkv)]
 
 
-def _one_device(tensors, what: str) -> torch.device:
+def _one_device(tensors, what: str, require_cuda: bool = True) -> torch.device:
     devices = {t.device for t in tensors}
     if len(devices) != 1:
         raise RuntimeError(f"{what} tensors span devices: {devices}")
     dev = next(iter(devices))
-    if dev.type != "cuda":
+    if require_cuda and dev.type != "cuda":
         raise RuntimeError(f"{what} tensors must be CUDA tensors, got {dev}")
     return dev
 
@@ -170,7 +170,7 @@ class KiviDslLaunchBinding:
         if self.seq_len < 1 or self.seq_len > MAX_SEQ_LEN:
             raise ValueError("SEQ_LEN must be in [1, 4096] for the first KIVI DSL lane")
         tensors = (self.q, self.block_table) + tuple(self.cache[name] for name in _CACHE_TENSORS) + (self.out,)
-        _one_device(tensors, "KIVI jac_launch")
+        _one_device(tensors, "KIVI jac_launch", require_cuda=False)
         return tensors[:-1] + (self.seq_len, self.out)
 
 
@@ -178,7 +178,8 @@ def launch_kivi_dsl_decode(q: torch.Tensor, block_table: torch.Tensor, cache: Ma
                            *, seq_len: int, stream: Any = None) -> None:
     """Decode one query token of one sequence (reference: source_patch.py:294-315 -> C++
     ``kivi_decode_dsl`` :768-869 -> ``jac_launch``)."""
-    KiviDslLaunchBinding(q, block_table, cache, seq_len, out).jac_launch_args()
+    args = KiviDslLaunchBinding(q, block_table, cache, seq_len, out).jac_launch_args()
+    _one_device([a for a in args if isinstance(a, torch.Tensor)], "KIVI jac_launch")
     nkv, suffix = _check_cache_shapes(cache)
     if tuple(q.shape) != (nkv * 5, HD) or tuple(out.shape) != (nkv * 5, HD):
         raise RuntimeError(f"Q and O must be [{nkv * 5}, {HD}] for the KIVI v1 ABI")
@@ -316,7 +317,7 @@ def require_kivi_cache_write_batched(key: torch.Tensor, value: torch.Tensor, slo
 
 
 def _split_old_tokens_batched(seq_len: int, residual: int, block_size: int) -> int:
-    return max(0, seq_len - residual) // block_size * block_size if seq_len >= residual else 0
+    return max(0, seq_len - residual) // block_size * block_size
 
 
 @dataclass(frozen=True)
