@@ -46,6 +46,8 @@ WORKLOADS = {
     # same kernel and geometry as the default, a quarter of the batch: 373 MB of pages, still 3x the L2;
     # sized for `ncu --set full` captures
     "mistral7b_decode_attn_b32_t8192": ("mistral7b", 32, 8192),
+    # enough (sequence, kv head) units that the context is not split: every CTA walks a whole sequence
+    "mistral7b_decode_attn_b48_t8192": ("mistral7b", 48, 8192),
 }
 DEFAULT_WORKLOAD = "mistral7b_decode_attn_b128_t8192"
 METRIC = "KIVI decode-attn achieved HBM GB/s"

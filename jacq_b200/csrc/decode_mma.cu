@@ -53,6 +53,10 @@ constexpr int kSub = 32;                 // tokens per ring slot
 constexpr int kBarBytes = 512;           // room for 64 mbarriers
 constexpr int kMaxSlotsPerWarp = 4;
 constexpr int kBarArrivals = 33;         // lane 0's expect_tx arrive + one cp.async arrive per lane
+#ifndef KIVI_STAGE_BULK
+#define KIVI_STAGE_BULK 0
+#endif
+constexpr bool kStageBulk = KIVI_STAGE_BULK != 0;   // code pages by cp.async.bulk (1) or by 16-byte cp.async (0)
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleSlack = 8.0f;    // log2 units
 
@@ -72,9 +76,14 @@ struct Cfg {
     static constexpr int VC = KC + kSub * D / 2;
     static constexpr int VS = VC + kSub * D / 2;
     static constexpr int VZ = VS + kSub * HG * 2;
-    static constexpr int KS = VZ + kSub * HG * 2;
+    // Key scale/zero of a group are read once, when its first slot is consumed. With one slot per
+    // group they ride in the slot; otherwise they go to a small per-warp area (KP_BUFS buffers,
+    // enough that the copy for a later group never lands before the current one was read).
+    static constexpr int KP_BUFS = SUBS >= 4 ? 1 : (SUBS >= 2 ? 2 : 0);
+    static constexpr int KP_BYTES = 4 * D;             // scale [D] then zero [D], fp16
+    static constexpr int KS = KP_BUFS ? 0 : VZ + kSub * HG * 2;
     static constexpr int KZ = KS + D * 2;
-    static constexpr int QUANT_BYTES = KZ + D * 2;
+    static constexpr int QUANT_BYTES = VZ + kSub * HG * 2 + (KP_BUFS ? 0 : KP_BYTES);
     static constexpr int CODE_BYTES = kSub * D;        // K + V codes of one slot
     static constexpr int RES_STRIDE = 2 * D + 16;      // padded fp16 row: ldmatrix rows hit distinct banks
     static constexpr int RES_BYTES = kResTile * RES_STRIDE;   // 16 key rows OR 16 value rows
@@ -102,13 +111,14 @@ __device__ __forceinline__ void pair_by_four(const uint4& v, uint32_t (&o)[4]) {
     o[3] = __byte_perm(v.y, v.w, 0x7632);
 }
 
-template <int D, int G, int W>
-__global__ void __launch_bounds__(W * 32, 1) decode_mma_kernel(const DecodeParams p, int per_warp) {
+template <int D, int G, int LOGB, int W, int CTAS>
+__global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodeParams p, int per_warp) {
     using C = Cfg<D, G>;
     extern __shared__ __align__(128) unsigned char smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
     uint4* qsm = reinterpret_cast<uint4*>(smem + kBarBytes);
-    unsigned char* ring = smem + kBarBytes + C::Q_BYTES;
+    unsigned char* kparams = smem + kBarBytes + C::Q_BYTES;
+    unsigned char* ring = kparams + W * C::KP_BUFS * C::KP_BYTES;
 
     const Geom& g = p.geom;
     const int i = blockIdx.z, kv = blockIdx.y, chunk = blockIdx.x;
@@ -126,7 +136,8 @@ __global__ void __launch_bounds__(W * 32, 1) decode_mma_kernel(const DecodeParam
 
     const int* bt = p.seq.block_tables + (size_t)i * p.seq.bt_stride;
     const int slot = slot_of(p.seq, i);
-    const int B = g.b;
+    constexpr int B = 1 << LOGB;                       // tokens per page
+    constexpr int PB = B >= kSub ? 1 : kSub / B;       // pages a slot touches
     const size_t page_code_bytes = (size_t)B * (D / 2);
     const size_t page_stride = (size_t)g.nkv * page_code_bytes;
     const uint8_t* kc_head = p.cache.k_code + (size_t)kv * page_code_bytes;
@@ -162,74 +173,107 @@ __global__ void __launch_bounds__(W * 32, 1) decode_mma_kernel(const DecodeParam
     // and is the only one to wait on them: its items are, in order, the slots of its key groups
     // (group warp, warp + W, ...) and then its residual tiles (key rows, then value rows). After
     // draining an item it issues the one `per_warp` items ahead into the slot it just freed.
-    unsigned char* my_ring = ring + (size_t)warp * per_warp * C::SLOT;
-    uint64_t* my_bars = full + warp * per_warp;
+    // All shared-memory traffic below goes through 32-bit shared-window addresses.
+    const uint32_t ring32 = smem_u32(ring) + (uint32_t)(warp * per_warp) * C::SLOT;
+    const uint32_t bars32 = smem_u32(full) + (uint32_t)(warp * per_warp) * 8u;
+    const uint32_t q32 = smem_u32(qsm) + (uint32_t)lane * 16u;
+    const uint32_t kp32 = smem_u32(kparams) + (uint32_t)warp * C::KP_BUFS * C::KP_BYTES;
     const int my_groups = ngroups > warp ? (ngroups - warp + W - 1) / W : 0;
     const int my_quant = my_groups * C::SUBS;
     const int res_first = ((warp - ngroups) % W + W) % W;   // residual tiles go to the least loaded warps first
     const int my_res = nres > res_first ? (nres - res_first + W - 1) / W : 0;
     const int my_items = my_quant + 2 * my_res;
-    const int logb = g.log2b, bmask = B - 1;
+    constexpr int logb = LOGB, bmask = B - 1;
 
-    // per-lane constants of the 16-byte parameter copies
+    // per-lane constants of the 16-byte copies. Page strides fit 32 bits, so page * stride + base
+    // is one wide multiply-add.
+    constexpr uint32_t SLOT_PAGE_BYTES = (B >= kSub ? kSub : B) * (D / 2);   // a page's share of a slot's codes
+    static_assert(kStageBulk || SLOT_PAGE_BYTES % 512 == 0, "cp.async staging moves 512 bytes per warp instruction");
+    const uint32_t page_stride32 = (uint32_t)page_stride;
+    const uint8_t* kc_lane = kc_head + lane * 16;
+    const uint8_t* vc_lane = vc_head + lane * 16;
     constexpr int CH = 4 * C::HG;          // chunks per value-parameter array per slot
     const bool vp_on = lane < 2 * CH;
     const int vp_c = lane < CH ? lane : lane - CH;
-    const int vp_tok = (vp_c * 8) / C::HG;
-    const __half* vp_base = (lane < CH ? p.cache.v_scale : p.cache.v_zero) + (size_t)kv * B * C::HG;
-    const int vp_dst = (lane < CH ? C::VS : C::VZ) + vp_c * 16;
-    const size_t vp_page_stride = (size_t)g.nkv * B * C::HG;
+    const int vp_tok = (vp_c * 8) / C::HG;              // slot-relative token of this lane's chunk
+    const int vp_page = vp_tok >> logb;                  // which of the slot's pages it lies in
+    const __half* vp_lane = (lane < CH ? p.cache.v_scale : p.cache.v_zero) +
+                            ((size_t)kv * B + (vp_tok & bmask)) * C::HG;
+    const uint32_t vp_dst = (lane < CH ? C::VS : C::VZ) + vp_c * 16;
+    const uint32_t vp_stride32 = (uint32_t)(g.nkv * B * C::HG);
     constexpr int CK = D / 8;              // chunks per key-parameter array
     const bool kp_on = lane < 2 * CK;
     const int kp_c = lane < CK ? lane : lane - CK;
-    const __half* kp_base = (lane < CK ? p.cache.k_scale : p.cache.k_zero) + (size_t)kv * D + kp_c * 8;
-    const int kp_dst = (lane < CK ? C::KS : C::KZ) + kp_c * 16;
-    const size_t kp_page_stride = (size_t)g.nkv * D;
+    const __half* kp_lane = (lane < CK ? p.cache.k_scale : p.cache.k_zero) + (size_t)kv * D + kp_c * 8;
+    const uint32_t kp_dst = (lane < CK ? C::KS : C::KZ) + kp_c * 16;
+    const uint32_t kp_stride32 = (uint32_t)(g.nkv * D);
     static_assert(2 * CK <= 32 && 2 * CH <= 32, "parameter copies must fit one warp instruction");
 
-    int i_item = 0, i_slot = 0, i_grp = warp, i_sub = 0, i_tile = res_first, i_isv = 0;
+    int i_item = 0, i_slot = 0, i_grp = warp, i_sub = 0, i_tile = res_first, i_isv = 0, i_kbuf = 0;
     auto issue_next = [&]() {
         if (i_item >= my_items) return;
-        unsigned char* st = my_ring + (size_t)i_slot * C::SLOT;
-        uint64_t* bar = my_bars + i_slot;
+        const uint32_t st = ring32 + (uint32_t)i_slot * C::SLOT;
+        const uint32_t bar = bars32 + (uint32_t)i_slot * 8u;
         fence_proxy_async();
         if (i_item < my_quant) {
             const int tokbase = tok0 + i_grp * G + i_sub * kSub;
             const int lp = tokbase >> logb;
-            if (lane == 0) {
-                mbar_expect_tx(bar, (uint32_t)C::CODE_BYTES);
-                if (B >= kSub) {
-                    const size_t off = (size_t)bt[lp] * page_stride + (size_t)(tokbase & bmask) * (D / 2);
-                    bulk_g2s(st + C::KC, kc_head + off, kSub * (D / 2), bar);
-                    bulk_g2s(st + C::VC, vc_head + off, kSub * (D / 2), bar);
-                } else {
-                    for (int j = 0; j < (kSub >> logb); ++j) {
-                        const size_t off = (size_t)bt[lp + j] * page_stride;
-                        bulk_g2s(st + C::KC + j * page_code_bytes, kc_head + off, (uint32_t)page_code_bytes, bar);
-                        bulk_g2s(st + C::VC + j * page_code_bytes, vc_head + off, (uint32_t)page_code_bytes, bar);
+            // the slot's page ids: lanes 0..PB-1 fetch them, shuffles hand them round
+            const int my_page = lane < PB ? bt[lp + lane] : 0;
+            uint32_t pg[PB];
+#pragma unroll
+            for (int j = 0; j < PB; ++j) pg[j] = (uint32_t)__shfl_sync(0xffffffffu, my_page, j);
+            if (lane == 0) mbar_expect_tx32(bar, kStageBulk ? (uint32_t)C::CODE_BYTES : 0u);
+            if constexpr (kStageBulk) {
+                if (lane == 0) {
+#pragma unroll
+                    for (int j = 0; j < PB; ++j) {
+                        const size_t off = (size_t)pg[j] * page_stride + (B > kSub ? (size_t)(tokbase & bmask) * (D / 2) : 0);
+                        bulk_g2s32(st + C::KC + j * SLOT_PAGE_BYTES, kc_head + off, SLOT_PAGE_BYTES, bar);
+                        bulk_g2s32(st + C::VC + j * SLOT_PAGE_BYTES, vc_head + off, SLOT_PAGE_BYTES, bar);
+                    }
+                }
+            } else {
+                // each page's share of the slot is contiguous in both memories: lane l moves the
+                // 16-byte chunks l, l+32, ... of it, one cp.async warp instruction per 512 bytes
+                const uint32_t dst = st + (uint32_t)lane * 16u;
+#pragma unroll
+                for (int j = 0; j < PB; ++j) {
+                    const uint8_t* ks = kc_lane + (size_t)pg[j] * page_stride32 + (B > kSub ? (size_t)(tokbase & bmask) * (D / 2) : 0);
+                    const uint8_t* vs = vc_lane + (size_t)pg[j] * page_stride32 + (B > kSub ? (size_t)(tokbase & bmask) * (D / 2) : 0);
+#pragma unroll
+                    for (int h = 0; h < (int)SLOT_PAGE_BYTES / 512; ++h) {
+                        cp_async16_32(dst + C::KC + j * SLOT_PAGE_BYTES + h * 512, ks + h * 512);
+                        cp_async16_32(dst + C::VC + j * SLOT_PAGE_BYTES + h * 512, vs + h * 512);
                     }
                 }
             }
             if (vp_on) {   // value scale / zero of the slot's 32 tokens
-                const int at = tokbase + vp_tok;
-                cp_async16(st + vp_dst, vp_base + (size_t)bt[at >> logb] * vp_page_stride + (size_t)(at & bmask) * C::HG);
+                uint32_t pv = pg[0];
+#pragma unroll
+                for (int j = 1; j < PB; ++j) pv = vp_page == j ? pg[j] : pv;
+                cp_async16_32(st + vp_dst, vp_lane + (size_t)pv * vp_stride32 +
+                                               (B > kSub ? (size_t)(tokbase & bmask) * C::HG : 0));
             }
-            if (i_sub == 0 && kp_on)   // key scale / zero of the group, from its first page
-                cp_async16(st + kp_dst, kp_base + (size_t)bt[lp] * kp_page_stride);
+            if (i_sub == 0) {   // key scale / zero of the group, from its first page
+                const uint32_t dst = C::KP_BUFS ? kp32 + (uint32_t)i_kbuf * C::KP_BYTES : st;
+                if (kp_on) cp_async16_32(dst + kp_dst, kp_lane + (size_t)pg[0] * kp_stride32);
+                if (C::KP_BUFS > 1) i_kbuf ^= 1;
+            }
             if (++i_sub == C::SUBS) { i_sub = 0; i_grp += W; }
         } else {
             const int row0 = i_tile * kResTile;
             const int rows = min(kResTile, bnd.res_valid - row0);
-            if (lane == 0) mbar_expect_tx(bar, 0u);
+            if (lane == 0) mbar_expect_tx32(bar, 0u);
             const __half* src = (i_isv ? v_res : k_res) + (size_t)row0 * D;
             constexpr int CPR = D / 8;
             for (int c = lane; c < rows * CPR; c += 32) {
                 const int rr = c / CPR, cc = c - rr * CPR;
-                cp_async16(st + rr * C::RES_STRIDE + cc * 16, src + (size_t)rr * D + cc * 8);
+                cp_async16_32(st + rr * C::RES_STRIDE + cc * 16, src + (size_t)rr * D + cc * 8);
             }
             if (i_isv) { i_isv = 0; i_tile += W; } else i_isv = 1;
         }
-        cp_async_arrive_noinc(bar);
+        cp_async_arrive_noinc32(bar);
         ++i_item;
         if (++i_slot == per_warp) i_slot = 0;
     };
@@ -243,8 +287,9 @@ __global__ void __launch_bounds__(W * 32, 1) decode_mma_kernel(const DecodeParam
     uint32_t qs[4 * C::KW];   // query fragment times the key scales of the current group (residual: natural pairs)
     const float scale_log2 = rsqrtf((float)D) * kLog2e;
     const float sc_code = scale_log2 * 16777216.0f;   // undo the 2^-24 of the subnormal codes
-    float bias0 = 0.0f, bias1 = 0.0f;
+    // Scores are s = raw * mult + add (log2 units); the state keeps m and b = add - m per head.
     float m0 = -1.0e30f, m1 = -1.0e30f, l0 = 0.0f, l1 = 0.0f;
+    float add0 = 0.0f, add1 = 0.0f, b0 = 1.0e30f, b1 = 1.0e30f;
     float zacc[C::HG][2];
 #pragma unroll
     for (int cg = 0; cg < C::HG; ++cg) zacc[cg][0] = zacc[cg][1] = 0.0f;
@@ -253,17 +298,18 @@ __global__ void __launch_bounds__(W * 32, 1) decode_mma_kernel(const DecodeParam
     for (int m = 0; m < C::NMMA; ++m) o[m][0] = o[m][1] = o[m][2] = o[m][3] = 0.0f;
     bool failed = false;
 
-    // Online-softmax update shared by both phases: scores s[4] (log2 units) of tokens (rowA: s0,s1;
-    // rowB: s2,s3) for heads (2t, 2t+1) -> probabilities in s[], state rescaled when needed.
-    auto softmax_step = [&](float (&s)[4]) {
-        float mx0 = fmaxf(s[0], s[2]), mx1 = fmaxf(s[1], s[3]);
+    // Online-softmax update shared by both phases: raw accumulators x[4] of tokens (rowA: x0,x1;
+    // rowB: x2,x3) for heads (2t, 2t+1) -> probabilities in x[]; state rescaled when a score exceeds
+    // the running maximum by more than the slack.
+    auto softmax_step = [&](float (&x)[4], const float mult) {
+        float mx0 = fmaxf(x[0], x[2]), mx1 = fmaxf(x[1], x[3]);
 #pragma unroll
         for (int off = 4; off < 32; off <<= 1) {
             mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
             mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
         }
-        if (__any_sync(0xffffffffu, mx0 > m0 + kRescaleSlack || mx1 > m1 + kRescaleSlack)) {
-            const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+        if (__any_sync(0xffffffffu, fmaf(mx0, mult, b0) > kRescaleSlack || fmaf(mx1, mult, b1) > kRescaleSlack)) {
+            const float n0 = fmaxf(m0, fmaf(mx0, mult, add0)), n1 = fmaxf(m1, fmaf(mx1, mult, add1));
             const float c0 = fast_exp2(m0 - n0), c1 = fast_exp2(m1 - n1);
             l0 *= c0; l1 *= c1;
 #pragma unroll
@@ -271,28 +317,41 @@ __global__ void __launch_bounds__(W * 32, 1) decode_mma_kernel(const DecodeParam
 #pragma unroll
             for (int m = 0; m < C::NMMA; ++m) { o[m][0] *= c0; o[m][1] *= c1; o[m][2] *= c0; o[m][3] *= c1; }
             m0 = n0; m1 = n1;
+            b0 = add0 - m0; b1 = add1 - m1;
         }
-        s[0] = fast_exp2(s[0] - m0); s[1] = fast_exp2(s[1] - m1);
-        s[2] = fast_exp2(s[2] - m0); s[3] = fast_exp2(s[3] - m1);
-        l0 += s[0] + s[2];
-        l1 += s[1] + s[3];
+        x[0] = fast_exp2(fmaf(x[0], mult, b0)); x[1] = fast_exp2(fmaf(x[1], mult, b1));
+        x[2] = fast_exp2(fmaf(x[2], mult, b0)); x[3] = fast_exp2(fmaf(x[3], mult, b1));
+        l0 += x[0] + x[2];
+        l1 += x[1] + x[3];
     };
+
+    // lane-constant byte offsets inside a slot
+    const uint32_t k_off = C::KC + row_token(r) * (D / 2) + (D / 8) * t;
+    const uint32_t v_lane = C::HALF ? 4u * (r & 3) : 4u * r;
+    const uint32_t vA_off = C::VC + (2 * t + (t & 1)) * (D / 2) + v_lane;          // k-slots 2t, 2t+1 of this lane are
+    const uint32_t vB_off = C::VC + (2 * t + ((t & 1) ^ 1)) * (D / 2) + v_lane;    // tokens tA, tB (and +8 for 2t+8, 2t+9)
+    const uint32_t vs_off = C::VS + row_token(r) * C::HG * 2;
+    const uint32_t ks_off = C::KS + (D / 2) * t;
+    const uint32_t sel_lo = C::HALF ? ((r >> 2) ? 0x7632u : 0x5410u) : 0x5410u;
+    constexpr uint32_t UNIT_STEP = C::HALF ? 16u : 32u;      // bytes between the value words of two units
+    constexpr uint32_t TILE_STEP = 16u * (D / 2);            // bytes between 16-token tiles of codes
 
     // ================= key groups of int4 pages =================
     for (int gi = 0; gi < my_groups && !failed; ++gi) {
 #pragma unroll 1
         for (int sub = 0; sub < C::SUBS; ++sub) {
-            const unsigned char* st = my_ring + (size_t)c_slot * C::SLOT;
-            if (!mbar_wait(my_bars + c_slot, c_phase)) { failed = true; break; }
+            const uint32_t st = ring32 + (uint32_t)c_slot * C::SLOT;
+            if (!mbar_wait32(bars32 + (uint32_t)c_slot * 8u, c_phase)) { failed = true; break; }
 
             if (sub == 0) {
                 float ca[4] = {0.0f, 0.0f, 0.0f, 0.0f}, cb[4] = {0.0f, 0.0f, 0.0f, 0.0f};
                 const uint32_t sixteenth = 0x2C002C00u;
+                const uint32_t kbase = C::KP_BUFS ? kp32 + (uint32_t)(C::KP_BUFS > 1 ? (gi & 1) : 0) * C::KP_BYTES : st;
 #pragma unroll
                 for (int j = 0; j < C::KW; ++j) {
-                    const uint4 qv = qsm[j * 32 + lane];
-                    const uint4 sv = *reinterpret_cast<const uint4*>(st + C::KS + ((D / 4) * t + 8 * j) * 2);
-                    const uint4 zv = *reinterpret_cast<const uint4*>(st + C::KZ + ((D / 4) * t + 8 * j) * 2);
+                    const uint4 qv = lds128(q32 + j * 512u);
+                    const uint4 sv = lds128(kbase + ks_off + 16u * j);
+                    const uint4 zv = lds128(kbase + ks_off + (C::KZ - C::KS) + 16u * j);
                     uint32_t sp[4], zp[4];
                     pair_by_four(sv, sp);
                     pair_by_four(zv, zp);
@@ -305,28 +364,25 @@ __global__ void __launch_bounds__(W * 32, 1) decode_mma_kernel(const DecodeParam
                     mma16816(ca, z0, z0, zp[1], zp[1], qv.x, qv.y);
                     mma16816(cb, z2, z2, zp[3], zp[3], qv.z, qv.w);
                 }
-                bias0 = (ca[0] + cb[0]) * 16.0f * scale_log2;
-                bias1 = (ca[1] + cb[1]) * 16.0f * scale_log2;
+                add0 = (ca[0] + cb[0]) * 16.0f * scale_log2;
+                add1 = (ca[1] + cb[1]) * 16.0f * scale_log2;
+                b0 = add0 - m0;
+                b1 = add1 - m1;
             }
 
 #pragma unroll
             for (int tile = 0; tile < kSub / 16; ++tile) {
-                const int tb = tile * 16;
-                const int rowA = tb + row_token(r);
                 // ---- QK^T: S^T[token, head]; two accumulators halve the dependent MMA chain ----
                 float sc[4] = {0.0f, 0.0f, 0.0f, 0.0f}, sd[4] = {0.0f, 0.0f, 0.0f, 0.0f};
                 {
                     uint32_t ka[C::KW], kb[C::KW];
-                    const unsigned char* kpa = st + C::KC + rowA * (D / 2) + (D / 8) * t;
-                    const unsigned char* kpb = kpa + 8 * (D / 2);
+                    const uint32_t kaddr = st + k_off + tile * TILE_STEP;
                     if constexpr (C::KW == 4) {
-                        const uint4 a = *reinterpret_cast<const uint4*>(kpa);
-                        const uint4 b = *reinterpret_cast<const uint4*>(kpb);
+                        const uint4 a = lds128(kaddr), b = lds128(kaddr + 8 * (D / 2));
                         ka[0] = a.x; ka[1] = a.y; ka[2] = a.z; ka[3] = a.w;
                         kb[0] = b.x; kb[1] = b.y; kb[2] = b.z; kb[3] = b.w;
                     } else {
-                        const uint2 a = *reinterpret_cast<const uint2*>(kpa);
-                        const uint2 b = *reinterpret_cast<const uint2*>(kpb);
+                        const uint2 a = lds64(kaddr), b = lds64(kaddr + 8 * (D / 2));
                         ka[0] = a.x; ka[1] = a.y;
                         kb[0] = b.x; kb[1] = b.y;
                     }
@@ -339,19 +395,18 @@ __global__ void __launch_bounds__(W * 32, 1) decode_mma_kernel(const DecodeParam
                                  qs[4 * j + 2], qs[4 * j + 3]);
                     }
                 }
-                sc[0] = fmaf(sc[0] + sd[0], sc_code, bias0); sc[1] = fmaf(sc[1] + sd[1], sc_code, bias1);
-                sc[2] = fmaf(sc[2] + sd[2], sc_code, bias0); sc[3] = fmaf(sc[3] + sd[3], sc_code, bias1);
-                softmax_step(sc);
+                sc[0] += sd[0]; sc[1] += sd[1]; sc[2] += sd[2]; sc[3] += sd[3];
+                softmax_step(sc, sc_code);
 
                 // ---- P' = p * value scale (per channel group), token-major -> head-major ----
                 uint32_t pb01[C::HG], pb23[C::HG];
                 {
-                    const __half* vs = reinterpret_cast<const __half*>(st + C::VS);
-                    const __half* vz = reinterpret_cast<const __half*>(st + C::VZ);
+                    const uint32_t pa = st + vs_off + tile * (16u * C::HG * 2u);
 #pragma unroll
                     for (int cg = 0; cg < C::HG; ++cg) {
-                        const float sa = __half2float(vs[rowA * C::HG + cg]), sb = __half2float(vs[(rowA + 8) * C::HG + cg]);
-                        const float za = __half2float(vz[rowA * C::HG + cg]), zb = __half2float(vz[(rowA + 8) * C::HG + cg]);
+                        const float sa = lds_half(pa + 2u * cg), sb = lds_half(pa + 8u * C::HG * 2u + 2u * cg);
+                        const float za = lds_half(pa + (C::VZ - C::VS) + 2u * cg);
+                        const float zb = lds_half(pa + (C::VZ - C::VS) + 8u * C::HG * 2u + 2u * cg);
                         pb01[cg] = movmatrix_trans(pack_half2(sc[0] * sa, sc[1] * sa));
                         pb23[cg] = movmatrix_trans(pack_half2(sc[2] * sb, sc[3] * sb));
                         zacc[cg][0] = fmaf(sc[0], za, fmaf(sc[2], zb, zacc[cg][0]));
@@ -360,33 +415,28 @@ __global__ void __launch_bounds__(W * 32, 1) decode_mma_kernel(const DecodeParam
                 }
 
                 // ---- PV: O^T[channel, head] += V^T[channel, token] P'[token, head] ----
-                {
-                    // k-slots (2t, 2t+1, 2t+8, 2t+9) of this lane are tokens tA, tB, tA+8, tB+8.
-                    const int tA = tb + 2 * t + (t & 1), tB = tb + 2 * t + ((t & 1) ^ 1);
-                    const uint32_t* vw = reinterpret_cast<const uint32_t*>(st + C::VC);
-                    const uint32_t sel_lo = C::HALF ? ((r >> 2) ? 0x7632u : 0x5410u) : 0x5410u;
 #pragma unroll
-                    for (int u = 0; u < C::UNITS; ++u) {
-                        const int widx = C::HALF ? (4 * u + (r & 3)) : (8 * u + r);
-                        const int cg = C::HALF ? u : (64 * u) / C::VG;
-                        const uint32_t wA = vw[tA * C::WPR + widx], wB = vw[tB * C::WPR + widx];
-                        const uint32_t wA8 = vw[(tA + 8) * C::WPR + widx], wB8 = vw[(tB + 8) * C::WPR + widx];
-                        {
-                            const uint32_t xl = __byte_perm(wA, wB, sel_lo), xh = __byte_perm(wA8, wB8, sel_lo);
-                            const uint32_t xl8 = xl >> 8, xh8 = xh >> 8;
-                            mma16816(o[u * C::MPU + 0], xl & 0x000f000fu, xl & 0x00f000f0u, xh & 0x000f000fu,
-                                     xh & 0x00f000f0u, pb01[cg], pb23[cg]);
-                            mma16816(o[u * C::MPU + 1], xl8 & 0x000f000fu, xl8 & 0x00f000f0u, xh8 & 0x000f000fu,
-                                     xh8 & 0x00f000f0u, pb01[cg], pb23[cg]);
-                        }
-                        if constexpr (!C::HALF) {
-                            const uint32_t xl = __byte_perm(wA, wB, 0x7632), xh = __byte_perm(wA8, wB8, 0x7632);
-                            const uint32_t xl8 = xl >> 8, xh8 = xh >> 8;
-                            mma16816(o[u * C::MPU + 2], xl & 0x000f000fu, xl & 0x00f000f0u, xh & 0x000f000fu,
-                                     xh & 0x00f000f0u, pb01[cg], pb23[cg]);
-                            mma16816(o[u * C::MPU + 3], xl8 & 0x000f000fu, xl8 & 0x00f000f0u, xh8 & 0x000f000fu,
-                                     xh8 & 0x00f000f0u, pb01[cg], pb23[cg]);
-                        }
+                for (int u = 0; u < C::UNITS; ++u) {
+                    const int cg = C::HALF ? u : (64 * u) / C::VG;
+                    const uint32_t va = st + vA_off + tile * TILE_STEP + u * UNIT_STEP;
+                    const uint32_t vb = st + vB_off + tile * TILE_STEP + u * UNIT_STEP;
+                    const uint32_t wA = lds32(va), wB = lds32(vb);
+                    const uint32_t wA8 = lds32(va + 8 * (D / 2)), wB8 = lds32(vb + 8 * (D / 2));
+                    {
+                        const uint32_t xl = __byte_perm(wA, wB, sel_lo), xh = __byte_perm(wA8, wB8, sel_lo);
+                        const uint32_t xl8 = xl >> 8, xh8 = xh >> 8;
+                        mma16816(o[u * C::MPU + 0], xl & 0x000f000fu, xl & 0x00f000f0u, xh & 0x000f000fu,
+                                 xh & 0x00f000f0u, pb01[cg], pb23[cg]);
+                        mma16816(o[u * C::MPU + 1], xl8 & 0x000f000fu, xl8 & 0x00f000f0u, xh8 & 0x000f000fu,
+                                 xh8 & 0x00f000f0u, pb01[cg], pb23[cg]);
+                    }
+                    if constexpr (!C::HALF) {
+                        const uint32_t xl = __byte_perm(wA, wB, 0x7632), xh = __byte_perm(wA8, wB8, 0x7632);
+                        const uint32_t xl8 = xl >> 8, xh8 = xh >> 8;
+                        mma16816(o[u * C::MPU + 2], xl & 0x000f000fu, xl & 0x00f000f0u, xh & 0x000f000fu,
+                                 xh & 0x00f000f0u, pb01[cg], pb23[cg]);
+                        mma16816(o[u * C::MPU + 3], xl8 & 0x000f000fu, xl8 & 0x00f000f0u, xh8 & 0x000f000fu,
+                                 xh8 & 0x00f000f0u, pb01[cg], pb23[cg]);
                     }
                 }
             }
@@ -411,62 +461,60 @@ __global__ void __launch_bounds__(W * 32, 1) decode_mma_kernel(const DecodeParam
             qs[2 * m] = head_on ? *reinterpret_cast<const uint32_t*>(qrow + 16 * m + 2 * t) : 0u;
             qs[2 * m + 1] = head_on ? *reinterpret_cast<const uint32_t*>(qrow + 16 * m + 2 * t + 8) : 0u;
         }
+        add0 = add1 = 0.0f;
+        b0 = -m0; b1 = -m1;
+        // ldmatrix: lanes 0-7 / 8-15 / 16-23 / 24-31 give the row addresses of the four
+        // 8x8 blocks (rows 0-7 | 8-15) x (channels +0 | +8).
+        const uint32_t ldm_off = (row_token(lane & 7) + 8 * ((lane >> 3) & 1)) * C::RES_STRIDE + 16 * (lane >> 4);
+        const int rA = row_token(r);
+        const int tA = 2 * t + (t & 1), tB = 2 * t + ((t & 1) ^ 1);
         for (int tile = res_first; tile < nres; tile += W) {
-            const unsigned char* stk = my_ring + (size_t)c_slot * C::SLOT;
-            if (!mbar_wait(my_bars + c_slot, c_phase)) { failed = true; break; }
+            const uint32_t stk = ring32 + (uint32_t)c_slot * C::SLOT;
+            if (!mbar_wait32(bars32 + (uint32_t)c_slot * 8u, c_phase)) { failed = true; break; }
             advance_consumer();
-            const unsigned char* stv = my_ring + (size_t)c_slot * C::SLOT;
-            if (!mbar_wait(my_bars + c_slot, c_phase)) { failed = true; break; }
+            const uint32_t stv = ring32 + (uint32_t)c_slot * C::SLOT;
+            if (!mbar_wait32(bars32 + (uint32_t)c_slot * 8u, c_phase)) { failed = true; break; }
             advance_consumer();
             const int rows = min(kResTile, bnd.res_valid - tile * kResTile);
-            const int rA = row_token(r);
             float sc[4] = {0.0f, 0.0f, 0.0f, 0.0f}, sd[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            {
-                // ldmatrix: lanes 0-7 / 8-15 / 16-23 / 24-31 give the row addresses of the four
-                // 8x8 blocks (rows 0-7 | 8-15) x (channels +0 | +8).
-                const int lrow = row_token(lane & 7) + 8 * ((lane >> 3) & 1);
-                const unsigned char* base = stk + lrow * C::RES_STRIDE + 16 * (lane >> 4);
 #pragma unroll
-                for (int m = 0; m < C::NMMA; m += 2) {
-                    uint32_t a[4], b[4];
-                    ldmatrix_x4(a, base + 32 * m);
-                    ldmatrix_x4(b, base + 32 * (m + 1));
-                    mma16816(sc, a[0], a[1], a[2], a[3], qs[2 * m], qs[2 * m + 1]);
-                    mma16816(sd, b[0], b[1], b[2], b[3], qs[2 * m + 2], qs[2 * m + 3]);
-                }
+            for (int m = 0; m < C::NMMA; m += 2) {
+                uint32_t a[4], b[4];
+                ldmatrix_x4_32(a, stk + ldm_off + 32 * m);
+                ldmatrix_x4_32(b, stk + ldm_off + 32 * (m + 1));
+                mma16816(sc, a[0], a[1], a[2], a[3], qs[2 * m], qs[2 * m + 1]);
+                mma16816(sd, b[0], b[1], b[2], b[3], qs[2 * m + 2], qs[2 * m + 3]);
             }
+            // rows past the end of the residual hold stale bytes: give them a score no maximum will see
             const bool onA = rA < rows, onB = rA + 8 < rows;
-            sc[0] = onA ? (sc[0] + sd[0]) * scale_log2 : -1.0e30f; sc[1] = onA ? (sc[1] + sd[1]) * scale_log2 : -1.0e30f;
-            sc[2] = onB ? (sc[2] + sd[2]) * scale_log2 : -1.0e30f; sc[3] = onB ? (sc[3] + sd[3]) * scale_log2 : -1.0e30f;
-            softmax_step(sc);
+            sc[0] = onA ? sc[0] + sd[0] : -1.0e30f; sc[1] = onA ? sc[1] + sd[1] : -1.0e30f;
+            sc[2] = onB ? sc[2] + sd[2] : -1.0e30f; sc[3] = onB ? sc[3] + sd[3] : -1.0e30f;
+            softmax_step(sc, scale_log2);
             if (!onA) { sc[0] = 0.0f; sc[1] = 0.0f; }
             if (!onB) { sc[2] = 0.0f; sc[3] = 0.0f; }
             const uint32_t pb01 = movmatrix_trans(pack_half2(sc[0], sc[1]));
             const uint32_t pb23 = movmatrix_trans(pack_half2(sc[2], sc[3]));
-            {
-                const int tA = 2 * t + (t & 1), tB = 2 * t + ((t & 1) ^ 1);
-                const bool vA = tA < rows, vB = tB < rows, vA8 = tA + 8 < rows, vB8 = tB + 8 < rows;
+            const bool vA = tA < rows, vB = tB < rows, vA8 = tA + 8 < rows, vB8 = tB + 8 < rows;
 #pragma unroll
-                for (int u = 0; u < C::UNITS; ++u) {
-                    // same channel-to-row assignment as the int4 path: rows (r, r+8) of MMA q are
-                    // channels (c0 + 2q, c0 + 2q + 1)
-                    const int c0 = C::HALF ? (C::VG * u + 8 * (r & 3) + 4 * (r >> 2)) : (64 * u + 8 * r);
-                    uint32_t xa[C::MPU], xb[C::MPU], xa8[C::MPU], xb8[C::MPU];
-                    auto load = [&](int tok, bool on, uint32_t (&x)[C::MPU]) {
-                        if constexpr (C::HALF) {
-                            uint2 v = *reinterpret_cast<const uint2*>(stv + tok * C::RES_STRIDE + c0 * 2);
-                            x[0] = on ? v.x : 0u; x[1] = on ? v.y : 0u;
-                        } else {
-                            uint4 v = *reinterpret_cast<const uint4*>(stv + tok * C::RES_STRIDE + c0 * 2);
-                            x[0] = on ? v.x : 0u; x[1] = on ? v.y : 0u; x[2] = on ? v.z : 0u; x[3] = on ? v.w : 0u;
-                        }
-                    };
-                    load(tA, vA, xa); load(tB, vB, xb); load(tA + 8, vA8, xa8); load(tB + 8, vB8, xb8);
+            for (int u = 0; u < C::UNITS; ++u) {
+                // same channel-to-row assignment as the int4 path: rows (r, r+8) of MMA q are
+                // channels (c0 + 2q, c0 + 2q + 1)
+                const int c0 = C::HALF ? (C::VG * u + 8 * (r & 3) + 4 * (r >> 2)) : (64 * u + 8 * r);
+                uint32_t xa[C::MPU], xb[C::MPU], xa8[C::MPU], xb8[C::MPU];
+                auto load = [&](int tok, bool on, uint32_t (&x)[C::MPU]) {
+                    if constexpr (C::HALF) {
+                        const uint2 v = lds64(stv + tok * C::RES_STRIDE + c0 * 2);
+                        x[0] = on ? v.x : 0u; x[1] = on ? v.y : 0u;
+                    } else {
+                        const uint4 v = lds128(stv + tok * C::RES_STRIDE + c0 * 2);
+                        x[0] = on ? v.x : 0u; x[1] = on ? v.y : 0u; x[2] = on ? v.z : 0u; x[3] = on ? v.w : 0u;
+                    }
+                };
+                load(tA, vA, xa); load(tB, vB, xb); load(tA + 8, vA8, xa8); load(tB + 8, vB8, xb8);
 #pragma unroll
-                    for (int q = 0; q < C::MPU; ++q)
-                        mma16816(o[u * C::MPU + q], __byte_perm(xa[q], xb[q], 0x5410), __byte_perm(xa[q], xb[q], 0x7632),
-                                 __byte_perm(xa8[q], xb8[q], 0x5410), __byte_perm(xa8[q], xb8[q], 0x7632), pb01, pb23);
-                }
+                for (int q = 0; q < C::MPU; ++q)
+                    mma16816(o[u * C::MPU + q], __byte_perm(xa[q], xb[q], 0x5410), __byte_perm(xa[q], xb[q], 0x7632),
+                             __byte_perm(xa8[q], xb8[q], 0x5410), __byte_perm(xa8[q], xb8[q], 0x7632), pb01, pb23);
             }
             __syncwarp();
             issue_next();
@@ -534,27 +582,35 @@ __global__ void __launch_bounds__(W * 32, 1) decode_mma_kernel(const DecodeParam
     if (nchunks > 1) merge_when_last(p, i, kv, nchunks);
 }
 
-template <int D, int G, int W>
+template <int D, int G, int LOGB, int W, int CTAS>
 cudaError_t launch(const DecodeParams& p, cudaStream_t stream) {
     using C = Cfg<D, G>;
-    constexpr int kBudget = 226 * 1024;   // of the 227 KB a CTA may opt into
-    int per_warp = (kBudget - kBarBytes - C::Q_BYTES) / (C::SLOT * W);
+    // 227 KB of shared memory per SM may be opted into; every resident CTA also costs 1 KB.
+    constexpr int kBudget = 227 * 1024 / CTAS - 1024 - 256;
+    constexpr int kFixed = kBarBytes + C::Q_BYTES + W * C::KP_BUFS * C::KP_BYTES;
+    int per_warp = (kBudget - kFixed) / (C::SLOT * W);
     if (per_warp > kMaxSlotsPerWarp) per_warp = kMaxSlotsPerWarp;
     if (per_warp * W > 64) per_warp = 64 / W;
     const int state_bytes = W * C::STATE_FLOATS * (int)sizeof(float);
     while (per_warp * W * C::SLOT < state_bytes) ++per_warp;
     if (per_warp < 2) return cudaErrorInvalidConfiguration;
-    const int smem = kBarBytes + C::Q_BYTES + per_warp * W * C::SLOT;
-    cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<D, G, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    const int smem = kFixed + per_warp * W * C::SLOT;
+    cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<D, G, LOGB, W, CTAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    decode_mma_kernel<D, G, W><<<dim3(p.max_chunks, p.geom.nkv, p.n), W * 32, smem, stream>>>(p, per_warp);
+    decode_mma_kernel<D, G, LOGB, W, CTAS><<<dim3(p.max_chunks, p.geom.nkv, p.n), W * 32, smem, stream>>>(p, per_warp);
     return cudaGetLastError();
 }
 
+// Warps per CTA and CTAs per SM: two CTAs of eight warps overlap one CTA's ramp-up and final merge
+// with the other's steady state, and halve the per-warp fixed cost against one CTA of sixteen.
 #ifndef KIVI_DECODE_WARPS
-#define KIVI_DECODE_WARPS 16
+#define KIVI_DECODE_WARPS 8
+#endif
+#ifndef KIVI_DECODE_CTAS
+#define KIVI_DECODE_CTAS 2
 #endif
 constexpr int kWarps = KIVI_DECODE_WARPS;
+constexpr int kCtas = KIVI_DECODE_CTAS;
 
 }  // namespace
 
@@ -562,21 +618,28 @@ bool decode_mma_supports(const Geom& g, int retained_pages) {
     if (g.d != 64 && g.d != 128) return false;
     if (g.g != 32 && g.g != 64 && g.g != 128) return false;
     if (g.qpk > 8) return false;
-    if (g.log2b < 3) return false;                                     // power-of-two pages of at least 8 tokens
+    if (g.log2b != 4 && g.log2b != 5) return false;                    // pages of 16 or 32 tokens
     if ((g.b * g.hg * 2) % 16 || (g.b * g.d / 2) % 16) return false;   // async copies move 16-byte multiples
     if (retained_pages >= 0 && g.g != g.b) return false;  // a compact table breaks groups that span pages
     return true;
 }
 
+template <int D, int G>
+cudaError_t launch_for_block(const DecodeParams& p, cudaStream_t stream) {
+    if (p.geom.log2b == 4) return launch<D, G, 4, kWarps, kCtas>(p, stream);
+    if (p.geom.log2b == 5) return launch<D, G, 5, kWarps, kCtas>(p, stream);
+    return cudaErrorInvalidValue;
+}
+
 cudaError_t launch_decode_mma(const DecodeParams& p, cudaStream_t stream) {
     if (p.n <= 0) return cudaSuccess;
     const int d = p.geom.d, g = p.geom.g;
-    if (d == 128 && g == 128) return launch<128, 128, kWarps>(p, stream);
-    if (d == 128 && g == 64) return launch<128, 64, kWarps>(p, stream);
-    if (d == 128 && g == 32) return launch<128, 32, kWarps>(p, stream);
-    if (d == 64 && g == 128) return launch<64, 128, kWarps>(p, stream);
-    if (d == 64 && g == 64) return launch<64, 64, kWarps>(p, stream);
-    if (d == 64 && g == 32) return launch<64, 32, kWarps>(p, stream);
+    if (d == 128 && g == 128) return launch_for_block<128, 128>(p, stream);
+    if (d == 128 && g == 64) return launch_for_block<128, 64>(p, stream);
+    if (d == 128 && g == 32) return launch_for_block<128, 32>(p, stream);
+    if (d == 64 && g == 128) return launch_for_block<64, 128>(p, stream);
+    if (d == 64 && g == 64) return launch_for_block<64, 64>(p, stream);
+    if (d == 64 && g == 32) return launch_for_block<64, 32>(p, stream);
     return cudaErrorInvalidValue;
 }
 
