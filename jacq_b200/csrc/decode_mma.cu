@@ -103,6 +103,8 @@ __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
     __half2 r = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
     return *reinterpret_cast<uint32_t*>(&r);
 }
+// w >> 8 (a multiply-high by 2^24 on the FMA pipe was measured slower than the ALU shift).
+__device__ __forceinline__ uint32_t shr8(uint32_t w) { return w >> 8; }
 // (x0,x1),(x2,x3),(x4,x5),(x6,x7) -> (x0,x4),(x1,x5),(x2,x6),(x3,x7): the pairing the nibble masks give.
 __device__ __forceinline__ void pair_by_four(const uint4& v, uint32_t (&o)[4]) {
     o[0] = __byte_perm(v.x, v.z, 0x5410);
@@ -122,7 +124,8 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
 
     const Geom& g = p.geom;
     const int i = blockIdx.z, kv = blockIdx.y, chunk = blockIdx.x;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // the warp index through a broadcast, so that everything derived from it is known to be warp-uniform
+    const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
     const int r = lane >> 2, t = lane & 3;
 
     const int seq_len = seq_len_of(p.seq, i);
@@ -302,13 +305,18 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
     // rowB: x2,x3) for heads (2t, 2t+1) -> probabilities in x[]; state rescaled when a score exceeds
     // the running maximum by more than the slack.
     auto softmax_step = [&](float (&x)[4], const float mult) {
-        float mx0 = fmaxf(x[0], x[2]), mx1 = fmaxf(x[1], x[3]);
+        // exponents relative to the running maximum; the common case needs no reduction at all:
+        // only when some score tops the maximum by more than the slack is the tile maximum formed
+        // (three shuffle rounds) and the state rescaled.
+        float e0 = fmaf(x[0], mult, b0), e1 = fmaf(x[1], mult, b1);
+        float e2 = fmaf(x[2], mult, b0), e3 = fmaf(x[3], mult, b1);
+        if (__any_sync(0xffffffffu, fmaxf(fmaxf(e0, e1), fmaxf(e2, e3)) > kRescaleSlack)) {
+            float mx0 = fmaxf(x[0], x[2]), mx1 = fmaxf(x[1], x[3]);
 #pragma unroll
-        for (int off = 4; off < 32; off <<= 1) {
-            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
-            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
-        }
-        if (__any_sync(0xffffffffu, fmaf(mx0, mult, b0) > kRescaleSlack || fmaf(mx1, mult, b1) > kRescaleSlack)) {
+            for (int off = 4; off < 32; off <<= 1) {
+                mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+                mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+            }
             const float n0 = fmaxf(m0, fmaf(mx0, mult, add0)), n1 = fmaxf(m1, fmaf(mx1, mult, add1));
             const float c0 = fast_exp2(m0 - n0), c1 = fast_exp2(m1 - n1);
             l0 *= c0; l1 *= c1;
@@ -318,9 +326,11 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
             for (int m = 0; m < C::NMMA; ++m) { o[m][0] *= c0; o[m][1] *= c1; o[m][2] *= c0; o[m][3] *= c1; }
             m0 = n0; m1 = n1;
             b0 = add0 - m0; b1 = add1 - m1;
+            e0 = fmaf(x[0], mult, b0); e1 = fmaf(x[1], mult, b1);
+            e2 = fmaf(x[2], mult, b0); e3 = fmaf(x[3], mult, b1);
         }
-        x[0] = fast_exp2(fmaf(x[0], mult, b0)); x[1] = fast_exp2(fmaf(x[1], mult, b1));
-        x[2] = fast_exp2(fmaf(x[2], mult, b0)); x[3] = fast_exp2(fmaf(x[3], mult, b1));
+        x[0] = fast_exp2(e0); x[1] = fast_exp2(e1);
+        x[2] = fast_exp2(e2); x[3] = fast_exp2(e3);
         l0 += x[0] + x[2];
         l1 += x[1] + x[3];
     };
@@ -388,7 +398,7 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
                     }
 #pragma unroll
                     for (int j = 0; j < C::KW; ++j) {
-                        const uint32_t wa = ka[j], wb = kb[j], wa8 = wa >> 8, wb8 = wb >> 8;
+                        const uint32_t wa = ka[j], wb = kb[j], wa8 = shr8(wa), wb8 = shr8(wb);
                         mma16816(sc, wa & 0x000f000fu, wb & 0x000f000fu, wa & 0x00f000f0u, wb & 0x00f000f0u,
                                  qs[4 * j + 0], qs[4 * j + 1]);
                         mma16816(sd, wa8 & 0x000f000fu, wb8 & 0x000f000fu, wa8 & 0x00f000f0u, wb8 & 0x00f000f0u,
@@ -424,7 +434,7 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
                     const uint32_t wA8 = lds32(va + 8 * (D / 2)), wB8 = lds32(vb + 8 * (D / 2));
                     {
                         const uint32_t xl = __byte_perm(wA, wB, sel_lo), xh = __byte_perm(wA8, wB8, sel_lo);
-                        const uint32_t xl8 = xl >> 8, xh8 = xh >> 8;
+                        const uint32_t xl8 = shr8(xl), xh8 = shr8(xh);
                         mma16816(o[u * C::MPU + 0], xl & 0x000f000fu, xl & 0x00f000f0u, xh & 0x000f000fu,
                                  xh & 0x00f000f0u, pb01[cg], pb23[cg]);
                         mma16816(o[u * C::MPU + 1], xl8 & 0x000f000fu, xl8 & 0x00f000f0u, xh8 & 0x000f000fu,
@@ -432,7 +442,7 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
                     }
                     if constexpr (!C::HALF) {
                         const uint32_t xl = __byte_perm(wA, wB, 0x7632), xh = __byte_perm(wA8, wB8, 0x7632);
-                        const uint32_t xl8 = xl >> 8, xh8 = xh >> 8;
+                        const uint32_t xl8 = shr8(xl), xh8 = shr8(xh);
                         mma16816(o[u * C::MPU + 2], xl & 0x000f000fu, xl & 0x00f000f0u, xh & 0x000f000fu,
                                  xh & 0x00f000f0u, pb01[cg], pb23[cg]);
                         mma16816(o[u * C::MPU + 3], xl8 & 0x000f000fu, xl8 & 0x00f000f0u, xh8 & 0x000f000fu,
@@ -601,13 +611,16 @@ cudaError_t launch(const DecodeParams& p, cudaStream_t stream) {
     return cudaGetLastError();
 }
 
-// Warps per CTA and CTAs per SM: two CTAs of eight warps overlap one CTA's ramp-up and final merge
-// with the other's steady state, and halve the per-warp fixed cost against one CTA of sixteen.
+// Warps per CTA and CTAs per SM. Twelve warps per SM leave each thread about 170 registers, which
+// the unrolled two-tile body needs (at 128 it spills and throttles); several small CTAs instead of
+// one large one overlap a CTA's ramp-up and final merge with the steady state of the others and
+// give every warp a long run of groups to amortise its fixed costs. Measured on the Mistral-7B
+// shape (GB/s): 4x3 5043, 6x2 5008, 5x3 4768, 3x4 4691, 8x2 4628, 12x1 4537, 16x1 4113.
 #ifndef KIVI_DECODE_WARPS
-#define KIVI_DECODE_WARPS 8
+#define KIVI_DECODE_WARPS 4
 #endif
 #ifndef KIVI_DECODE_CTAS
-#define KIVI_DECODE_CTAS 2
+#define KIVI_DECODE_CTAS 3
 #endif
 constexpr int kWarps = KIVI_DECODE_WARPS;
 constexpr int kCtas = KIVI_DECODE_CTAS;
