@@ -135,6 +135,28 @@ int kivi_b200_decode(const kivi_geometry* geom, const kivi_cache* cache, const k
                      const int32_t* slot_ids, int batch, int max_seq_len, float* out,
                      void* workspace, size_t workspace_bytes, cudaStream_t stream);
 
+/* Decode for callers that cannot allocate device memory. Some hosts of this library hand it
+ * buffers but have no allocator of their own to ask for a workspace: a serving runtime whose memory
+ * pool was sized and frozen at start-up, a plugin running inside someone else's captured step, a
+ * C caller with no CUDA allocation rights in its sandbox. This entry point (no counterpart in the
+ * reference, which never splits the context and so needs no scratch) is kivi_b200_decode with the
+ * split-context scratch taken from a fixed array inside the library instead of from the caller:
+ *   - it calls no cudaMalloc / cudaFree and no allocating library routine;
+ *   - the array is KIVI_B200_NOALLOC_SCRATCH_BYTES long and every GPU that loads the library holds
+ *     it until the process exits; a (batch, max_seq_len) whose launch plan needs more is refused
+ *     with KIVI_ERR_WORKSPACE and nothing is launched (kivi_b200_decode_workspace_bytes tells the
+ *     need in advance);
+ *   - the first call on each device, made with that device current, looks the array's device
+ *     address up; make that first call before any stream capture begins;
+ *   - every call uses the same array: two calls whose kernels can overlap on the GPU (different
+ *     streams, different host threads) race on it. Calls on one stream are safe back to back.
+ * Arguments and results are those of kivi_b200_decode. */
+#define KIVI_B200_NOALLOC_SCRATCH_BYTES (1u << 20)
+int kivi_b200_decode_noalloc(const kivi_geometry* geom, const kivi_cache* cache, const kivi_f16* q,
+                             const int32_t* block_tables, int max_blocks_per_seq, const int32_t* seq_lens,
+                             const int32_t* slot_ids, int batch, int max_seq_len, float* out,
+                             cudaStream_t stream);
+
 /* fp16 GEMV / skinny GEMM of the generated decode runtime: y[b, o] = sum_i W[o, i] * x[b, i],
  * W row-major [out_dim, in_dim], fp32 accumulation (reference: gemv(),
  * crates/jac-codegen-cuda/src/templates/runtime.cu:15-26, a cublasGemmEx call). 1 <= batch <= 64.

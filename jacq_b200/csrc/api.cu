@@ -299,6 +299,60 @@ extern "C" int kivi_b200_decode(const kivi_geometry* geom, const kivi_cache* cac
                       workspace, workspace_bytes, stream);
 }
 
+// ------------------------------------------------------------------ decode without a workspace --
+//
+// Scratch of kivi_b200_decode_noalloc: a fixed array in the library's device image, so the entry
+// point never allocates. Every GPU that loads the library carries these bytes until the process
+// exits. All calls share it.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[KIVI_B200_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+// Device address of g_noalloc_scratch, looked up once per device. In host code the array's name is
+// only a handle for the runtime, not an address a kernel could use.
+void* g_noalloc_ptr[kivi::kMaxDevices];
+}  // namespace
+
+extern "C" int kivi_b200_decode_noalloc(const kivi_geometry* geom, const kivi_cache* cache, const kivi_f16* q,
+                                        const int32_t* block_tables, int max_blocks_per_seq,
+                                        const int32_t* seq_lens, const int32_t* slot_ids, int batch,
+                                        int max_seq_len, float* out, cudaStream_t stream) {
+    int rc = check_geometry(geom);
+    if (rc != KIVI_OK) return rc;
+    rc = check_cache(cache);
+    if (rc != KIVI_OK) return rc;
+    if (!q || !block_tables || !seq_lens || !out) return KIVI_ERR_NULL_POINTER;
+    if (!aligned16(q) || !aligned16(out)) return KIVI_ERR_ALIGNMENT;
+    if (batch < 0 || max_seq_len < 0 || max_seq_len > 0x3fffffff || max_blocks_per_seq < 0) return KIVI_ERR_RANGE;
+    if (batch == 0) return KIVI_OK;
+    if (!slot_ids && batch > cache->num_slots) return KIVI_ERR_RANGE;
+    const Geom g = make_geom(*geom);
+    const int max_old = split_old(max_seq_len, g.r, g.g);
+    if ((long long)max_old > (long long)max_blocks_per_seq * g.b) return KIVI_ERR_BLOCK_TABLE;
+    // the launch plan decides how much scratch this call needs; refuse what the fixed array cannot hold
+    const WsLayout wl = ws_layout(g, batch, plan_split(g, batch, max_old));
+    if (wl.total > (size_t)KIVI_B200_NOALLOC_SCRATCH_BYTES) return KIVI_ERR_WORKSPACE;
+
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return KIVI_ERR_CUDA;
+    if (!g_noalloc_ptr[dev]) {
+        // first call on this device (with it current): resolve the array's device address
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_noalloc_scratch) != cudaSuccess || !ptr) return KIVI_ERR_CUDA;
+        g_noalloc_ptr[dev] = ptr;
+    }
+    void* scratch = g_noalloc_ptr[dev];
+    // the array keeps whatever the previous call left: the arrival counters must start at zero
+    if (cudaMemsetAsync(static_cast<unsigned char*>(scratch) + wl.count_off, 0, wl.ml_off - wl.count_off, stream) !=
+        cudaSuccess)
+        return KIVI_ERR_CUDA;
+    SeqAddressing a;
+    a.seq_lens = seq_lens; a.seq_len_scalar = 0;
+    a.block_tables = block_tables; a.bt_stride = max_blocks_per_seq; a.bt_width = max_blocks_per_seq;
+    a.slot_ids = slot_ids; a.slot_shared = 0;
+    return run_decode(g, cache_ptrs(*cache), a, reinterpret_cast<const __half*>(q), out, batch, max_seq_len, max_old,
+                      -1, scratch, (size_t)KIVI_B200_NOALLOC_SCRATCH_BYTES, stream);
+}
+
 extern "C" int kivi_b200_gemv_f16(const kivi_f16* w, const kivi_f16* x, kivi_f16* y_f16, float* y_f32, int out_dim,
                                   int in_dim, int batch, cudaStream_t stream) {
     if (!w || !x || (!y_f16 && !y_f32)) return KIVI_ERR_NULL_POINTER;
