@@ -27,6 +27,20 @@ namespace {
 
 constexpr int kThreads = 256;
 
+// Geometry as seen by the writer kernels: compile-time for the shapes the decode kernel's fast
+// path covers (index arithmetic becomes shifts and masks), run-time for everything else.
+template <int D_, int G_, int B_>
+struct StaticShape {
+    __device__ __forceinline__ explicit StaticShape(const Geom&) {}
+    static constexpr int d = D_, g = G_, b = B_;
+    static constexpr int vg = G_ < D_ ? G_ : D_, hg = D_ / vg, pages_per_group = G_ / B_;
+};
+struct DynamicShape {
+    __device__ __forceinline__ explicit DynamicShape(const Geom& x)
+        : d(x.d), g(x.g), b(x.b), vg(x.vg), hg(x.hg), pages_per_group(x.pages_per_group) {}
+    const int d, g, b, vg, hg, pages_per_group;
+};
+
 struct SeqWrite {
     int start, num_new, end, prev_old, next_old, new_row0, slot;
     const int* bt;
@@ -63,15 +77,36 @@ __device__ __forceinline__ const __half* token_row(const WriteParams& p, const S
 
 // clamp_code of the reference (source_patch.py:1517-1522). __float2int_rn rounds to nearest even
 // like rintf, saturates, and maps NaN to 0.
-__device__ __forceinline__ unsigned code_of(float x, float mn, float scale) {
-    int c = __float2int_rn(__fdiv_rn(__fsub_rn(x, mn), scale));
+__device__ __forceinline__ unsigned clamp_code(float q) {
+    int c = __float2int_rn(q);
     c = c < 0 ? 0 : c;
     return (unsigned)(c > 15 ? 15 : c);
 }
 
-__device__ __forceinline__ void stage_tile(const WriteParams& p, const SeqWrite& s, const __half* scratch,
-                                           const __half* fresh, int h, int pos0, __half* tile) {
-    const Geom& g = p.geom;
+// The code of one element. The reference computes clamp(rintf((x - mn) / scale), 0, 15) with an
+// IEEE division. Fast form, bit-identical whenever mn and scale are finite:
+//   * quotient from the correctly rounded reciprocal rcp = 1/scale (computed once per scale):
+//     q0 = a*rcp, r = a - scale*q0 (exact in an FMA), q = q0 + r*rcp is the correctly rounded
+//     quotient (Markstein);
+//   * 0 <= q <= 15 then holds by construction (mn <= x <= mx, scale = (mx-mn)/15), so no clamp;
+//   * q + 1.5*2^23 leaves rint(q), ties to even, in the low mantissa bits. A NaN element gives
+//     NaN + magic = NaN, whose low nibble the caller masks: 0x7fffffff would give 15, so NaN is
+//     squashed to 0 first, as the reference's conversion does.
+// Returns the raw bits of q + magic; the caller folds eight of them into a word.
+__device__ __forceinline__ unsigned code_bits_fast(float x, float mn, float scale, float rcp) {
+    const float a = __fsub_rn(x, mn);
+    float q = __fmul_rn(a, rcp);
+    q = __fmaf_rn(__fmaf_rn(-scale, q, a), rcp, q);
+    q = q == q ? q : 0.0f;
+    return __float_as_uint(__fadd_rn(q, 12582912.0f));
+}
+__device__ __forceinline__ unsigned code_exact(float x, float mn, float scale) {
+    return clamp_code(__fdiv_rn(__fsub_rn(x, mn), scale));
+}
+
+template <class Shape>
+__device__ __forceinline__ void stage_tile(const Shape& g, const WriteParams& p, const SeqWrite& s,
+                                           const __half* scratch, const __half* fresh, int h, int pos0, __half* tile) {
     const int chunks_per_row = g.d / 8;
     const int total = g.g * chunks_per_row;
     for (int c = threadIdx.x; c < total; c += kThreads) {
@@ -81,105 +116,161 @@ __device__ __forceinline__ void stage_tile(const WriteParams& p, const SeqWrite&
     }
 }
 
+// Pack 8 channels of one token (16 bytes of fp16) into one 32-bit word of codes. `exact` selects
+// the plain IEEE division for tiles that hold an Inf/NaN scale or zero-point.
+__device__ __forceinline__ unsigned pack_word(const uint4& v, const float* mn, const float* sc, const float* rc,
+                                              bool exact) {
+    const __half2* h = reinterpret_cast<const __half2*>(&v);
+    float x[8];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const float2 f = __half22float2(h[e]);
+        x[2 * e] = f.x;
+        x[2 * e + 1] = f.y;
+    }
+    unsigned word = 0;
+    if (!exact) {
+        // Horner over the nibbles: every term is 0x4B400000 + code
+#pragma unroll
+        for (int e = 7; e >= 0; --e) word = word * 16u + code_bits_fast(x[e], mn[e], sc[e], rc[e]);
+        word -= 0x4B400000u * 0x11111111u;
+    } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) word |= code_exact(x[e], mn[e], sc[e]) << (4 * e);
+    }
+    return word;
+}
+
+template <class Shape>
 __global__ void __launch_bounds__(kThreads) pack_groups_kernel(const WriteParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    const Geom& g = p.geom;
+    const Shape g(p.geom);
+    const int nkv = p.geom.nkv;
     const int i = blockIdx.z, h = blockIdx.y, j = blockIdx.x;
     const SeqWrite s = seq_write(p, i);
     const int ngroups = (s.next_old - s.prev_old) / g.g;
     if (j >= ngroups) return;
 
+    const int nparam = g.d > g.g * g.hg ? g.d : g.g * g.hg;
     __half* tile = reinterpret_cast<__half*>(smem_raw);                  // [G, D]
-    float* p_min = reinterpret_cast<float*>(tile + (size_t)g.g * g.d);   // [max(D, G*HG)]
-    float* p_scale = p_min + (g.d > g.g * g.hg ? g.d : g.g * g.hg);
+    float* p_min = reinterpret_cast<float*>(tile + (size_t)g.g * g.d);   // [nparam] each
+    float* p_scale = p_min + nparam;
+    float* p_rcp = p_scale + nparam;
+    float* part_min = p_rcp + nparam;                                    // [parts, D]
+    float* part_max = part_min + kThreads * 2;
 
+    __shared__ int s_exact;   // some scale or zero-point of the tile is Inf/NaN: use the plain division
+    if (threadIdx.x == 0) s_exact = 0;
     const int pos0 = s.prev_old + j * g.g;
     const int lp0 = pos0 / g.b;
     if (lp0 + g.pages_per_group > p.seq.bt_width) return;  // table too narrow: host validation failed
     const int words_per_row = g.d / 8;
 
     // ---------------- keys: per channel over the G tokens ----------------
-    stage_tile(p, s, p.cache.k_scratch, p.new_k, h, pos0, tile);
+    stage_tile(g, p, s, p.cache.k_scratch, p.new_k, h, pos0, tile);
     __syncthreads();
-    for (int c = threadIdx.x; c < g.d; c += kThreads) {
-        float mn = __half2float(tile[c]);
-        float mx = mn;
-        for (int t = 1; t < g.g; ++t) {
-            float x = __half2float(tile[(size_t)t * g.d + c]);
-            mn = fminf(mn, x);
-            mx = fmaxf(mx, x);
+    {
+        // thread = (channel pair, slice of the rows); fminf/fmaxf drop NaN and order -0 below +0, so
+        // any reduction order gives the reference's serial result
+        const int pairs = g.d / 2, parts = kThreads / pairs;
+        const int cp = threadIdx.x % pairs, part = threadIdx.x / pairs;
+        if (part < parts) {
+            const int rows = (g.g + parts - 1) / parts;
+            const int r0 = part * rows, r1 = min(g.g, r0 + rows);
+            float mn0 = NAN, mx0 = NAN, mn1 = NAN, mx1 = NAN;   // NaN is the neutral element of fmin/fmax
+            for (int t = r0; t < r1; ++t) {
+                const float2 x = __half22float2(reinterpret_cast<const __half2*>(tile + (size_t)t * g.d)[cp]);
+                mn0 = fminf(mn0, x.x); mx0 = fmaxf(mx0, x.x);
+                mn1 = fminf(mn1, x.y); mx1 = fmaxf(mx1, x.y);
+            }
+            part_min[part * g.d + 2 * cp] = mn0; part_max[part * g.d + 2 * cp] = mx0;
+            part_min[part * g.d + 2 * cp + 1] = mn1; part_max[part * g.d + 2 * cp + 1] = mx1;
         }
-        float scale = __fdiv_rn(__fsub_rn(mx, mn), 15.0f);
-        if (!(scale > 0.0f)) scale = 1.0f;
-        p_min[c] = mn;
-        p_scale[c] = scale;
-        const __half hs = __float2half_rn(scale), hz = __float2half_rn(mn);
-        for (int pi = 0; pi < g.pages_per_group; ++pi) {
-            size_t page = (size_t)s.bt[lp0 + pi];
-            p.cache.k_scale[(page * g.nkv + h) * g.d + c] = hs;
-            p.cache.k_zero[(page * g.nkv + h) * g.d + c] = hz;
+        __syncthreads();
+        for (int c = threadIdx.x; c < g.d; c += kThreads) {
+            float mn = part_min[c], mx = part_max[c];
+            for (int q = 1; q < parts; ++q) { mn = fminf(mn, part_min[q * g.d + c]); mx = fmaxf(mx, part_max[q * g.d + c]); }
+            float scale = __fdiv_rn(__fsub_rn(mx, mn), 15.0f);
+            if (!(scale > 0.0f)) scale = 1.0f;
+            p_min[c] = mn;
+            p_scale[c] = scale;
+            p_rcp[c] = __frcp_rn(scale);
+            if (!(fabsf(mn) < INFINITY && scale < INFINITY)) s_exact = 1;
+            const __half hs = __float2half_rn(scale), hz = __float2half_rn(mn);
+            for (int pi = 0; pi < g.pages_per_group; ++pi) {
+                size_t page = (size_t)s.bt[lp0 + pi];
+                p.cache.k_scale[(page * nkv + h) * g.d + c] = hs;
+                p.cache.k_zero[(page * nkv + h) * g.d + c] = hz;
+            }
         }
     }
     __syncthreads();
     for (int idx = threadIdx.x; idx < g.g * words_per_row; idx += kThreads) {
-        int t = idx / words_per_row, w = idx - t * words_per_row;
-        const __half* row = tile + (size_t)t * g.d + w * 8;
-        unsigned word = 0;
+        const int t = idx / words_per_row, w = idx - t * words_per_row;
+        const uint4 v = reinterpret_cast<const uint4*>(tile)[idx];
+        float mn[8], sc[8], rc[8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            int c = w * 8 + e;
-            word |= code_of(__half2float(row[e]), p_min[c], p_scale[c]) << (4 * e);
+        for (int e = 0; e < 8; e += 4) {
+            *reinterpret_cast<float4*>(mn + e) = *reinterpret_cast<const float4*>(p_min + w * 8 + e);
+            *reinterpret_cast<float4*>(sc + e) = *reinterpret_cast<const float4*>(p_scale + w * 8 + e);
+            *reinterpret_cast<float4*>(rc + e) = *reinterpret_cast<const float4*>(p_rcp + w * 8 + e);
         }
-        size_t page = (size_t)s.bt[lp0 + t / g.b];
-        uint32_t* dst = reinterpret_cast<uint32_t*>(p.cache.k_code + ((page * g.nkv + h) * g.b + (t % g.b)) * (g.d / 2));
-        dst[w] = word;
+        const size_t page = (size_t)s.bt[lp0 + t / g.b];
+        uint32_t* dst = reinterpret_cast<uint32_t*>(p.cache.k_code + ((page * nkv + h) * g.b + (t % g.b)) * (g.d / 2));
+        dst[w] = pack_word(v, mn, sc, rc, s_exact != 0);
     }
     __syncthreads();
+    if (threadIdx.x == 0) s_exact = 0;
 
     // ---------------- values: per token over each channel group ----------------
-    stage_tile(p, s, p.cache.v_scratch, p.new_v, h, pos0, tile);
+    stage_tile(g, p, s, p.cache.v_scratch, p.new_v, h, pos0, tile);
     __syncthreads();
-    // One thread per (token, channel group). fminf/fmaxf drop a NaN operand and order -0 below
-    // +0, so the result does not depend on the scan order; each thread starts at a different
-    // word to spread the shared-memory banks.
-    for (int idx = threadIdx.x; idx < g.g * g.hg; idx += kThreads) {
-        int t = idx / g.hg, cg = idx - t * g.hg;
-        const int seg_words = g.vg / 2;
-        const __half2* seg = reinterpret_cast<const __half2*>(tile + (size_t)t * g.d + cg * g.vg);
-        float2 x0 = __half22float2(seg[t % seg_words]);
-        float mn = fminf(x0.x, x0.y), mx = fmaxf(x0.x, x0.y);
-        for (int k = 1; k < seg_words; ++k) {
-            float2 x = __half22float2(seg[(k + t) % seg_words]);
-            mn = fminf(mn, fminf(x.x, x.y));
-            mx = fmaxf(mx, fmaxf(x.x, x.y));
+    {
+        // two adjacent lanes share one (token, channel group); each starts at a different word to
+        // spread the shared-memory banks
+        const int items = g.g * g.hg, seg_words = g.vg / 2, half_words = seg_words / 2;
+        for (int base = 0; base < items * 2; base += kThreads) {
+            const int id = base + threadIdx.x;
+            const int item = id >> 1, side = id & 1;
+            float mn = NAN, mx = NAN;
+            if (item < items) {
+                const int t = item / g.hg, cg = item - t * g.hg;
+                const __half2* seg = reinterpret_cast<const __half2*>(tile + (size_t)t * g.d + cg * g.vg) + side * half_words;
+                for (int k = 0; k < half_words; ++k) {
+                    const float2 x = __half22float2(seg[(k + t) % half_words]);
+                    mn = fminf(mn, fminf(x.x, x.y));
+                    mx = fmaxf(mx, fmaxf(x.x, x.y));
+                }
+            }
+            mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            if (item < items && side == 0) {
+                const int t = item / g.hg, cg = item - t * g.hg;
+                float scale = __fdiv_rn(__fsub_rn(mx, mn), 15.0f);
+                if (!(scale > 0.0f)) scale = 1.0f;
+                p_min[item] = mn;
+                p_scale[item] = scale;
+                p_rcp[item] = __frcp_rn(scale);
+                if (!(fabsf(mn) < INFINITY && scale < INFINITY)) s_exact = 1;
+                const size_t page = (size_t)s.bt[lp0 + t / g.b];
+                const size_t param = ((page * nkv + h) * g.b + (t % g.b)) * g.hg + cg;
+                p.cache.v_scale[param] = __float2half_rn(scale);
+                p.cache.v_zero[param] = __float2half_rn(mn);
+            }
         }
-        p_min[idx] = mn;
-        p_scale[idx] = mx;
-    }
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < g.g * g.hg; idx += kThreads) {
-        int t = idx / g.hg, cg = idx - t * g.hg;
-        float mn = p_min[idx], mx = p_scale[idx];
-        float scale = __fdiv_rn(__fsub_rn(mx, mn), 15.0f);
-        if (!(scale > 0.0f)) scale = 1.0f;
-        p_scale[idx] = scale;
-        size_t page = (size_t)s.bt[lp0 + t / g.b];
-        size_t param = ((page * g.nkv + h) * g.b + (t % g.b)) * g.hg + cg;
-        p.cache.v_scale[param] = __float2half_rn(scale);
-        p.cache.v_zero[param] = __float2half_rn(mn);
     }
     __syncthreads();
     for (int idx = threadIdx.x; idx < g.g * words_per_row; idx += kThreads) {
-        int t = idx / words_per_row, w = idx - t * words_per_row;
-        const __half* row = tile + (size_t)t * g.d + w * 8;
-        const int cg = (w * 8) / g.vg;
-        const float mn = p_min[t * g.hg + cg], scale = p_scale[t * g.hg + cg];
-        unsigned word = 0;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) word |= code_of(__half2float(row[e]), mn, scale) << (4 * e);
-        size_t page = (size_t)s.bt[lp0 + t / g.b];
-        uint32_t* dst = reinterpret_cast<uint32_t*>(p.cache.v_code + ((page * g.nkv + h) * g.b + (t % g.b)) * (g.d / 2));
-        dst[w] = word;
+        const int t = idx / words_per_row, w = idx - t * words_per_row;
+        const uint4 v = reinterpret_cast<const uint4*>(tile)[idx];
+        const int item = t * g.hg + (w * 8) / g.vg;
+        const float m1 = p_min[item], s1 = p_scale[item], r1 = p_rcp[item];
+        const float mn[8] = {m1, m1, m1, m1, m1, m1, m1, m1};
+        const float sc[8] = {s1, s1, s1, s1, s1, s1, s1, s1};
+        const float rc[8] = {r1, r1, r1, r1, r1, r1, r1, r1};
+        const size_t page = (size_t)s.bt[lp0 + t / g.b];
+        uint32_t* dst = reinterpret_cast<uint32_t*>(p.cache.v_code + ((page * nkv + h) * g.b + (t % g.b)) * (g.d / 2));
+        dst[w] = pack_word(v, mn, sc, rc, s_exact != 0);
     }
 }
 
@@ -224,7 +315,26 @@ __global__ void __launch_bounds__(kThreads) scratch_update_kernel(const WritePar
 
 size_t pack_smem_bytes(const Geom& g) {
     size_t params = (size_t)(g.d > g.g * g.hg ? g.d : g.g * g.hg);
-    return (size_t)g.g * g.d * sizeof(__half) + 2 * params * sizeof(float);
+    return (size_t)g.g * g.d * sizeof(__half) + (3 * params + 4 * kThreads) * sizeof(float);
+}
+
+template <class Shape>
+cudaError_t launch_pack(const WriteParams& p, dim3 grid, size_t smem, cudaStream_t stream) {
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(pack_groups_kernel<Shape>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+    }
+    pack_groups_kernel<Shape><<<grid, kThreads, smem, stream>>>(p);
+    return cudaSuccess;
+}
+
+template <int D, int G>
+cudaError_t launch_pack_for_block(const WriteParams& p, dim3 grid, size_t smem, cudaStream_t stream, bool* done) {
+    *done = true;
+    if (p.geom.b == 16) return launch_pack<StaticShape<D, G, 16>>(p, grid, smem, stream);
+    if (p.geom.b == 32) return launch_pack<StaticShape<D, G, 32>>(p, grid, smem, stream);
+    *done = false;
+    return cudaSuccess;
 }
 
 }  // namespace
@@ -233,12 +343,21 @@ cudaError_t launch_cache_write(const WriteParams& p, int max_new_per_seq, cudaSt
     const Geom& g = p.geom;
     if (p.n <= 0 || max_new_per_seq <= 0) return cudaSuccess;
     const size_t smem = pack_smem_bytes(g);
-    if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(pack_groups_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const int max_groups = max_new_per_seq / g.g + 1;
+    const dim3 grid(max_groups, g.nkv, p.n);
+    bool done = false;
+    cudaError_t e = cudaSuccess;
+    if (g.d == 128 && g.g == 128) e = launch_pack_for_block<128, 128>(p, grid, smem, stream, &done);
+    else if (g.d == 128 && g.g == 64) e = launch_pack_for_block<128, 64>(p, grid, smem, stream, &done);
+    else if (g.d == 128 && g.g == 32) e = launch_pack_for_block<128, 32>(p, grid, smem, stream, &done);
+    else if (g.d == 64 && g.g == 128) e = launch_pack_for_block<64, 128>(p, grid, smem, stream, &done);
+    else if (g.d == 64 && g.g == 64) e = launch_pack_for_block<64, 64>(p, grid, smem, stream, &done);
+    else if (g.d == 64 && g.g == 32) e = launch_pack_for_block<64, 32>(p, grid, smem, stream, &done);
+    if (e != cudaSuccess) return e;
+    if (!done) {
+        e = launch_pack<DynamicShape>(p, grid, smem, stream);
         if (e != cudaSuccess) return e;
     }
-    const int max_groups = max_new_per_seq / g.g + 1;
-    pack_groups_kernel<<<dim3(max_groups, g.nkv, p.n), kThreads, smem, stream>>>(p);
     scratch_update_kernel<<<dim3(g.nkv, p.n), kThreads, 0, stream>>>(p);
     return cudaGetLastError();
 }
