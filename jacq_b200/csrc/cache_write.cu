@@ -112,8 +112,9 @@ __device__ __forceinline__ void stage_tile(const Shape& g, const WriteParams& p,
     for (int c = threadIdx.x; c < total; c += kThreads) {
         int t = c / chunks_per_row, w = c - t * chunks_per_row;
         const uint4* src = reinterpret_cast<const uint4*>(token_row(p, s, scratch, fresh, h, pos0 + t));
-        reinterpret_cast<uint4*>(tile)[c] = src[w];
+        cp_async16(reinterpret_cast<uint4*>(tile) + c, src + w);
     }
+    asm volatile("cp.async.commit_group;" ::: "memory");
 }
 
 // Pack 8 channels of one token (16 bytes of fp16) into one 32-bit word of codes. `exact` selects
@@ -152,8 +153,11 @@ __global__ void __launch_bounds__(kThreads) pack_groups_kernel(const WriteParams
     if (j >= ngroups) return;
 
     const int nparam = g.d > g.g * g.hg ? g.d : g.g * g.hg;
-    __half* tile = reinterpret_cast<__half*>(smem_raw);                  // [G, D]
-    float* p_min = reinterpret_cast<float*>(tile + (size_t)g.g * g.d);   // [nparam] each
+    // both tiles are requested up front (asynchronous copies), so the value rows stream in while
+    // the keys are being quantised
+    __half* tile = reinterpret_cast<__half*>(smem_raw);                  // keys   [G, D]
+    __half* tile_v = tile + (size_t)g.g * g.d;                           // values [G, D]
+    float* p_min = reinterpret_cast<float*>(tile_v + (size_t)g.g * g.d); // [nparam] each
     float* p_scale = p_min + nparam;
     float* p_rcp = p_scale + nparam;
     float* part_min = p_rcp + nparam;                                    // [parts, D]
@@ -168,6 +172,8 @@ __global__ void __launch_bounds__(kThreads) pack_groups_kernel(const WriteParams
 
     // ---------------- keys: per channel over the G tokens ----------------
     stage_tile(g, p, s, p.cache.k_scratch, p.new_k, h, pos0, tile);
+    stage_tile(g, p, s, p.cache.v_scratch, p.new_v, h, pos0, tile_v);
+    asm volatile("cp.async.wait_group 1;" ::: "memory");
     __syncthreads();
     {
         // thread = (channel pair, slice of the rows); fminf/fmaxf drop NaN and order -0 below +0, so
@@ -223,8 +229,9 @@ __global__ void __launch_bounds__(kThreads) pack_groups_kernel(const WriteParams
     if (threadIdx.x == 0) s_exact = 0;
 
     // ---------------- values: per token over each channel group ----------------
-    stage_tile(g, p, s, p.cache.v_scratch, p.new_v, h, pos0, tile);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
+    tile = tile_v;
     {
         // two adjacent lanes share one (token, channel group); each starts at a different word to
         // spread the shared-memory banks
@@ -315,7 +322,7 @@ __global__ void __launch_bounds__(kThreads) scratch_update_kernel(const WritePar
 
 size_t pack_smem_bytes(const Geom& g) {
     size_t params = (size_t)(g.d > g.g * g.hg ? g.d : g.g * g.hg);
-    return (size_t)g.g * g.d * sizeof(__half) + (3 * params + 4 * kThreads) * sizeof(float);
+    return 2 * (size_t)g.g * g.d * sizeof(__half) + (3 * params + 4 * kThreads) * sizeof(float);
 }
 
 template <class Shape>
