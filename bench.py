@@ -49,6 +49,15 @@ WORKLOADS = {
     # enough (sequence, kv head) units that the context is not split: every CTA walks a whole sequence
     "mistral7b_decode_attn_b48_t8192": ("mistral7b", 48, 8192),
 }
+# secondary workloads: the other two parts of the path, each against its own HBM roofline
+SECONDARY = {
+    # one step = the four projections (qkv, o, gate_up, down) of 8 layers of the Qwen2.5-14B shape at
+    # batch 1, every GEMV on its own weights: 4.4 GB of fp16 weights streamed once per step
+    "gemv_qwen25_14b_8layers_b1": "gemv",
+    # one step = one 512-token chunk appended to each of 128 sequences (Mistral-7B shape): every
+    # sequence ages out four key groups
+    "writer_mistral7b_b128_chunk512": "writer",
+}
 DEFAULT_WORKLOAD = "mistral7b_decode_attn_b128_t8192"
 METRIC = "KIVI decode-attn achieved HBM GB/s"
 
@@ -346,6 +355,99 @@ def run_b200(args):
     print(json.dumps(line))
 
 
+def _timed_steps(fn, steps, warmup, device):
+    import torch
+    for _ in range(max(3, warmup)):
+        fn()
+    torch.cuda.synchronize(device)
+    ms = []
+    for _ in range(steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize(device)
+        ms.append(e0.elapsed_time(e1))
+    return ms
+
+
+def run_secondary(args):
+    """GEMV and cache-writer workloads: one GPU, value = algorithmic bytes / CUDA-event time."""
+    import torch
+    from tests import helpers
+    from jacq_b200 import _native
+    from jacq_b200.cache import gemv
+    _native.lib()
+    device = torch.device("cuda:0")
+    torch.cuda.set_device(device)
+    peak, peak_kind = _peaks()
+    kind = SECONDARY[args.workload]
+    if kind == "gemv":
+        hidden, ffn, qkv = 5120, 13824, 7168
+        shapes = [(qkv, hidden), (hidden, hidden), (2 * ffn, hidden), (hidden, ffn)]
+        layers = 8
+        gen = torch.Generator(device=device).manual_seed(11)
+        weights = [[(torch.randn((o, i), device=device, dtype=torch.float16, generator=gen) * 0.02) for o, i in shapes]
+                   for _ in range(layers)]
+        xs = {i: torch.randn((i,), device=device, dtype=torch.float16, generator=gen) for i in (hidden, ffn)}
+        ys = [[torch.empty((o,), device=device, dtype=torch.float16) for o, _ in shapes] for _ in range(layers)]
+        lib = _native.lib()
+        import ctypes
+        stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+        def step():
+            for lw, ly in zip(weights, ys):
+                for w, y in zip(lw, ly):
+                    rc = lib.kivi_b200_gemv_f16(w.data_ptr(), xs[w.shape[1]].data_ptr(), y.data_ptr(), None,
+                                                w.shape[0], w.shape[1], 1, stream)
+                    assert rc == 0
+        step_bytes = layers * sum(o * i * 2 + (o + i) * 2 for o, i in shapes)
+        launches = layers * len(shapes)
+        metric, kernel = "fp16 GEMV achieved HBM GB/s", "gemv_kernel<1>"
+        ms = _timed_steps(step, args.steps, args.warmup, device)
+        extra = {"shapes_out_in": shapes, "layers": layers, "batch": 1}
+    else:
+        case = helpers.CONFIGS["mistral7b"]
+        lay = helpers.layout_of(case)
+        batch, chunk, start = 128, 512, 512
+        from jacq_b200.cache import KiviCache
+        pages = lay.old_pages(start + chunk * (args.steps + max(3, args.warmup) + 1)) + 1
+        cache = KiviCache(lay, batch * pages, batch, pages, device)
+        gen = torch.Generator(device=device).manual_seed(5)
+        cache.set_block_tables(torch.randperm(batch * pages, device=device, generator=gen).to(torch.int32)
+                               .reshape(batch, pages))
+        k = torch.randn((batch * chunk, case.nkv, case.d), device=device, dtype=torch.float16, generator=gen)
+        v = torch.randn((batch * chunk, case.nkv, case.d), device=device, dtype=torch.float16, generator=gen)
+        offs = torch.arange(batch + 1, device=device, dtype=torch.int32) * chunk
+        state = {"len": 0}
+
+        def step():
+            cache.write(k, v, offs, max_new_per_seq=chunk, max_start_seq_len=state["len"])
+            state["len"] += chunk
+        step()   # from empty: afterwards every step ages out exactly chunk / group groups per sequence
+        g, d, nkv, r, hg = case.g, case.d, case.nkv, case.r, lay.hd_groups
+        groups = chunk // g
+        per_head = (2 * chunk * d * 2                      # new K and V rows read (by the pack or the append)
+                    + groups * (g * d + (g // case.b) * d * 4 + g * hg * 4)   # codes, key params per page, value params
+                    + 2 * 2 * r * d * 2)                   # rows that stay fp16: read once, written once, K and V
+        step_bytes = batch * nkv * per_head
+        launches = 2
+        metric, kernel = "KIVI cache-writer achieved HBM GB/s", "pack_groups_kernel + scratch_update_kernel"
+        ms = _timed_steps(step, args.steps, args.warmup, device)
+        extra = {"batch": batch, "chunk_tokens": chunk, "tokens_per_s": batch * chunk / (statistics.mean(ms) * 1e-3)}
+    mean_ms = statistics.mean(ms)
+    value = step_bytes / (mean_ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": metric, "value": value, "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup),
+        "ms_per_step": mean_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16/u4",
+        "data": "synthetic", "config": {"workload": args.workload, "algorithmic_bytes_per_step": step_bytes,
+                                        "l2": "working set exceeds the 126 MB L2", **extra},
+        "gpu_launches": launches * args.steps,
+        "roofline": {"bound": "hbm", "achieved": value, "peak": peak, "unit": "GB/s", "frac": value / peak,
+                     "traffic": None, "peak_source": f"{peak_kind} HBM copy bandwidth", "kernel": kernel},
+    }))
+
+
 def run_reference(args):
     """Reference arm: the CPU port of the reference's writer + decode math, all host threads, no GPU."""
     rank, local_rank, world = _dist_env()
@@ -396,7 +498,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + sorted(SECONDARY))
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
     ap.add_argument("--profile-only", action="store_true",
                     help="build the cache, run warmup+steps decode launches and exit (for ncu)")
@@ -409,7 +511,9 @@ def main():
         raise SystemExit(subprocess.call(cmd))
     if world > 1:
         args.cpu_baseline = False   # rank 0 at N = 1 only
-    if args.impl == "reference":
+    if args.workload in SECONDARY:
+        run_secondary(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_b200(args)

@@ -12,7 +12,7 @@
 // the end, and across chunks by the last CTA to arrive. The last chunk also takes the residual
 // rows, in 16-row tiles.
 //
-// Data movement: every warp owns a small ring of shared-memory slots of 32 tokens each (codes of
+// Data movement: every warp owns a small ring of shared-memory slots of 64 tokens each (codes of
 // K and V, the value scale/zero of those tokens, and with the first slot of a group its key
 // scale/zero). Code pages arrive by 1-D bulk asynchronous copies (cp.async.bulk, the TMA engine
 // without a tensor map: a page is contiguous per kv head); the small parameter arrays and the fp16
@@ -49,7 +49,10 @@ namespace kivi {
 namespace {
 
 constexpr int kResTile = 16;
-constexpr int kSub = 32;                 // tokens per ring slot
+#ifndef KIVI_SUB
+#define KIVI_SUB 64
+#endif
+constexpr int kSubMax = KIVI_SUB;        // tokens per ring slot (never more than a key group)
 constexpr int kBarBytes = 512;           // room for 64 mbarriers
 constexpr int kMaxSlotsPerWarp = 4;
 constexpr int kBarArrivals = 33;         // lane 0's expect_tx arrive + one cp.async arrive per lane
@@ -67,30 +70,31 @@ struct Cfg {
     static constexpr int WPR = D / 8;          // 32-bit code words per token row
     static constexpr int KW = D / 32;          // key words per lane per token
     static constexpr int NMMA = D / 16;        // MMAs per 16-token tile, QK^T and PV each
-    static constexpr int SUBS = G / kSub;      // ring slots per key group
+    static constexpr int SUB = G < kSubMax ? G : kSubMax;   // tokens per ring slot
+    static constexpr int SUBS = G / SUB;       // ring slots per key group
     static constexpr bool HALF = (VG == 32);   // a lane uses half a value word per channel group
     static constexpr int UNITS = HALF ? HG : WPR / 8;   // value words per lane per token
     static constexpr int MPU = HALF ? 2 : 4;   // PV MMAs fed by one unit
     // slot layout (bytes)
     static constexpr int KC = 0;
-    static constexpr int VC = KC + kSub * D / 2;
-    static constexpr int VS = VC + kSub * D / 2;
-    static constexpr int VZ = VS + kSub * HG * 2;
+    static constexpr int VC = KC + SUB * D / 2;
+    static constexpr int VS = VC + SUB * D / 2;
+    static constexpr int VZ = VS + SUB * HG * 2;
     // Key scale/zero of a group are read once, when its first slot is consumed. With one slot per
     // group they ride in the slot; otherwise they go to a small per-warp area (KP_BUFS buffers,
     // enough that the copy for a later group never lands before the current one was read).
     static constexpr int KP_BUFS = SUBS >= 4 ? 1 : (SUBS >= 2 ? 2 : 0);
     static constexpr int KP_BYTES = 4 * D;             // scale [D] then zero [D], fp16
-    static constexpr int KS = KP_BUFS ? 0 : VZ + kSub * HG * 2;
+    static constexpr int KS = KP_BUFS ? 0 : VZ + SUB * HG * 2;
     static constexpr int KZ = KS + D * 2;
-    static constexpr int QUANT_BYTES = VZ + kSub * HG * 2 + (KP_BUFS ? 0 : KP_BYTES);
-    static constexpr int CODE_BYTES = kSub * D;        // K + V codes of one slot
+    static constexpr int QUANT_BYTES = VZ + SUB * HG * 2 + (KP_BUFS ? 0 : KP_BYTES);
+    static constexpr int CODE_BYTES = SUB * D;        // K + V codes of one slot
     static constexpr int RES_STRIDE = 2 * D + 16;      // padded fp16 row: ldmatrix rows hit distinct banks
     static constexpr int RES_BYTES = kResTile * RES_STRIDE;   // 16 key rows OR 16 value rows
     static constexpr int SLOT = ((QUANT_BYTES > RES_BYTES ? QUANT_BYTES : RES_BYTES) + 127) / 128 * 128;
     static constexpr int Q_BYTES = KW * 32 * 16;       // permuted query fragments of all lanes
     static constexpr int STATE_FLOATS = 8 * D + 16;    // per warp: O[8][D], m[8], l[8]
-    static_assert(G % kSub == 0, "a key group must be whole slots");
+    static_assert(G % SUB == 0, "a key group must be whole slots");
     static_assert(UNITS == 1 || UNITS == 2 || UNITS == 4, "unexpected value-word count");
     static_assert(NMMA == UNITS * MPU, "value MMA bookkeeping");
 };
@@ -116,6 +120,7 @@ __device__ __forceinline__ void pair_by_four(const uint4& v, uint32_t (&o)[4]) {
 template <int D, int G, int LOGB, int W, int CTAS>
 __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodeParams p, int per_warp) {
     using C = Cfg<D, G>;
+    constexpr int kSub = C::SUB;
     extern __shared__ __align__(128) unsigned char smem[];
     uint64_t* full = reinterpret_cast<uint64_t*>(smem);
     uint4* qsm = reinterpret_cast<uint4*>(smem + kBarBytes);
@@ -195,7 +200,7 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
     const uint32_t page_stride32 = (uint32_t)page_stride;
     const uint8_t* kc_lane = kc_head + lane * 16;
     const uint8_t* vc_lane = vc_head + lane * 16;
-    constexpr int CH = 4 * C::HG;          // chunks per value-parameter array per slot
+    constexpr int CH = kSub * C::HG / 8;   // 16-byte chunks per value-parameter array per slot
     const bool vp_on = lane < 2 * CH;
     const int vp_c = lane < CH ? lane : lane - CH;
     const int vp_tok = (vp_c * 8) / C::HG;              // slot-relative token of this lane's chunk
@@ -615,7 +620,8 @@ cudaError_t launch(const DecodeParams& p, cudaStream_t stream) {
 // the unrolled two-tile body needs (at 128 it spills and throttles); several small CTAs instead of
 // one large one overlap a CTA's ramp-up and final merge with the steady state of the others and
 // give every warp a long run of groups to amortise its fixed costs. Measured on the Mistral-7B
-// shape (GB/s): 4x3 5043, 6x2 5008, 5x3 4768, 3x4 4691, 8x2 4628, 12x1 4537, 16x1 4113.
+// shape with 32-token slots (GB/s): 4x3 5043, 6x2 5008, 5x3 4768, 3x4 4691, 8x2 4628, 12x1 4537, 16x1 4113;
+// with 64-token slots (half the per-slot wait/refill work, two slots per warp): 4x3 5461, 6x2 5359.
 #ifndef KIVI_DECODE_WARPS
 #define KIVI_DECODE_WARPS 4
 #endif
