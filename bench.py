@@ -448,11 +448,73 @@ def run_secondary(args):
     }))
 
 
+def run_reference_cuda_lane(args):
+    """Reference arm at the reference's own lane (40/8 heads, head_dim 128, block = group = 32,
+    context 4096): the reference's emitted CUDA kernel, compiled unmodified into oracle/_ref, timed on
+    this GPU the way the reference serves it -- one jac_launch per sequence (it has no batch form)."""
+    import ctypes
+    import torch
+    from tests import helpers
+    from oracle import kivi_oracle as ko
+    key, batch, context = WORKLOADS[args.workload]
+    case = helpers.CONFIGS[key]
+    lib_path = ROOT / "oracle" / "_ref" / "libjacq_ref.so"
+    if not lib_path.exists():
+        print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libjacq_ref.so was not built "
+                          "(needs the reference checkout at build time)"}))
+        return
+    ref = ctypes.CDLL(str(lib_path))
+    device = torch.device("cuda:0")
+    torch.cuda.set_device(device)
+    geom = helpers.oracle_geometry(case)
+    lay = helpers.layout_of(case)
+    pages = lay.old_pages(context)
+    nthreads = os.cpu_count() or 1
+    tables = helpers.shuffled_block_tables(batch, pages, batch * pages)
+    oc = ko.OracleCache(geom, batch * pages, batch)
+    kv = [helpers.make_kv(case, context, stream=i) for i in range(batch)]
+    ko.write_batch(oc, np.concatenate([k for k, _ in kv]), np.concatenate([v for _, v in kv]), tables,
+                   np.zeros(batch, np.int32), np.arange(batch + 1, dtype=np.int32) * context, nthreads=nthreads)
+
+    def dev(a):
+        t = torch.from_numpy(a.view(np.int16) if a.dtype == np.uint16 else a).to(device)
+        return t.view(torch.float16) if a.dtype == np.uint16 else t
+    pools = [dev(getattr(oc, n)) for n in ("k_code", "k_scale", "k_zero", "v_code", "v_scale", "v_zero")]
+    ks, vs = dev(oc.k_scratch), dev(oc.v_scratch)
+    bt = torch.from_numpy(tables).to(device)
+    q = dev(helpers.make_q(case, batch).view(np.uint16))
+    out = torch.zeros((batch, case.nh, case.d), dtype=torch.float32, device=device)
+    P = ctypes.c_void_p
+    stream = P(torch.cuda.current_stream(device).cuda_stream)
+
+    def step():
+        for i in range(batch):
+            ref.jac_launch(P(q[i].data_ptr()), P(bt[i].data_ptr()), *[P(t.data_ptr()) for t in pools],
+                           P(ks[i].data_ptr()), P(vs[i].data_ptr()), ctypes.c_int(context), P(out[i].data_ptr()), stream)
+    ms = _timed_steps(step, args.steps, args.warmup, device)
+    mean_ms = statistics.mean(ms)
+    step_bytes = lay.decode_algorithmic_bytes(context) * batch
+    value = step_bytes / (mean_ms * 1e-3) / 1e9
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(3, args.warmup), "ms_per_step": mean_ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32 SIMT", "data": "synthetic",
+        "config": {"workload": args.workload, "note": "the reference's own CUDA (decode_attention_kivi_paged snapshot, "
+                   "nvcc -O3 for sm_100a), one launch per sequence as in its serving loop"},
+        "tokens_per_s": batch / (mean_ms * 1e-3),
+        "cpu_baseline": None,
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
 def run_reference(args):
-    """Reference arm: the CPU port of the reference's writer + decode math, all host threads, no GPU."""
+    """Reference arm: the CPU port of the reference's writer + decode math, all host threads, no GPU.
+    At the reference's own lane the reference's CUDA itself is timed instead."""
     rank, local_rank, world = _dist_env()
     if rank != 0:
         return
+    if WORKLOADS[args.workload][0] == "reflane":
+        return run_reference_cuda_lane(args)
     from tests import helpers
     from oracle import kivi_oracle as ko
     key, batch, context = WORKLOADS[args.workload]
