@@ -59,6 +59,16 @@ SECONDARY = {
     "writer_mistral7b_b128_chunk512": "writer",
 }
 DEFAULT_WORKLOAD = "mistral7b_decode_attn_b128_t8192"
+# the whole decode step of the generated runtime around the KIVI cache (Qwen2.5-14B shape, 48 layers,
+# random-init fp16 weights, context 32768). With --gpus N the model is split over N ranks by KV heads
+# (strong scaling) with an all-reduce after o_proj and down_proj.
+STEP_WORKLOADS = {
+    # name: (batch, context)
+    "qwen25_14b_decode_step_b1_t32768": (1, 32768),
+    "qwen25_14b_decode_step_b8_t32768": (8, 32768),
+    "qwen25_14b_decode_step_b32_t32768": (32, 32768),
+    "qwen25_14b_decode_step_b64_t32768": (64, 32768),   # needs >= 2 GPUs: 132 GB of KV pages + 29.5 GB of weights
+}
 METRIC = "KIVI decode-attn achieved HBM GB/s"
 
 
@@ -448,6 +458,141 @@ def run_secondary(args):
     }))
 
 
+def run_step(args):
+    """Whole decode step (config: Qwen2.5-14B shape) through jacq_b200.runtime.DecodeRuntime.
+
+    value = tokens/s of the whole job (batch / step time, CUDA-graph replay, device-resident token
+    ids); roofline = the bytes one rank must stream per step (its weight shard + the KV bytes of its
+    heads) / step time against the measured HBM copy bandwidth; e2e = the same step fed from and
+    read back into pinned host memory."""
+    import torch
+    import torch.distributed as dist
+    from jacq_b200 import _native
+    from jacq_b200.runtime import DecodeModelConfig, DecodeRuntime, random_layer
+    _native.lib()
+    rank, local_rank, world = _dist_env()
+    device = torch.device(f"cuda:{local_rank}")
+    torch.cuda.set_device(device)
+    group = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+        group = dist.group.WORLD
+    cfg = DecodeModelConfig.qwen25_14b()
+    batch, context = STEP_WORKLOADS[args.workload]
+    warm = max(3, args.warmup)
+    total_steps = warm + 2 * args.steps + 2          # warm-up, device-timed steps, end-to-end steps
+    start = context - total_steps
+    gen = torch.Generator(device=device).manual_seed(1234)   # same seed on every rank: replicated tensors agree
+
+    def mat(rows, cols):
+        return (torch.randn((rows, cols), generator=gen, device=device, dtype=torch.float32) * 0.02).half()
+
+    weights = {"embed": mat(cfg.vocab, cfg.hidden),
+               "final_norm": (1.0 + 0.1 * torch.randn((cfg.hidden,), generator=gen, device=device)).half(),
+               "lm_head": mat(cfg.vocab // world, cfg.hidden),
+               "layers": [random_layer(cfg, gen, device, rank=rank, world=world) for _ in range(cfg.layers)]}
+    tables = torch.randperm(batch * (-(-(context - cfg.residual) // cfg.block_size)), generator=gen, device=device)
+    rt = DecodeRuntime(cfg, weights, batch=batch, max_seq_len=context, device=device, rank=rank, world=world,
+                       group=group, block_tables=tables.to(torch.int32).reshape(batch, -1))
+    # synthetic context: fill layer 0 through the library's writer, then give every layer the same pages
+    c0 = rt.caches[0]
+    c0.set_block_tables(rt.block_tables)
+    nkv_l, d = cfg.num_kv_heads // world, cfg.head_dim
+    chunk = 2048
+    offs = torch.arange(batch + 1, device=device, dtype=torch.int32)
+    done = 0
+    while done < start:
+        n = min(chunk, start - done)
+        k = torch.randn((batch * n, nkv_l, d), generator=gen, device=device, dtype=torch.float16)
+        k[:, :, :3] *= 10.0                              # a few outlier key channels, as in the attention workloads
+        v = torch.randn((batch * n, nkv_l, d), generator=gen, device=device, dtype=torch.float16)
+        c0.write(k, v, offs * n, max_new_per_seq=n, max_start_seq_len=done)
+        done += n
+    del k, v
+    for c in rt.caches[1:]:
+        for name in c0.tensors.names():
+            getattr(c.tensors, name).copy_(getattr(c0.tensors, name))
+    rt.set_seq_lens([start] * batch)
+    rt.tokens.copy_(torch.arange(batch, dtype=torch.int32) * 997 + 11)
+    if world > 1:
+        dist.all_reduce(torch.zeros(8, device=device, dtype=torch.float16))   # communicator up before the capture
+    torch.cuda.synchronize(device)
+    rt.capture()
+    for _ in range(warm):
+        rt.step()
+    torch.cuda.synchronize(device)
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        rt.step()
+    e1.record()
+    torch.cuda.synchronize(device)
+    if world > 1:
+        dist.barrier()
+    total_ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        t = torch.tensor([total_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+
+    # end to end: token ids from pinned host memory in, next ids back out, every step
+    tok_host = rt.tokens.cpu().pin_memory()
+    out_host = torch.empty_like(tok_host).pin_memory()
+    torch.cuda.synchronize(device)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        rt.tokens.copy_(tok_host, non_blocking=True)
+        rt.step()
+        out_host.copy_(rt.tokens, non_blocking=True)
+        torch.cuda.synchronize(device)
+        tok_host.copy_(out_host)
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    final_lens = rt.seq_lens.cpu().tolist()
+
+    if rank == 0:
+        peak, peak_kind = _peaks()
+        weight_bytes = cfg.weight_bytes(world)
+        kv_bytes = rt.kv_bytes_per_step(context)
+        rank_bytes = weight_bytes + kv_bytes
+        achieved = rank_bytes / (ms_per_step * 1e-3) / 1e9
+        launches_per_step = cfg.layers * 10 + 6
+        print(json.dumps({
+            "metric": "decode-step tokens/s", "value": batch / (ms_per_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": warm, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f16/u4", "data": "synthetic",
+            "config": {"workload": args.workload, "model_shape": cfg.name, "layers": cfg.layers, "batch": batch,
+                       "context": context, "block": cfg.block_size, "group": cfg.group_size, "residual": cfg.residual,
+                       "parallelism": f"tp{world} over kv heads" if world > 1 else "1 gpu",
+                       "weights": "random-init fp16 N(0, 0.02)", "step": "CUDA-graph replay of kivi_b200_decode_step",
+                       "l2": "29.5 GB of weights and the KV pages exceed the 126 MB L2",
+                       "final_seq_lens_ok": final_lens == [context - 2] * batch},
+            "e2e": {"value": batch / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 4 * batch,
+                    "d2h_bytes_per_step": 4 * batch, "ms_per_step": e2e_ms},
+            "gpu_launches": launches_per_step * (warm + 2 * args.steps),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_source": f"{peak_kind} HBM copy bandwidth",
+                         "bytes_per_rank_per_step": {"weights": weight_bytes, "kv_cache": kv_bytes},
+                         "kernel": "whole step: gemv / skinny GEMM, decode_mma_kernel, writer, element-wise"},
+            "cpu_baseline": None,
+            "clocks": clocks,
+        }))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_reference_cuda_lane(args):
     """Reference arm at the reference's own lane (40/8 heads, head_dim 128, block = group = 32,
     context 4096): the reference's emitted CUDA kernel, compiled unmodified into oracle/_ref, timed on
@@ -560,7 +705,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + sorted(SECONDARY))
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + sorted(SECONDARY) + sorted(STEP_WORKLOADS))
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
     ap.add_argument("--profile-only", action="store_true",
                     help="build the cache, run warmup+steps decode launches and exit (for ncu)")
@@ -573,7 +718,9 @@ def main():
         raise SystemExit(subprocess.call(cmd))
     if world > 1:
         args.cpu_baseline = False   # rank 0 at N = 1 only
-    if args.workload in SECONDARY:
+    if args.workload in STEP_WORKLOADS and args.impl != "reference":
+        run_step(args)
+    elif args.workload in SECONDARY:
         run_secondary(args)
     elif args.impl == "reference":
         run_reference(args)

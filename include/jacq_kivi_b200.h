@@ -161,11 +161,125 @@ int kivi_b200_decode_noalloc(const kivi_geometry* geom, const kivi_cache* cache,
  * W row-major [out_dim, in_dim], fp32 accumulation (reference: gemv(),
  * crates/jac-codegen-cuda/src/templates/runtime.cu:15-26, a cublasGemmEx call). 1 <= batch <= 64.
  * in_dim % 8 == 0. Exactly one of y_f16 / y_f32 may be NULL; y_f32 is the kernel-DSL form
- * (crates/jac-codegen-cuda/src/variants.rs:318-329). */
+ * (crates/jac-codegen-cuda/src/variants.rs:318-329). Batches of 5..64 columns with in_dim % 64 == 0
+ * run as a tensor-core skinny GEMM that splits the contraction over a thread-block cluster and
+ * reduces through distributed shared memory; no call of this entry point allocates. */
 int kivi_b200_gemv_f16(const kivi_f16* w, const kivi_f16* x, kivi_f16* y_f16, float* y_f32,
                        int out_dim, int in_dim, int batch, cudaStream_t stream);
 
 /* ------------------------------------------------------------------ ABI v1 (reference lane) -- */
+
+/* ---------------------------------------------------------------------------------------------
+ * Decode step of the generated runtime around the KIVI cache.
+ *
+ * forward() of crates/jac-codegen-cuda/src/templates/runtime.cu:125-187 runs one token through
+ * embed -> L x [RMSNorm, fused QKV projection (+bias), RoPE, KV store, attention, O projection,
+ * residual add, RMSNorm, fused gate|up projection, SiLU(gate)*up, down projection, residual add]
+ * -> RMSNorm -> lm_head, with the kernels of templates/kernels.cu:4-227 between cuBLAS GEMVs and
+ * an fp16 KV cache [L, NKV, MAX_SEQ, HD]. kivi_b200_decode_step is that step for `batch`
+ * sequences at once with the fp16 cache replaced by the int4-KIVI paged cache (one kivi_cache per
+ * layer; all layers share the block tables, the sequence lengths and the scratch slot ids) and
+ * the arg-max of kernels.cu:203-227 at the end. Arithmetic follows the reference kernels
+ * (fp16 storage of every intermediate, fp32 inside a kernel; RMSNorm, SiLU, bias and residual add
+ * are bit-identical to the reference kernels on the same GPU, RoPE too up to rare one-ulp
+ * differences at large positions; the projections are fp32-accumulated like the cuBLAS call they
+ * replace, in a different summation order).
+ *
+ * Weights use the reference's file layout (templates/export.py:69-92, loader runtime.cu:59-97):
+ * row-major [out, in]; qkv = q|k|v rows fused; gate_up = gate|up rows fused.
+ *
+ * Tensor parallelism over KV heads (no counterpart in the reference): rank r of tp_size holds the
+ * query/key/value rows of its KV heads, the matching columns of `o`, FFN/tp_size gate and up rows,
+ * the matching columns of `down` and VOCAB/tp_size rows of lm_head; the head, FFN and vocabulary
+ * counts in kivi_step_config are those LOCAL sizes. The two partial projections per layer are
+ * summed across ranks by the caller's all-reduce hook (fp16 sum, in place), the per-rank arg-max
+ * candidates by its all-gather hook.
+ * --------------------------------------------------------------------------------------------- */
+typedef struct kivi_step_config {
+    int32_t layers;
+    int32_t hidden;        /* H (global) */
+    int32_t num_q_heads;   /* local NH */
+    int32_t num_kv_heads;  /* local NKV */
+    int32_t head_dim;
+    int32_t ffn;           /* local FFN rows of gate and of up */
+    int32_t vocab;         /* local lm_head rows */
+    int32_t vocab_offset;  /* global id of local row 0 */
+    int32_t attn_bias;     /* 1: qkv_bias is added after the QKV projection (Config::ATTN_BIAS) */
+    float rope_base;       /* Config::ROPE_BASE */
+    float norm_eps;        /* Config::NORM_EPS */
+    int32_t block_size;    /* KIVI page geometry, as in kivi_geometry */
+    int32_t group_size;
+    int32_t residual;
+    int32_t tp_size;       /* 1 = no tensor parallelism */
+    int32_t tp_rank;
+} kivi_step_config;
+
+typedef struct kivi_layer_weights {
+    const kivi_f16* attn_norm;  /* [H] */
+    const kivi_f16* qkv;        /* [(NH + 2 NKV) * D, H] */
+    const kivi_f16* qkv_bias;   /* [(NH + 2 NKV) * D] or NULL */
+    const kivi_f16* o;          /* [H, NH * D] */
+    const kivi_f16* ffn_norm;   /* [H] */
+    const kivi_f16* gate_up;    /* [2 * FFN, H] */
+    const kivi_f16* down;       /* [H, FFN] */
+} kivi_layer_weights;
+
+typedef struct kivi_step_weights {
+    const kivi_f16* embed;               /* [VOCAB_GLOBAL, H], replicated on every rank */
+    const kivi_f16* final_norm;          /* [H] */
+    const kivi_f16* lm_head;             /* [VOCAB, H] */
+    const kivi_layer_weights* layers;    /* host array [layers] of device pointers */
+} kivi_step_weights;
+
+typedef struct kivi_step_state {
+    const kivi_cache* caches;        /* host array [layers] */
+    const int32_t* block_tables;     /* device [batch, max_blocks_per_seq] */
+    int32_t max_blocks_per_seq;
+    int32_t* seq_lens;               /* device [batch]: tokens already cached; the step adds one to each */
+    const int32_t* slot_ids;         /* device [batch] or NULL (slot i for sequence i) */
+    void* workspace;                 /* device, kivi_b200_decode_step_workspace_bytes, zeroed once */
+    size_t workspace_bytes;
+} kivi_step_state;
+
+/* Collective hooks for tp_size > 1; both run on `stream` and return 0 on success. */
+typedef int (*kivi_allreduce_f16_fn)(void* user, kivi_f16* buf, size_t count, cudaStream_t stream);
+typedef int (*kivi_allgather_fn)(void* user, const void* send, void* recv, size_t bytes_per_rank,
+                                 cudaStream_t stream);
+typedef struct kivi_step_comm {
+    kivi_allreduce_f16_fn allreduce_f16;
+    kivi_allgather_fn allgather;
+    void* user;
+} kivi_step_comm;
+
+size_t kivi_b200_decode_step_workspace_bytes(const kivi_step_config* cfg, int batch, int max_seq_len);
+
+/* One decode step. tokens_in / tokens_out: device int32 [batch] (global token ids; they may alias).
+ * logits_out: optional device fp16 [batch, vocab] (local rows). max_seq_len bounds every sequence
+ * length AFTER the step (launch planning; a captured graph stays valid while the bound holds).
+ * The whole step is stream-ordered and allocation-free, so it can be captured in a CUDA graph. */
+int kivi_b200_decode_step(const kivi_step_config* cfg, const kivi_step_weights* weights,
+                          const kivi_step_state* state, const int32_t* tokens_in, int batch,
+                          int max_seq_len, int32_t* tokens_out, kivi_f16* logits_out,
+                          const kivi_step_comm* comm, cudaStream_t stream);
+
+/* The step's element-wise kernels on their own (parity tests against the reference kernels):
+ * rows of `hidden` (resp. heads, `n`) fp16 values, `batch` rows.
+ *   residual_rmsnorm: x_out = x + delta (delta may be NULL); normed = RMSNorm(x_out) * weight
+ *                     (kernels.cu:10-33 after vadd, :156-159)
+ *   bias_rope:        qkv (+bias) -> RoPE on q and k heads at positions[b] (kernels.cu:40-54, :163-166)
+ *                     written split as q [batch, NH*D], k and v [batch, NKV*D]
+ *   silu_mul:         out = SiLU(gate) * up for gate_up rows [gate | up] (kernels.cu:146-153)
+ *   argmax:           first index of the row maximum (kernels.cu:203-227) */
+int kivi_b200_residual_rmsnorm(const kivi_f16* x, const kivi_f16* delta, const kivi_f16* weight,
+                               kivi_f16* x_out, kivi_f16* normed, int batch, int hidden, float eps,
+                               cudaStream_t stream);
+int kivi_b200_bias_rope(const kivi_f16* qkv, const kivi_f16* bias, const int32_t* positions,
+                        kivi_f16* q, kivi_f16* k, kivi_f16* v, int batch, int num_q_heads,
+                        int num_kv_heads, int head_dim, float rope_base, cudaStream_t stream);
+int kivi_b200_silu_mul(const kivi_f16* gate_up, kivi_f16* out, int batch, int ffn, cudaStream_t stream);
+int kivi_b200_argmax(const kivi_f16* logits, int32_t* out_index, int batch, int n, void* workspace,
+                     size_t workspace_bytes, cudaStream_t stream);
+
 
 /* Replaces the emitted `jac_launch` of decode_attention_kivi_paged
  * (crates/jac-codegen-cuda/src/variants.rs:2593-2601; declared by the binding at

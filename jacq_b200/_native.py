@@ -6,7 +6,7 @@ shared object has not been built (``python -m jacq_b200.build``).
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_int, c_int32, c_size_t, c_void_p
+from ctypes import c_float, c_int, c_int32, c_size_t, c_void_p
 from pathlib import Path
 
 LIB_PATH = Path(__file__).resolve().parent / "_lib" / "libjacq_kivi_b200.so"
@@ -32,6 +32,38 @@ class KiviCacheStruct(ctypes.Structure):
                [("num_blocks", c_int32), ("num_slots", c_int32)]
 
 
+class KiviStepConfig(ctypes.Structure):
+    """``kivi_step_config`` of the header (head, FFN and vocabulary counts are per rank)."""
+
+    _fields_ = [(n, c_int32) for n in ("layers", "hidden", "num_q_heads", "num_kv_heads", "head_dim", "ffn", "vocab",
+                                        "vocab_offset", "attn_bias")] + \
+               [("rope_base", c_float), ("norm_eps", c_float)] + \
+               [(n, c_int32) for n in ("block_size", "group_size", "residual", "tp_size", "tp_rank")]
+
+
+class KiviLayerWeights(ctypes.Structure):
+    _fields_ = [(n, c_void_p) for n in ("attn_norm", "qkv", "qkv_bias", "o", "ffn_norm", "gate_up", "down")]
+
+
+class KiviStepWeights(ctypes.Structure):
+    _fields_ = [("embed", c_void_p), ("final_norm", c_void_p), ("lm_head", c_void_p),
+                ("layers", ctypes.POINTER(KiviLayerWeights))]
+
+
+class KiviStepState(ctypes.Structure):
+    _fields_ = [("caches", ctypes.POINTER(KiviCacheStruct)), ("block_tables", c_void_p),
+                ("max_blocks_per_seq", c_int32), ("seq_lens", c_void_p), ("slot_ids", c_void_p),
+                ("workspace", c_void_p), ("workspace_bytes", c_size_t)]
+
+
+ALLREDUCE_F16_FN = ctypes.CFUNCTYPE(c_int, c_void_p, c_void_p, c_size_t, c_void_p)
+ALLGATHER_FN = ctypes.CFUNCTYPE(c_int, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p)
+
+
+class KiviStepComm(ctypes.Structure):
+    _fields_ = [("allreduce_f16", ALLREDUCE_F16_FN), ("allgather", ALLGATHER_FN), ("user", c_void_p)]
+
+
 STATUS_NAMES = {
     0: "KIVI_OK", 1: "KIVI_ERR_NULL_POINTER", 2: "KIVI_ERR_GEOMETRY", 3: "KIVI_ERR_RANGE",
     4: "KIVI_ERR_ALIGNMENT", 5: "KIVI_ERR_WORKSPACE", 6: "KIVI_ERR_CUDA", 7: "KIVI_ERR_BLOCK_TABLE",
@@ -54,6 +86,14 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "kivi_b200_decode_noalloc": (c_int, [ctypes.POINTER(KiviGeometry), ctypes.POINTER(KiviCacheStruct), _P, _P, c_int, _P,
                                          _P, c_int, c_int, _P, _P]),
     "kivi_b200_gemv_f16": (c_int, [_P, _P, _P, _P, c_int, c_int, c_int, _P]),
+    "kivi_b200_decode_step_workspace_bytes": (c_size_t, [ctypes.POINTER(KiviStepConfig), c_int, c_int]),
+    "kivi_b200_decode_step": (c_int, [ctypes.POINTER(KiviStepConfig), ctypes.POINTER(KiviStepWeights),
+                                      ctypes.POINTER(KiviStepState), _P, c_int, c_int, _P, _P,
+                                      ctypes.POINTER(KiviStepComm), _P]),
+    "kivi_b200_residual_rmsnorm": (c_int, [_P, _P, _P, _P, _P, c_int, c_int, c_float, _P]),
+    "kivi_b200_bias_rope": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_float, _P]),
+    "kivi_b200_silu_mul": (c_int, [_P, _P, c_int, c_int, _P]),
+    "kivi_b200_argmax": (c_int, [_P, _P, c_int, c_int, _P, c_size_t, _P]),
     "jac_launch": (None, [_P, _P] + _V1_CACHE + [c_int, _P, _P]),
     "jac_launch_tp2_local": (None, [_P, _P] + _V1_CACHE + [c_int, _P, _P]),
     "jac_launch_batched": (None, [_P, _P, _P] + _V1_CACHE + [c_int, _P, _P]),

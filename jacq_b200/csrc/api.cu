@@ -86,11 +86,17 @@ WsLayout ws_layout(const Geom& g, int n, const SplitPlan& sp) {
     return w;
 }
 
-int run_decode(const Geom& g, const CachePtrs& cache, const SeqAddressing& seq, const __half* q, float* out, int n,
-               int max_seq_cap, int max_old_tokens, int retained_pages, void* ws, size_t ws_bytes,
-               cudaStream_t stream) {
+}  // namespace
+
+size_t decode_workspace_total(const Geom& g, int n, int max_old_tokens) {
+    return ws_layout(g, n, plan_split(g, n, max_old_tokens)).total;
+}
+
+int run_decode(const Geom& g, const CachePtrs& cache, const SeqAddressing& seq, const __half* q, float* out,
+               __half* out_h, int n, int max_seq_cap, int max_old_tokens, int retained_pages, void* ws,
+               size_t ws_bytes, cudaStream_t stream) {
     DecodeParams p;
-    p.geom = g; p.cache = cache; p.seq = seq; p.q = q; p.out = out; p.n = n;
+    p.geom = g; p.cache = cache; p.seq = seq; p.q = q; p.out = out; p.out_h = out_h; p.n = n;
     p.max_seq = max_seq_cap; p.retained_pages = retained_pages; p.status = nullptr;
     const SplitPlan sp = plan_split(g, n, max_old_tokens);
     const WsLayout wl = ws_layout(g, n, sp);
@@ -108,6 +114,8 @@ int run_decode(const Geom& g, const CachePtrs& cache, const SeqAddressing& seq, 
                                                            : launch_decode_generic(p, stream);
     return e == cudaSuccess ? KIVI_OK : KIVI_ERR_CUDA;
 }
+
+namespace {
 
 // ------------------------------------------------------------------ reference lane (ABI v1) --
 
@@ -182,7 +190,7 @@ void ref_decode(int nh, int nkv, const kivi_f16* Q, const int* seq_lens, int seq
     a.slot_ids = nullptr; a.slot_shared = 1;
     size_t ws_bytes = 0;
     void* ws = ref_workspace(g, n, &ws_bytes, stream);
-    int rc = run_decode(g, cache, a, reinterpret_cast<const __half*>(Q), O, n, kRefLQ + kRefR, kRefLQ, retained, ws, ws_bytes,
+    int rc = run_decode(g, cache, a, reinterpret_cast<const __half*>(Q), O, nullptr, n, kRefLQ + kRefR, kRefLQ, retained, ws, ws_bytes,
                         stream);
     if (rc != KIVI_OK) { fprintf(stderr, "jac_launch: %s\n", kivi_b200_status_string(rc)); exit(1); }
 }
@@ -295,7 +303,7 @@ extern "C" int kivi_b200_decode(const kivi_geometry* geom, const kivi_cache* cac
     a.slot_ids = slot_ids; a.slot_shared = 0;
     // max_seq_len also clamps a device-side length beyond the stated bound, so the launch plan and
     // the workspace stay valid whatever seq_lens holds.
-    return run_decode(g, cache_ptrs(*cache), a, reinterpret_cast<const __half*>(q), out, batch, max_seq_len, max_old, -1,
+    return run_decode(g, cache_ptrs(*cache), a, reinterpret_cast<const __half*>(q), out, nullptr, batch, max_seq_len, max_old, -1,
                       workspace, workspace_bytes, stream);
 }
 
@@ -349,7 +357,7 @@ extern "C" int kivi_b200_decode_noalloc(const kivi_geometry* geom, const kivi_ca
     a.seq_lens = seq_lens; a.seq_len_scalar = 0;
     a.block_tables = block_tables; a.bt_stride = max_blocks_per_seq; a.bt_width = max_blocks_per_seq;
     a.slot_ids = slot_ids; a.slot_shared = 0;
-    return run_decode(g, cache_ptrs(*cache), a, reinterpret_cast<const __half*>(q), out, batch, max_seq_len, max_old,
+    return run_decode(g, cache_ptrs(*cache), a, reinterpret_cast<const __half*>(q), out, nullptr, batch, max_seq_len, max_old,
                       -1, scratch, (size_t)KIVI_B200_NOALLOC_SCRATCH_BYTES, stream);
 }
 
@@ -358,9 +366,12 @@ extern "C" int kivi_b200_gemv_f16(const kivi_f16* w, const kivi_f16* x, kivi_f16
     if (!w || !x || (!y_f16 && !y_f32)) return KIVI_ERR_NULL_POINTER;
     if (out_dim <= 0 || in_dim <= 0 || batch < 1 || batch > 64 || in_dim % 8) return KIVI_ERR_RANGE;
     if (!aligned16(w) || !aligned16(x)) return KIVI_ERR_ALIGNMENT;
-    return launch_gemv(reinterpret_cast<const __half*>(w), reinterpret_cast<const __half*>(x),
-                       reinterpret_cast<__half*>(y_f16), y_f32, out_dim, in_dim, batch, stream) == cudaSuccess
-               ? KIVI_OK : KIVI_ERR_CUDA;
+    const __half* wh = reinterpret_cast<const __half*>(w);
+    const __half* xh = reinterpret_cast<const __half*>(x);
+    __half* yh = reinterpret_cast<__half*>(y_f16);
+    if (skinny_gemm_supports(in_dim, batch))
+        return launch_skinny_gemm(wh, xh, yh, y_f32, out_dim, in_dim, batch, stream) == cudaSuccess ? KIVI_OK : KIVI_ERR_CUDA;
+    return launch_gemv(wh, xh, yh, y_f32, out_dim, in_dim, batch, stream) == cudaSuccess ? KIVI_OK : KIVI_ERR_CUDA;
 }
 
 // ------------------------------------------------------------------ ABI v1 symbols -----------

@@ -141,13 +141,13 @@ __global__ void __launch_bounds__(256) decode_generic_kernel(const DecodeParams 
 
         if (nchunks == 1) {
             const float inv_l = 1.0f / fmaxf(l, 1.0e-30f);
-            float* oh = p.out + ((size_t)i * g.nh + h) * g.d;
+            const size_t oh = ((size_t)i * g.nh + h) * g.d;
 #pragma unroll
             for (int k = 0; k < kMaxBytesPerLane; ++k) {
                 int j = lane + 32 * k;
                 if (j < bytes_per_row) {
-                    oh[2 * j] = a0[k] * inv_l;
-                    oh[2 * j + 1] = a1[k] * inv_l;
+                    store_out(p, oh + 2 * j, a0[k] * inv_l);
+                    store_out(p, oh + 2 * j + 1, a1[k] * inv_l);
                 }
             }
         } else {

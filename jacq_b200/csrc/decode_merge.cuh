@@ -52,7 +52,7 @@ __device__ __forceinline__ void merge_when_last(const DecodeParams& p, int i, in
             l += w * __ldcg(p.ws_ml + pi * 2 + 1);
             acc += w * __ldcg(p.ws_o + pi * g.d + d);
         }
-        p.out[((size_t)i * g.nh + kv * g.qpk + hq) * g.d + d] = acc / fmaxf(l, 1.0e-30f);
+        store_out(p, ((size_t)i * g.nh + kv * g.qpk + hq) * g.d + d, acc / fmaxf(l, 1.0e-30f));
     }
     if (threadIdx.x == 0) *counter = 0u;  // leave the workspace ready for the next launch
 }

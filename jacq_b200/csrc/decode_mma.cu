@@ -103,6 +103,19 @@ struct Cfg {
 // With this pair swap the 16-byte key loads of a quarter warp touch rows of both parities.
 __device__ __forceinline__ int row_token(int rho) { return rho ^ ((rho >> 1) & 1); }
 
+// Split query fragment: q*scale is rounded to fp16 once (hi); lo = q*scale - hi is exact in an fp16
+// FMA, and a second MMA set over the same code registers adds it back. It costs about a tenth of
+// the kernel's throughput and cuts the output error by an order of magnitude. KIVI_QK_SPLIT:
+// 0 = never, 1 = always, 2 (default) = for head_dim 64 only, whose short dot products with
+// outlier channels otherwise come within a factor of two of the 1e-2 tolerance.
+#ifndef KIVI_QK_SPLIT
+#define KIVI_QK_SPLIT 2
+#endif
+__device__ __forceinline__ uint32_t hfma2_residual_u32(uint32_t a, uint32_t b, uint32_t hi) {
+    __half2 r = __hfma2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b),
+                        __hneg2(*reinterpret_cast<__half2*>(&hi)));
+    return *reinterpret_cast<uint32_t*>(&r);
+}
 __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
     __half2 r = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
     return *reinterpret_cast<uint32_t*>(&r);
@@ -293,6 +306,8 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
 
     // ---- per-warp state --------------------------------------------------------------------------
     uint32_t qs[4 * C::KW];   // query fragment times the key scales of the current group (residual: natural pairs)
+    constexpr bool kSplitQ = KIVI_QK_SPLIT == 1 || (KIVI_QK_SPLIT == 2 && D == 64);
+    uint32_t ql[kSplitQ ? 4 * C::KW : 1];   // rounding residual of qs
     const float scale_log2 = rsqrtf((float)D) * kLog2e;
     const float sc_code = scale_log2 * 16777216.0f;   // undo the 2^-24 of the subnormal codes
     // Scores are s = raw * mult + add (log2 units); the state keeps m and b = add - m per head.
@@ -374,6 +389,12 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
                     qs[4 * j + 1] = hmul2_u32(qv.y, sp[1]);
                     qs[4 * j + 2] = hmul2_u32(qv.z, sp[2]);
                     qs[4 * j + 3] = hmul2_u32(qv.w, sp[3]);
+                    if constexpr (kSplitQ) {
+                        ql[4 * j + 0] = hfma2_residual_u32(qv.x, sp[0], qs[4 * j + 0]);
+                        ql[4 * j + 1] = hfma2_residual_u32(qv.y, sp[1], qs[4 * j + 1]);
+                        ql[4 * j + 2] = hfma2_residual_u32(qv.z, sp[2], qs[4 * j + 2]);
+                        ql[4 * j + 3] = hfma2_residual_u32(qv.w, sp[3], qs[4 * j + 3]);
+                    }
                     // zero-point term: all rows equal; even channels scaled 2^-4 to match the odd 2^-4 of q
                     const uint32_t z0 = hmul2_u32(zp[0], sixteenth), z2 = hmul2_u32(zp[2], sixteenth);
                     mma16816(ca, z0, z0, zp[1], zp[1], qv.x, qv.y);
@@ -404,10 +425,14 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
 #pragma unroll
                     for (int j = 0; j < C::KW; ++j) {
                         const uint32_t wa = ka[j], wb = kb[j], wa8 = shr8(wa), wb8 = shr8(wb);
-                        mma16816(sc, wa & 0x000f000fu, wb & 0x000f000fu, wa & 0x00f000f0u, wb & 0x00f000f0u,
-                                 qs[4 * j + 0], qs[4 * j + 1]);
-                        mma16816(sd, wa8 & 0x000f000fu, wb8 & 0x000f000fu, wa8 & 0x00f000f0u, wb8 & 0x00f000f0u,
-                                 qs[4 * j + 2], qs[4 * j + 3]);
+                        const uint32_t a0 = wa & 0x000f000fu, a1 = wb & 0x000f000fu, a2 = wa & 0x00f000f0u, a3 = wb & 0x00f000f0u;
+                        const uint32_t c0 = wa8 & 0x000f000fu, c1 = wb8 & 0x000f000fu, c2 = wa8 & 0x00f000f0u, c3 = wb8 & 0x00f000f0u;
+                        mma16816(sc, a0, a1, a2, a3, qs[4 * j + 0], qs[4 * j + 1]);
+                        mma16816(sd, c0, c1, c2, c3, qs[4 * j + 2], qs[4 * j + 3]);
+                        if constexpr (kSplitQ) {
+                            mma16816(sd, a0, a1, a2, a3, ql[4 * j + 0], ql[4 * j + 1]);
+                            mma16816(sc, c0, c1, c2, c3, ql[4 * j + 2], ql[4 * j + 3]);
+                        }
                     }
                 }
                 sc[0] += sd[0]; sc[1] += sd[1]; sc[2] += sd[2]; sc[3] += sd[3];
@@ -587,7 +612,7 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
             acc += wt * sw[hq * D + d];
         }
         if (nchunks == 1) {
-            p.out[((size_t)i * g.nh + (size_t)kv * g.qpk + hq) * D + d] = acc / fmaxf(l, 1.0e-30f);
+            store_out(p, ((size_t)i * g.nh + (size_t)kv * g.qpk + hq) * D + d, acc / fmaxf(l, 1.0e-30f));
         } else {
             const size_t part = (((size_t)i * g.nkv + kv) * p.max_chunks + chunk) * g.qpk + hq;
             p.ws_o[part * D + d] = acc;

@@ -6,6 +6,8 @@
 // a time, every lane issues 16-byte loads of W (row-contiguous, 512 bytes per warp instruction),
 // four k-steps are in flight per row, x sits in shared memory as fp16, products accumulate in fp32
 // and a shuffle tree finishes each row. Up to four batch columns share one pass over W.
+#include <cooperative_groups.h>
+
 #include "kivi_common.cuh"
 
 namespace kivi {
@@ -135,6 +137,239 @@ cudaError_t launch_gemv(const __half* w, const __half* x, __half* y16, float* y3
         if (e != cudaSuccess) return e;
     }
     return cudaSuccess;
+}
+
+}  // namespace kivi
+
+// ------------------------------------------------------------------------------------------------
+// Skinny GEMM for 5..64 batch columns: y[b, o] = sum_i W[o, i] x[b, i] on the tensor cores.
+//
+// The product is still weight-bandwidth bound (every W byte is used once per batch column), so the
+// kernel is a W streamer whose arithmetic happens to be MMAs. A CTA of four warps owns 128 output
+// rows (32 per warp, so each x fragment read from shared memory feeds two row tiles) and one slice
+// of the contraction; W tiles [128 x 64] and the matching x chunk [batch x 64] move through a
+// 3-stage cp.async pipeline, so the x chunk is fetched once per CTA, not once per warp. Tile rows
+// are 128 bytes with the two 64-byte halves swapped on odd rows, which makes both the 16-byte
+// cp.async stores and the 16-byte fragment loads bank-conflict free. Fragments: lane (r, t) takes
+// elements 8t..8t+7 of row r for both operands, which fixes the same permutation of the
+// contraction on W and x. With few row blocks the contraction is split over the CTAs of a thread-block
+// cluster (grid.y = cluster size <= 8): each CTA leaves its partial tile in its own shared memory,
+// and after a cluster barrier every CTA adds up one slice of the tile across its peers through
+// distributed shared memory and stores it. No workspace, no global round trip, a fixed summation
+// order.
+namespace kivi {
+namespace {
+
+constexpr int kSgRows = 128, kSgK = 64, kSgStages = 3, kSgThreads = 128, kSgCtasPerSm = 3;
+constexpr int kSgRowBytes = kSgK * 2;
+
+__device__ __forceinline__ uint32_t sg_offset(int row, int chunk) {
+    return (uint32_t)row * kSgRowBytes + (uint32_t)((chunk ^ ((row & 1) << 2)) << 4);
+}
+
+template <int NT>   // batch columns padded to 8 * NT
+__global__ void __launch_bounds__(kSgThreads, kSgCtasPerSm) skinny_gemm_kernel(
+    const __half* __restrict__ w, const __half* __restrict__ x, __half* __restrict__ y16, float* __restrict__ y32,
+    int out_dim, int in_dim, int batch, int chunks_per_split) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    constexpr int XROWS = 8 * NT;
+    constexpr int W_BYTES = kSgRows * kSgRowBytes, X_BYTES = XROWS * kSgRowBytes, STAGE = W_BYTES + X_BYTES;
+    const uint32_t s32 = smem_u32(smem);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, r = lane >> 2, t = lane & 3;
+    const int row0 = blockIdx.x * kSgRows;
+    const int total_chunks = in_dim / kSgK;
+    const int c0 = blockIdx.y * chunks_per_split;
+    const int c1 = min(total_chunks, c0 + chunks_per_split);
+    const int nchunks = c1 - c0;
+
+    // rows of x beyond the batch are zero in every stage (they are never overwritten)
+    for (int idx = threadIdx.x; idx < kSgStages * (XROWS - batch) * (kSgRowBytes / 4); idx += kSgThreads) {
+        const int st = idx / ((XROWS - batch) * (kSgRowBytes / 4));
+        const int rem = idx - st * ((XROWS - batch) * (kSgRowBytes / 4));
+        reinterpret_cast<uint32_t*>(smem + st * STAGE + W_BYTES + batch * kSgRowBytes)[rem] = 0u;
+    }
+
+    // each thread always copies the same (row, 16-byte column) positions of a tile
+    const int cp_row = threadIdx.x >> 3, cp_chunk = threadIdx.x & 7;   // rows cp_row + 16 k
+    const uint32_t cp_dst = sg_offset(cp_row, cp_chunk);               // row parity is that of cp_row
+    auto issue = [&](int c) {
+        const uint32_t st = s32 + (uint32_t)(c % kSgStages) * STAGE;
+        const size_t k0 = (size_t)(c0 + c) * kSgK;
+#pragma unroll
+        for (int k = 0; k < kSgRows / 16; ++k) {
+            const int row = min(row0 + cp_row + 16 * k, out_dim - 1);
+            cp_async16_32(st + cp_dst + (uint32_t)(16 * k) * kSgRowBytes, w + (size_t)row * in_dim + k0 + cp_chunk * 8);
+        }
+#pragma unroll
+        for (int k = 0; k < (XROWS + 15) / 16; ++k) {
+            const int row = cp_row + 16 * k;
+            if (row < batch)
+                cp_async16_32(st + W_BYTES + cp_dst + (uint32_t)(16 * k) * kSgRowBytes,
+                              x + (size_t)row * in_dim + k0 + cp_chunk * 8);
+        }
+    };
+    for (int c = 0; c < kSgStages - 1; ++c) {
+        if (c < nchunks) issue(c);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+
+    float acc[2][NT][4];
+#pragma unroll
+    for (int m = 0; m < 2; ++m)
+#pragma unroll
+        for (int j = 0; j < NT; ++j) acc[m][j][0] = acc[m][j][1] = acc[m][j][2] = acc[m][j][3] = 0.0f;
+
+    // fragment addresses inside a stage: the lane's 16 bytes of the low half; ^64 gives the high half
+    const uint32_t frag = (uint32_t)((t ^ ((r & 1) << 2)) << 4);
+    const uint32_t wa0 = (uint32_t)(warp * 32 + r) * kSgRowBytes + frag;
+    const uint32_t xa0 = W_BYTES + (uint32_t)r * kSgRowBytes + frag;
+
+    for (int c = 0; c < nchunks; ++c) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(kSgStages - 2) : "memory");
+        __syncthreads();   // chunk c has landed for every thread; the stage refilled below is no longer read
+        if (c + kSgStages - 1 < nchunks) issue(c + kSgStages - 1);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        const uint32_t st = s32 + (uint32_t)(c % kSgStages) * STAGE;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {   // 32 contraction elements per half: lane t holds 8t..8t+7
+            const uint32_t wa = (st + wa0) ^ (64u * half), xa = (st + xa0) ^ (64u * half);
+            uint4 a[2][2];
+#pragma unroll
+            for (int m = 0; m < 2; ++m) {
+                a[m][0] = lds128(wa + (uint32_t)(16 * m) * kSgRowBytes);
+                a[m][1] = lds128(wa + (uint32_t)(16 * m + 8) * kSgRowBytes);
+            }
+            uint4 b[NT];
+#pragma unroll
+            for (int j = 0; j < NT; ++j) b[j] = lds128(xa + (uint32_t)(8 * j) * kSgRowBytes);
+            // the two MMAs that update one accumulator are issued a whole sweep apart, so neither waits on the other
+#pragma unroll
+            for (int j = 0; j < NT; ++j)
+#pragma unroll
+                for (int m = 0; m < 2; ++m)
+                    mma16816(acc[m][j], a[m][0].x, a[m][1].x, a[m][0].y, a[m][1].y, b[j].x, b[j].y);
+#pragma unroll
+            for (int j = 0; j < NT; ++j)
+#pragma unroll
+                for (int m = 0; m < 2; ++m)
+                    mma16816(acc[m][j], a[m][0].z, a[m][1].z, a[m][0].w, a[m][1].w, b[j].z, b[j].w);
+        }
+    }
+
+    // acc[m][j] = rows (row0 + 32 warp + 16 m + r, +8) x batch columns (8j + 2t, +1)
+    const int splits = gridDim.y;
+    if (splits == 1) {
+#pragma unroll
+        for (int m = 0; m < 2; ++m)
+#pragma unroll
+            for (int j = 0; j < NT; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int row = row0 + warp * 32 + 16 * m + r + ((e & 2) ? 8 : 0), col = 8 * j + 2 * t + (e & 1);
+                    if (row < out_dim && col < batch) {
+                        if (y32) y32[(size_t)col * out_dim + row] = acc[m][j][e];
+                        if (y16) y16[(size_t)col * out_dim + row] = __float2half_rn(acc[m][j][e]);
+                    }
+                }
+        return;
+    }
+    // Partial tile of this split, [batch column][row] with a padded column stride, in the (now idle)
+    // pipeline buffers; the cluster then shares the reduction out by flat 4-float slices.
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    asm volatile("cp.async.wait_all;" ::: "memory");
+    __syncthreads();
+    constexpr int TS = kSgRows + 4;                       // floats per column: 16-byte aligned, conflict-free stores
+    float* tile = reinterpret_cast<float*>(smem);
+#pragma unroll
+    for (int m = 0; m < 2; ++m)
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                tile[(8 * j + 2 * t + (e & 1)) * TS + warp * 32 + 16 * m + r + ((e & 2) ? 8 : 0)] = acc[m][j][e];
+    cluster.sync();
+    const unsigned rank = cluster.block_rank();
+    const int quads = batch * (kSgRows / 4);              // 4 consecutive rows of one column
+    const int per = (quads + splits - 1) / splits;
+    const int lo = (int)rank * per, hi = min(quads, lo + per);
+    for (int u = lo + (int)threadIdx.x; u < hi; u += kSgThreads) {
+        const int col = u / (kSgRows / 4), rr = (u - col * (kSgRows / 4)) * 4;
+        float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (int peer = 0; peer < splits; ++peer) {
+            const float4 v = *reinterpret_cast<const float4*>(cluster.map_shared_rank(tile, peer) + col * TS + rr);
+            sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+        }
+        const float vals[4] = {sum.x, sum.y, sum.z, sum.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int row = row0 + rr + k;
+            if (row < out_dim) {
+                if (y32) y32[(size_t)col * out_dim + row] = vals[k];
+                if (y16) y16[(size_t)col * out_dim + row] = __float2half_rn(vals[k]);
+            }
+        }
+    }
+    cluster.sync();   // nobody leaves while a peer may still read its tile
+}
+
+struct SkinnyPlan { int row_blocks, splits, chunks_per_split, nt; };
+
+constexpr int kSgMaxSplits = 8;   // portable cluster size
+
+SkinnyPlan plan_skinny(int out_dim, int in_dim, int batch) {
+    SkinnyPlan p;
+    p.nt = (batch + 7) / 8;
+    p.row_blocks = (out_dim + kSgRows - 1) / kSgRows;
+    const int chunks = in_dim / kSgK;
+    int splits = kSgCtasPerSm * 148 / p.row_blocks;              // at most one wave of resident CTAs
+    const int max_splits = chunks / 8 > 0 ? chunks / 8 : 1;      // at least 8 chunks (512 elements) per CTA
+    if (splits > max_splits) splits = max_splits;
+    if (splits > kSgMaxSplits) splits = kSgMaxSplits;
+    if (splits < 1) splits = 1;
+    p.chunks_per_split = (chunks + splits - 1) / splits;
+    p.splits = splits;   // a trailing split may get fewer chunks, or none: it still joins the reduction
+    return p;
+}
+
+template <int NT>
+cudaError_t launch_skinny_nt(const __half* w, const __half* x, __half* y16, float* y32, int out_dim, int in_dim, int batch,
+                             const SkinnyPlan& p, cudaStream_t stream) {
+    const int smem = kSgStages * (kSgRows + 8 * NT) * kSgRowBytes;
+    cudaError_t e = cudaFuncSetAttribute(skinny_gemm_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.row_blocks, p.splits, 1);
+    cfg.blockDim = dim3(kSgThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = p.splits;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, skinny_gemm_kernel<NT>, w, x, y16, y32, out_dim, in_dim, batch, p.chunks_per_split);
+}
+
+}  // namespace
+
+bool skinny_gemm_supports(int in_dim, int batch) { return batch > 4 && batch <= 64 && in_dim % kSgK == 0; }
+
+cudaError_t launch_skinny_gemm(const __half* w, const __half* x, __half* y16, float* y32, int out_dim, int in_dim,
+                               int batch, cudaStream_t stream) {
+    const SkinnyPlan p = plan_skinny(out_dim, in_dim, batch);
+    switch (p.nt) {
+        case 1: return launch_skinny_nt<1>(w, x, y16, y32, out_dim, in_dim, batch, p, stream);
+        case 2: return launch_skinny_nt<2>(w, x, y16, y32, out_dim, in_dim, batch, p, stream);
+        case 3: return launch_skinny_nt<3>(w, x, y16, y32, out_dim, in_dim, batch, p, stream);
+        case 4: return launch_skinny_nt<4>(w, x, y16, y32, out_dim, in_dim, batch, p, stream);
+        case 5: return launch_skinny_nt<5>(w, x, y16, y32, out_dim, in_dim, batch, p, stream);
+        case 6: return launch_skinny_nt<6>(w, x, y16, y32, out_dim, in_dim, batch, p, stream);
+        case 7: return launch_skinny_nt<7>(w, x, y16, y32, out_dim, in_dim, batch, p, stream);
+        default: return launch_skinny_nt<8>(w, x, y16, y32, out_dim, in_dim, batch, p, stream);
+    }
 }
 
 }  // namespace kivi

@@ -96,6 +96,7 @@ struct DecodeParams {
     SeqAddressing seq;
     const __half* q;      // [n, NH, D]
     float* out;           // [n, NH, D]
+    __half* out_h;        // when set, the result is written here as fp16 instead of `out`
     int n;                // queries (sequences) in this launch
     int max_seq;          // longest sequence the launch is planned for (reference: LQ + RESIDUAL), or -1
     int retained_pages;   // sparse-retained: pages to scan from the compact table, else -1
@@ -108,6 +109,11 @@ struct DecodeParams {
     unsigned int* ws_count;  // [n, NKV] arrival counters, zero between launches
     int* status;          // device status word (0 = ok), may be nullptr
 };
+
+__device__ __forceinline__ void store_out(const DecodeParams& p, size_t idx, float v) {
+    if (p.out_h) p.out_h[idx] = __float2half(v);
+    else p.out[idx] = v;
+}
 
 // Writer launch parameters.
 struct WriteParams {
@@ -265,10 +271,19 @@ __device__ __forceinline__ float fast_exp2(float x) {
 
 // Host-side launchers implemented in the .cu files.
 cudaError_t launch_cache_write(const WriteParams& p, int max_new_per_seq, cudaStream_t stream);
+// Plans the split over the context, binds the workspace and launches the decode kernel; returns a
+// kivi_status. `out_h` (fp16) replaces `out` (fp32) when non-null.
+int run_decode(const Geom& g, const CachePtrs& cache, const SeqAddressing& seq, const __half* q, float* out,
+               __half* out_h, int n, int max_seq_cap, int max_old_tokens, int retained_pages, void* ws,
+               size_t ws_bytes, cudaStream_t stream);
+size_t decode_workspace_total(const Geom& g, int n, int max_old_tokens);
 cudaError_t launch_decode_generic(const DecodeParams& p, cudaStream_t stream);
 cudaError_t launch_decode_mma(const DecodeParams& p, cudaStream_t stream);
 bool decode_mma_supports(const Geom& g, int retained_pages);
 cudaError_t launch_gemv(const __half* w, const __half* x, __half* y16, float* y32, int out_dim, int in_dim,
                         int batch, cudaStream_t stream);
+bool skinny_gemm_supports(int in_dim, int batch);
+cudaError_t launch_skinny_gemm(const __half* w, const __half* x, __half* y16, float* y32, int out_dim, int in_dim,
+                               int batch, cudaStream_t stream);
 
 }  // namespace kivi

@@ -1,0 +1,490 @@
+// Decode step of the generated runtime around the KIVI cache: the element-wise kernels between
+// the projections and the host loop that strings one step together.
+//
+// Reference: forward() in crates/jac-codegen-cuda/src/templates/runtime.cu:125-187 and its kernels
+// in templates/kernels.cu. The reference runs one token per step with <<<1,256>>>-style launches;
+// here a step carries `batch` sequences, every kernel takes one row per sequence, the residual add
+// is fused into the RMSNorm that follows it, bias add and the q/k/v split into RoPE, and the fp16
+// KV store plus three attention kernels are replaced by the int4-KIVI writer and paged decode.
+//
+// The arithmetic of each element keeps the reference's expression and order, so the results are
+// bit-identical to the reference kernels on the same GPU (RoPE: up to a handful of elements per
+// ten thousand one fp16 ulp away at positions in the thousands, where the reference's compile-time
+// ROPE_BASE lets the compiler fold part of powf):
+//   RMSNorm   thread t of 256 sums elements t, t+256, ...; xor-shuffle tree; warp totals added in
+//             order; scale = rsqrtf(sum / n + eps); out = (x * scale) * w        (kernels.cu:10-33)
+//   RoPE      freq = 1 / powf(base, (2 i) / HD); ang = pos * freq; rotate pair (i, i + HD/2)
+//                                                                                (kernels.cu:40-54)
+//   SiLU*up   g / (1 + expf(-g)) * up                                            (kernels.cu:146-153)
+//   add, bias fp16 __hadd                                                        (kernels.cu:156-166)
+#include "kivi_common.cuh"
+
+namespace kivi {
+namespace {
+
+constexpr int kNormThreads = 256;   // the reduction order of the reference depends on this value
+
+// x_out = x (+ delta); normed = RMSNorm(x_out) * weight. One CTA per row. `tokens` (optional)
+// makes row i of x the embedding row tokens[i] (kernels.cu:4-7).
+__global__ void __launch_bounds__(kNormThreads) residual_rmsnorm_kernel(
+    const __half* __restrict__ x, const int* __restrict__ tokens, const __half* __restrict__ delta,
+    const __half* __restrict__ weight, __half* __restrict__ x_out, __half* __restrict__ normed, int hidden, float eps) {
+    extern __shared__ __align__(16) unsigned char step_smem[];
+    __half* row = reinterpret_cast<__half*>(step_smem);
+    __shared__ float warp_sums[32];
+    const int tid = threadIdx.x;
+    const size_t src_row = tokens ? (size_t)tokens[blockIdx.x] : (size_t)blockIdx.x;
+    const uint4* xs = reinterpret_cast<const uint4*>(x + src_row * hidden);
+    const uint4* ds = delta ? reinterpret_cast<const uint4*>(delta + (size_t)blockIdx.x * hidden) : nullptr;
+    uint4* xo = x_out ? reinterpret_cast<uint4*>(x_out + (size_t)blockIdx.x * hidden) : nullptr;
+    const int vecs = hidden >> 3;
+    for (int v = tid; v < vecs; v += kNormThreads) {
+        uint4 a = xs[v];
+        if (ds) {
+            const uint4 d = ds[v];
+            __half2* ah = reinterpret_cast<__half2*>(&a);
+            const __half2* dh = reinterpret_cast<const __half2*>(&d);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) ah[k] = __hadd2(ah[k], dh[k]);
+        }
+        if (xo) xo[v] = a;
+        reinterpret_cast<uint4*>(row)[v] = a;
+    }
+    __syncthreads();
+    float local = 0.0f;
+    for (int i = tid; i < hidden; i += kNormThreads) {
+        const float v = __half2float(row[i]);
+        local += v * v;
+    }
+    for (int off = 16; off > 0; off >>= 1) local += __shfl_xor_sync(0xffffffffu, local, off);
+    if ((tid & 31) == 0) warp_sums[tid >> 5] = local;
+    __syncthreads();
+    if (tid == 0) {
+        float total = 0.0f;
+        for (int w = 0; w < kNormThreads / 32; ++w) total += warp_sums[w];
+        warp_sums[0] = total;
+    }
+    __syncthreads();
+    const float scale = rsqrtf(warp_sums[0] / hidden + eps);
+    uint4* no = reinterpret_cast<uint4*>(normed + (size_t)blockIdx.x * hidden);
+    const uint4* wv = reinterpret_cast<const uint4*>(weight);
+    for (int v = tid; v < vecs; v += kNormThreads) {
+        const uint4 a = reinterpret_cast<const uint4*>(row)[v];
+        const uint4 w = wv[v];
+        const __half* ah = reinterpret_cast<const __half*>(&a);
+        const __half* wh = reinterpret_cast<const __half*>(&w);
+        uint4 o;
+        __half* oh = reinterpret_cast<__half*>(&o);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) oh[k] = __float2half(__half2float(ah[k]) * scale * __half2float(wh[k]));
+        no[v] = o;
+    }
+}
+
+// qkv row [q heads | k heads | v heads] (+ bias) -> q and k rotated at positions[row], v copied.
+// Thread (i, lane group) owns pair index i of every head it visits, so the angle is computed once
+// per (row, i) and not once per head.
+__global__ void __launch_bounds__(256) bias_rope_kernel(
+    const __half* __restrict__ qkv, const __half* __restrict__ bias, const int* __restrict__ positions,
+    __half* __restrict__ q, __half* __restrict__ k, __half* __restrict__ v, int nh, int nkv, int hd, float rope_base) {
+    const int rowi = blockIdx.x;
+    const int half_dim = hd >> 1;
+    const int qkv_out = (nh + 2 * nkv) * hd;
+    const __half* in = qkv + (size_t)rowi * qkv_out;
+    const int pos = positions[rowi];
+    const int groups = blockDim.x / half_dim;            // head lanes working in parallel
+    const int i = threadIdx.x % half_dim, grp = threadIdx.x / half_dim;
+    if (grp < groups) {
+        const float freq = 1.0f / powf(rope_base, (2.0f * i) / hd);
+        const float ang = pos * freq;
+        const float c = cosf(ang), s = sinf(ang);
+        for (int h = grp; h < nh + nkv; h += groups) {
+            const int base = h * hd;
+            __half h0 = in[base + i], h1 = in[base + i + half_dim];
+            if (bias) { h0 = __hadd(h0, bias[base + i]); h1 = __hadd(h1, bias[base + i + half_dim]); }
+            const float x0 = __half2float(h0), x1 = __half2float(h1);
+            __half* out = h < nh ? q + ((size_t)rowi * nh + h) * hd : k + ((size_t)rowi * nkv + (h - nh)) * hd;
+            out[i] = __float2half(x0 * c - x1 * s);
+            out[i + half_dim] = __float2half(x1 * c + x0 * s);
+        }
+    }
+    const int voff = (nh + nkv) * hd;
+    for (int e = threadIdx.x; e < nkv * hd; e += blockDim.x) {
+        __half val = in[voff + e];
+        if (bias) val = __hadd(val, bias[voff + e]);
+        v[(size_t)rowi * nkv * hd + e] = val;
+    }
+}
+
+// out[row, i] = SiLU(gate_up[row, i]) * gate_up[row, ffn + i]; eight elements per thread.
+__global__ void __launch_bounds__(256) silu_mul_kernel(const __half* __restrict__ gate_up, __half* __restrict__ out,
+                                                        int ffn) {
+    const int rowi = blockIdx.y;
+    const int v = blockIdx.x * blockDim.x + threadIdx.x;
+    if (v >= (ffn >> 3)) return;
+    const uint4 g = reinterpret_cast<const uint4*>(gate_up + (size_t)rowi * 2 * ffn)[v];
+    const uint4 u = reinterpret_cast<const uint4*>(gate_up + (size_t)rowi * 2 * ffn + ffn)[v];
+    const __half* gh = reinterpret_cast<const __half*>(&g);
+    const __half* uh = reinterpret_cast<const __half*>(&u);
+    uint4 o;
+    __half* oh = reinterpret_cast<__half*>(&o);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const float gv = __half2float(gh[k]);
+        const float sv = gv / (1.0f + expf(-gv));
+        oh[k] = __float2half(sv * __half2float(uh[k]));
+    }
+    reinterpret_cast<uint4*>(out + (size_t)rowi * ffn)[v] = o;
+}
+
+// Arg-max, first pass: block (chunk, row) scans its slice of the row. A candidate is (value, index);
+// the larger value wins, the lower index on a tie, and nothing at or below -1e30 (or NaN) beats the
+// initial (-1e30, 0) of kernels.cu:208-209.
+constexpr int kArgmaxThreads = 256;
+constexpr int kArgmaxChunk = 8192;
+
+__device__ __forceinline__ bool better(float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); }
+
+__global__ void __launch_bounds__(kArgmaxThreads) argmax_partial_kernel(
+    const __half* __restrict__ logits, int n, int index_offset, float* __restrict__ part_val, int* __restrict__ part_idx) {
+    __shared__ float s_val[kArgmaxThreads / 32];
+    __shared__ int s_idx[kArgmaxThreads / 32];
+    const int rowi = blockIdx.y;
+    const __half* in = logits + (size_t)rowi * n;
+    const int lo = blockIdx.x * kArgmaxChunk, hi = min(n, lo + kArgmaxChunk);
+    float best = -1e30f;
+    int best_i = 0;
+    for (int i = lo + threadIdx.x; i < hi; i += kArgmaxThreads) {
+        const float v = __half2float(in[i]);
+        if (v > best) { best = v; best_i = i; }
+    }
+    for (int off = 16; off > 0; off >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, off);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_i, off);
+        if (better(ov, oi, best, best_i)) { best = ov; best_i = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { s_val[threadIdx.x >> 5] = best; s_idx[threadIdx.x >> 5] = best_i; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < kArgmaxThreads / 32; ++w)
+            if (better(s_val[w], s_idx[w], best, best_i)) { best = s_val[w]; best_i = s_idx[w]; }
+        part_val[(size_t)rowi * gridDim.x + blockIdx.x] = best;
+        // a slice with no candidate above the floor reports global index 0, like the reference
+        part_idx[(size_t)rowi * gridDim.x + blockIdx.x] = best > -1e30f ? best_i + index_offset : 0;
+    }
+}
+
+// Second pass: one warp per row over `parts` candidates laid out [rank][row][chunk]
+// (rank stride = rows * chunks); the winner goes to out[row].
+__global__ void argmax_merge_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx, int chunks,
+                                    int ranks, int rows, int* __restrict__ out) {
+    const int rowi = blockIdx.x;
+    float best = -1e30f;
+    int best_i = 0;
+    const int total = chunks * ranks;
+    for (int e = threadIdx.x; e < total; e += 32) {
+        const int rk = e / chunks, ch = e - rk * chunks;
+        const size_t at = ((size_t)rk * rows + rowi) * chunks + ch;
+        const float v = part_val[at];
+        const int i = part_idx[at];
+        if (better(v, i, best, best_i)) { best = v; best_i = i; }
+    }
+    for (int off = 16; off > 0; off >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, off);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_i, off);
+        if (better(ov, oi, best, best_i)) { best = ov; best_i = oi; }
+    }
+    if (threadIdx.x == 0) out[rowi] = best_i;
+}
+
+// Bookkeeping of a step: the decode sees the lengths after the append, the writer those before it.
+__global__ void step_begin_kernel(const int* __restrict__ seq_lens, int* __restrict__ lens_after, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) lens_after[i] = seq_lens[i] + 1;
+}
+__global__ void step_end_kernel(int* __restrict__ seq_lens, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) seq_lens[i] += 1;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+const __half* H(const kivi_f16* p) { return reinterpret_cast<const __half*>(p); }
+__half* H(kivi_f16* p) { return reinterpret_cast<__half*>(p); }
+
+int ok(cudaError_t e) { return e == cudaSuccess ? KIVI_OK : KIVI_ERR_CUDA; }
+
+int launch_residual_rmsnorm(const __half* x, const int* tokens, const __half* delta, const __half* weight,
+                            __half* x_out, __half* normed, int batch, int hidden, float eps, cudaStream_t stream) {
+    const size_t smem = (size_t)hidden * sizeof(__half);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(residual_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return KIVI_ERR_CUDA;
+    }
+    residual_rmsnorm_kernel<<<batch, kNormThreads, smem, stream>>>(x, tokens, delta, weight, x_out, normed, hidden, eps);
+    return ok(cudaGetLastError());
+}
+
+int launch_bias_rope(const __half* qkv, const __half* bias, const int* positions, __half* q, __half* k, __half* v,
+                     int batch, int nh, int nkv, int hd, float rope_base, cudaStream_t stream) {
+    bias_rope_kernel<<<batch, 256, 0, stream>>>(qkv, bias, positions, q, k, v, nh, nkv, hd, rope_base);
+    return ok(cudaGetLastError());
+}
+
+int launch_silu_mul(const __half* gate_up, __half* out, int batch, int ffn, cudaStream_t stream) {
+    silu_mul_kernel<<<dim3(((ffn >> 3) + 255) / 256, batch), 256, 0, stream>>>(gate_up, out, ffn);
+    return ok(cudaGetLastError());
+}
+
+int argmax_chunks(int n) { return (n + kArgmaxChunk - 1) / kArgmaxChunk; }
+
+// Projection y[b, :] = W x[b, :].
+int project(const __half* w, const __half* x, __half* y, int out_dim, int in_dim, int batch, cudaStream_t stream) {
+    if (skinny_gemm_supports(in_dim, batch))
+        return ok(launch_skinny_gemm(w, x, y, nullptr, out_dim, in_dim, batch, stream));
+    return ok(launch_gemv(w, x, y, nullptr, out_dim, in_dim, batch, stream));
+}
+
+size_t up256(size_t v) { return (v + 255) / 256 * 256; }
+
+struct StepLayout {
+    size_t x0, x1, normed, qkv, q, k, v, attn, proj, gate_up, mid, logits, lens_after, part_val, part_idx,
+        gather_val, gather_idx, decode_ws, total;
+    size_t decode_ws_bytes;
+};
+
+int qkv_rows(const kivi_step_config& c) { return (c.num_q_heads + 2 * c.num_kv_heads) * c.head_dim; }
+
+StepLayout step_layout(const kivi_step_config& c, const Geom& g, int batch, int max_seq_len) {
+    StepLayout L;
+    size_t at = 0;
+    auto take = [&](size_t bytes) { const size_t o = at; at += up256(bytes); return o; };
+    const size_t n = (size_t)batch, h2 = sizeof(__half);
+    const int tp = c.tp_size > 1 ? c.tp_size : 1;
+    // zero-initialised region first (arrival counters of the split decode)
+    L.decode_ws_bytes = decode_workspace_total(g, batch, split_old(max_seq_len, g.r, g.g));
+    L.decode_ws = take(L.decode_ws_bytes);
+    L.x0 = take(n * c.hidden * h2);
+    L.x1 = take(n * c.hidden * h2);
+    L.normed = take(n * c.hidden * h2);
+    L.qkv = take(n * qkv_rows(c) * h2);
+    L.q = take(n * c.num_q_heads * c.head_dim * h2);
+    L.k = take(n * c.num_kv_heads * c.head_dim * h2);
+    L.v = take(n * c.num_kv_heads * c.head_dim * h2);
+    L.attn = take(n * c.num_q_heads * c.head_dim * h2);
+    L.proj = take(n * c.hidden * h2);
+    L.gate_up = take(n * 2 * c.ffn * h2);
+    L.mid = take(n * c.ffn * h2);
+    L.logits = take(n * c.vocab * h2);
+    L.lens_after = take(n * sizeof(int));
+    const size_t parts = n * argmax_chunks(c.vocab);
+    L.part_val = take(parts * sizeof(float));
+    L.part_idx = take(parts * sizeof(int));
+    L.gather_val = take(parts * tp * sizeof(float));
+    L.gather_idx = take(parts * tp * sizeof(int));
+    L.total = at;
+    return L;
+}
+
+int check_step_config(const kivi_step_config* c) {
+    if (!c) return KIVI_ERR_NULL_POINTER;
+    if (c->layers <= 0 || c->hidden <= 0 || c->num_q_heads <= 0 || c->num_kv_heads <= 0 || c->head_dim <= 0 ||
+        c->ffn <= 0 || c->vocab <= 0 || c->vocab_offset < 0)
+        return KIVI_ERR_GEOMETRY;
+    if (c->hidden % 8 || c->ffn % 8 || c->head_dim % 8) return KIVI_ERR_GEOMETRY;   // 16-byte rows everywhere
+    if (c->num_q_heads % c->num_kv_heads) return KIVI_ERR_GEOMETRY;
+    if (c->head_dim / 2 > 256) return KIVI_ERR_GEOMETRY;
+    if (c->tp_size < 1 || c->tp_rank < 0 || c->tp_rank >= c->tp_size) return KIVI_ERR_GEOMETRY;
+    if (!(c->rope_base > 0.0f) || !(c->norm_eps >= 0.0f)) return KIVI_ERR_GEOMETRY;
+    return KIVI_OK;
+}
+
+kivi_geometry step_geometry(const kivi_step_config& c) {
+    kivi_geometry s = {c.num_q_heads, c.num_kv_heads, c.head_dim, c.block_size, c.group_size, c.residual};
+    return s;
+}
+
+CachePtrs to_ptrs(const kivi_cache& c) {
+    CachePtrs o;
+    o.k_code = c.k_code_pages;
+    o.k_scale = reinterpret_cast<__half*>(c.k_scale_pages);
+    o.k_zero = reinterpret_cast<__half*>(c.k_zero_pages);
+    o.v_code = c.v_code_pages;
+    o.v_scale = reinterpret_cast<__half*>(c.v_scale_pages);
+    o.v_zero = reinterpret_cast<__half*>(c.v_zero_pages);
+    o.k_scratch = reinterpret_cast<__half*>(c.k_residual_scratch);
+    o.v_scratch = reinterpret_cast<__half*>(c.v_residual_scratch);
+    return o;
+}
+
+}  // namespace
+}  // namespace kivi
+
+using namespace kivi;
+
+extern "C" size_t kivi_b200_decode_step_workspace_bytes(const kivi_step_config* cfg, int batch, int max_seq_len) {
+    if (check_step_config(cfg) != KIVI_OK || batch <= 0 || batch > 64 || max_seq_len < 1) return 0;
+    kivi_geometry gs = step_geometry(*cfg);
+    if (kivi_b200_validate_geometry(&gs, nullptr) != KIVI_OK) return 0;
+    return step_layout(*cfg, make_geom(gs), batch, max_seq_len).total;
+}
+
+extern "C" int kivi_b200_decode_step(const kivi_step_config* cfg, const kivi_step_weights* weights,
+                                     const kivi_step_state* state, const int32_t* tokens_in, int batch, int max_seq_len,
+                                     int32_t* tokens_out, kivi_f16* logits_out, const kivi_step_comm* comm,
+                                     cudaStream_t stream) {
+    int rc = check_step_config(cfg);
+    if (rc != KIVI_OK) return rc;
+    if (!weights || !state || !tokens_in || !tokens_out) return KIVI_ERR_NULL_POINTER;
+    if (!weights->embed || !weights->final_norm || !weights->lm_head || !weights->layers) return KIVI_ERR_NULL_POINTER;
+    if (!state->caches || !state->block_tables || !state->seq_lens) return KIVI_ERR_NULL_POINTER;
+    if (batch < 1 || batch > 64 || max_seq_len < 1 || max_seq_len > 0x3fffffff) return KIVI_ERR_RANGE;
+    const kivi_step_config& c = *cfg;
+    const bool tp = c.tp_size > 1;
+    if (tp && (!comm || !comm->allreduce_f16 || !comm->allgather)) return KIVI_ERR_NULL_POINTER;
+    kivi_geometry gs = step_geometry(c);
+    rc = kivi_b200_validate_geometry(&gs, nullptr);
+    if (rc != KIVI_OK) return rc;
+    const Geom g = make_geom(gs);
+    if ((long long)split_old(max_seq_len, g.r, g.g) > (long long)state->max_blocks_per_seq * g.b)
+        return KIVI_ERR_BLOCK_TABLE;
+    const StepLayout L = step_layout(c, g, batch, max_seq_len);
+    if (!state->workspace || state->workspace_bytes < L.total) return KIVI_ERR_WORKSPACE;
+    if (!aligned16(state->workspace)) return KIVI_ERR_ALIGNMENT;
+    for (int l = 0; l < c.layers; ++l) {
+        const kivi_layer_weights& lw = weights->layers[l];
+        if (!lw.attn_norm || !lw.qkv || !lw.o || !lw.ffn_norm || !lw.gate_up || !lw.down) return KIVI_ERR_NULL_POINTER;
+        if (c.attn_bias && !lw.qkv_bias) return KIVI_ERR_NULL_POINTER;
+        if (!state->caches[l].k_code_pages || !state->caches[l].k_residual_scratch) return KIVI_ERR_NULL_POINTER;
+        if (!state->slot_ids && batch > state->caches[l].num_slots) return KIVI_ERR_RANGE;
+    }
+
+    unsigned char* ws = static_cast<unsigned char*>(state->workspace);
+    auto hp = [&](size_t off) { return reinterpret_cast<__half*>(ws + off); };
+    __half *x_cur = hp(L.x0), *x_nxt = hp(L.x1);
+    __half *normed = hp(L.normed), *qkv = hp(L.qkv), *q = hp(L.q), *k = hp(L.k), *v = hp(L.v), *attn = hp(L.attn);
+    __half *proj = hp(L.proj), *gate_up = hp(L.gate_up), *mid = hp(L.mid);
+    __half* logits = logits_out ? H(logits_out) : hp(L.logits);
+    int* lens_after = reinterpret_cast<int*>(ws + L.lens_after);
+    void* decode_ws = L.decode_ws_bytes ? ws + L.decode_ws : nullptr;
+    const int q_dim = c.num_q_heads * c.head_dim;
+    const int max_old = split_old(max_seq_len, g.r, g.g);
+
+#define KIVI_STEP_TRY(expr) do { const int rc__ = (expr); if (rc__ != KIVI_OK) return rc__; } while (0)
+
+    step_begin_kernel<<<(batch + 127) / 128, 128, 0, stream>>>(state->seq_lens, lens_after, batch);
+    KIVI_STEP_TRY(ok(cudaGetLastError()));
+
+    SeqAddressing wa;   // writer: lengths before the append
+    wa.seq_lens = state->seq_lens; wa.seq_len_scalar = 0;
+    wa.block_tables = state->block_tables; wa.bt_stride = state->max_blocks_per_seq; wa.bt_width = state->max_blocks_per_seq;
+    wa.slot_ids = state->slot_ids; wa.slot_shared = 0;
+    SeqAddressing da = wa;   // decode: lengths after it
+    da.seq_lens = lens_after;
+
+    const __half* delta = nullptr;           // projection waiting to be added to the residual stream
+    const int* embed_tokens = tokens_in;     // layer 0 reads its rows from the embedding table
+    for (int l = 0; l < c.layers; ++l) {
+        const kivi_layer_weights& lw = weights->layers[l];
+        // attention block
+        KIVI_STEP_TRY(launch_residual_rmsnorm(embed_tokens ? H(weights->embed) : x_cur, embed_tokens, delta, H(lw.attn_norm),
+                                              x_nxt, normed, batch, c.hidden, c.norm_eps, stream));
+        embed_tokens = nullptr;
+        { __half* t = x_cur; x_cur = x_nxt; x_nxt = t; }
+        KIVI_STEP_TRY(project(H(lw.qkv), normed, qkv, qkv_rows(c), c.hidden, batch, stream));
+        KIVI_STEP_TRY(launch_bias_rope(qkv, c.attn_bias ? H(lw.qkv_bias) : nullptr, state->seq_lens, q, k, v, batch,
+                                       c.num_q_heads, c.num_kv_heads, c.head_dim, c.rope_base, stream));
+        WriteParams wp;
+        wp.geom = g; wp.cache = to_ptrs(state->caches[l]); wp.seq = wa;
+        wp.new_k = k; wp.new_v = v; wp.new_offsets = nullptr; wp.num_new_scalar = 1; wp.n = batch;   // row i = sequence i
+        KIVI_STEP_TRY(ok(launch_cache_write(wp, 1, stream)));
+        KIVI_STEP_TRY(run_decode(g, wp.cache, da, q, nullptr, attn, batch, max_seq_len, max_old, -1, decode_ws,
+                                 L.decode_ws_bytes, stream));
+        KIVI_STEP_TRY(project(H(lw.o), attn, proj, c.hidden, q_dim, batch, stream));
+        if (tp && comm->allreduce_f16(comm->user, reinterpret_cast<kivi_f16*>(proj), (size_t)batch * c.hidden, stream))
+            return KIVI_ERR_CUDA;
+        // feed-forward block
+        KIVI_STEP_TRY(launch_residual_rmsnorm(x_cur, nullptr, proj, H(lw.ffn_norm), x_nxt, normed, batch, c.hidden,
+                                              c.norm_eps, stream));
+        { __half* t = x_cur; x_cur = x_nxt; x_nxt = t; }
+        KIVI_STEP_TRY(project(H(lw.gate_up), normed, gate_up, 2 * c.ffn, c.hidden, batch, stream));
+        KIVI_STEP_TRY(launch_silu_mul(gate_up, mid, batch, c.ffn, stream));
+        KIVI_STEP_TRY(project(H(lw.down), mid, proj, c.hidden, c.ffn, batch, stream));
+        if (tp && comm->allreduce_f16(comm->user, reinterpret_cast<kivi_f16*>(proj), (size_t)batch * c.hidden, stream))
+            return KIVI_ERR_CUDA;
+        delta = proj;
+    }
+    KIVI_STEP_TRY(launch_residual_rmsnorm(x_cur, nullptr, delta, H(weights->final_norm), x_nxt, normed, batch, c.hidden,
+                                          c.norm_eps, stream));
+    KIVI_STEP_TRY(project(H(weights->lm_head), normed, logits, c.vocab, c.hidden, batch, stream));
+
+    const int chunks = argmax_chunks(c.vocab);
+    float* part_val = reinterpret_cast<float*>(ws + L.part_val);
+    int* part_idx = reinterpret_cast<int*>(ws + L.part_idx);
+    argmax_partial_kernel<<<dim3(chunks, batch), kArgmaxThreads, 0, stream>>>(logits, c.vocab, c.vocab_offset, part_val,
+                                                                             part_idx);
+    KIVI_STEP_TRY(ok(cudaGetLastError()));
+    const float* all_val = part_val;
+    const int* all_idx = part_idx;
+    if (tp) {
+        float* gv = reinterpret_cast<float*>(ws + L.gather_val);
+        int* gi = reinterpret_cast<int*>(ws + L.gather_idx);
+        const size_t per_rank = (size_t)batch * chunks;
+        if (comm->allgather(comm->user, part_val, gv, per_rank * sizeof(float), stream)) return KIVI_ERR_CUDA;
+        if (comm->allgather(comm->user, part_idx, gi, per_rank * sizeof(int), stream)) return KIVI_ERR_CUDA;
+        all_val = gv;
+        all_idx = gi;
+    }
+    argmax_merge_kernel<<<batch, 32, 0, stream>>>(all_val, all_idx, chunks, tp ? c.tp_size : 1, batch, tokens_out);
+    KIVI_STEP_TRY(ok(cudaGetLastError()));
+    step_end_kernel<<<(batch + 127) / 128, 128, 0, stream>>>(state->seq_lens, batch);
+    return ok(cudaGetLastError());
+#undef KIVI_STEP_TRY
+}
+
+extern "C" int kivi_b200_residual_rmsnorm(const kivi_f16* x, const kivi_f16* delta, const kivi_f16* weight,
+                                          kivi_f16* x_out, kivi_f16* normed, int batch, int hidden, float eps,
+                                          cudaStream_t stream) {
+    if (!x || !weight || !normed) return KIVI_ERR_NULL_POINTER;
+    if (batch < 0 || hidden <= 0 || hidden % 8 || (size_t)hidden * 2 > 200 * 1024) return KIVI_ERR_RANGE;
+    if (!aligned16(x) || !aligned16(weight) || !aligned16(normed) || (delta && !aligned16(delta)) ||
+        (x_out && !aligned16(x_out)))
+        return KIVI_ERR_ALIGNMENT;
+    if (batch == 0) return KIVI_OK;
+    return launch_residual_rmsnorm(H(x), nullptr, delta ? H(delta) : nullptr, H(weight), x_out ? H(x_out) : nullptr,
+                                   H(normed), batch, hidden, eps, stream);
+}
+
+extern "C" int kivi_b200_bias_rope(const kivi_f16* qkv, const kivi_f16* bias, const int32_t* positions, kivi_f16* q,
+                                   kivi_f16* k, kivi_f16* v, int batch, int num_q_heads, int num_kv_heads, int head_dim,
+                                   float rope_base, cudaStream_t stream) {
+    if (!qkv || !positions || !q || !k || !v) return KIVI_ERR_NULL_POINTER;
+    if (batch < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || head_dim <= 0 || head_dim % 2 || head_dim / 2 > 256)
+        return KIVI_ERR_RANGE;
+    if (batch == 0) return KIVI_OK;
+    return launch_bias_rope(H(qkv), bias ? H(bias) : nullptr, positions, H(q), H(k), H(v), batch, num_q_heads,
+                            num_kv_heads, head_dim, rope_base, stream);
+}
+
+extern "C" int kivi_b200_silu_mul(const kivi_f16* gate_up, kivi_f16* out, int batch, int ffn, cudaStream_t stream) {
+    if (!gate_up || !out) return KIVI_ERR_NULL_POINTER;
+    if (batch < 0 || ffn <= 0 || ffn % 8) return KIVI_ERR_RANGE;
+    if (!aligned16(gate_up) || !aligned16(out)) return KIVI_ERR_ALIGNMENT;
+    if (batch == 0) return KIVI_OK;
+    return launch_silu_mul(H(gate_up), H(out), batch, ffn, stream);
+}
+
+extern "C" int kivi_b200_argmax(const kivi_f16* logits, int32_t* out_index, int batch, int n, void* workspace,
+                                size_t workspace_bytes, cudaStream_t stream) {
+    if (!logits || !out_index) return KIVI_ERR_NULL_POINTER;
+    if (batch < 0 || n <= 0) return KIVI_ERR_RANGE;
+    if (batch == 0) return KIVI_OK;
+    const int chunks = argmax_chunks(n);
+    const size_t need = (size_t)batch * chunks * (sizeof(float) + sizeof(int));
+    if (!workspace || workspace_bytes < need) return KIVI_ERR_WORKSPACE;
+    float* pv = static_cast<float*>(workspace);
+    int* pi = reinterpret_cast<int*>(pv + (size_t)batch * chunks);
+    argmax_partial_kernel<<<dim3(chunks, batch), kArgmaxThreads, 0, stream>>>(H(logits), n, 0, pv, pi);
+    if (cudaGetLastError() != cudaSuccess) return KIVI_ERR_CUDA;
+    argmax_merge_kernel<<<batch, 32, 0, stream>>>(pv, pi, chunks, 1, batch, out_index);
+    return ok(cudaGetLastError());
+}

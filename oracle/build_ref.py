@@ -3,7 +3,8 @@
 TEST INFRASTRUCTURE ONLY. The reference sources are compiled from where they lie in the reference
 checkout; nothing of them is copied into this repository. Outputs (a generated ``.cu`` dumped from
 the reference's Python string, text-substituted TP=2 clones made exactly as the reference's own
-``dsl_decode._materialize_tp2_local_variant`` makes them, and the shared library) go to
+``dsl_decode._materialize_tp2_local_variant`` makes them, and the shared library, which also holds
+the generated-runtime templates ``kernels.cu`` / ``runtime.cu`` behind ``ref_runtime_shim.cu``) go to
 ``oracle/_ref/`` only, which is git-ignored.
 
 Usage: ``python oracle/build_ref.py [--reference /path/to/jacq]``; without a reference checkout it
@@ -21,6 +22,7 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 OUT = HERE / "_ref"
 SNAP = "crates/jac-codegen-cuda/tests/snapshots/kernels"
+TEMPLATES = "crates/jac-codegen-cuda/src/templates"
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 
@@ -72,9 +74,11 @@ def build(reference: Path) -> Path | None:
         clone.write_text(_tp2_clone(path.read_text(), kind))
         sources.append(str(clone))
     sources.append(str(HERE / "ref_writer_shim.cu"))
+    sources.append(str(HERE / "ref_runtime_shim.cu"))   # includes the runtime templates from the checkout
     lib = OUT / "libjacq_ref.so"
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-    cmd = [nvcc, "-O3", *ARCH, "-shared", "-Xcompiler", "-fPIC", "-I", str(OUT), "-o", str(lib), *sources,
+    cmd = [nvcc, "-O3", *ARCH, "-shared", "-Xcompiler", "-fPIC", "-I", str(OUT), "-I", str(HERE),
+           "-I", str(reference / TEMPLATES), "-o", str(lib), *sources,
            "-lcublas"]
     subprocess.run(cmd, check=True)
     return lib

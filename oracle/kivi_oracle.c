@@ -491,6 +491,116 @@ void kivi_oracle_gemv(const uint16_t* w, const uint16_t* x, uint16_t* y_f16, flo
     }
 }
 
+/* ---------------------------------------------------------------------------------------------
+ * Element-wise kernels of the generated decode runtime (templates/kernels.cu), restated per row
+ * for a batch of rows. Each keeps the reference's fp32 expression and, for the RMSNorm sum, its
+ * reduction order, so the only differences from the reference on a GPU are those of the device
+ * math library (rsqrtf, powf, cosf, sinf, expf are not correctly rounded there).
+ * --------------------------------------------------------------------------------------------- */
+
+/* __hadd: the exact sum of two fp16 values fits a double, so one rounding to fp16 follows. */
+static uint16_t hadd(uint16_t a, uint16_t b) {
+    _Float16 r = (_Float16)((double)h2f(a) + (double)h2f(b));
+    uint16_t bits;
+    memcpy(&bits, &r, 2);
+    return bits;
+}
+
+/* vadd (kernels.cu:156-159) then rmsnorm_kernel<<<1,256>>> (kernels.cu:10-33): thread t sums
+ * elements t, t+256, ...; a xor-shuffle tree adds the 32 lanes of a warp (every lane ends with
+ * the same value because fp32 addition commutes); thread 0 adds the warp totals in order.
+ * delta and x_out may be NULL. */
+void kivi_oracle_residual_rmsnorm(const uint16_t* x, const uint16_t* delta, const uint16_t* weight,
+                                  uint16_t* x_out, uint16_t* normed, int batch, int hidden, float eps) {
+    enum { THREADS = 256 };
+    uint16_t* row = (uint16_t*)malloc((size_t)hidden * sizeof(uint16_t));
+    for (int b = 0; b < batch; ++b) {
+        for (int i = 0; i < hidden; ++i) {
+            uint16_t v = x[(size_t)b * hidden + i];
+            if (delta) v = hadd(v, delta[(size_t)b * hidden + i]);
+            row[i] = v;
+            if (x_out) x_out[(size_t)b * hidden + i] = v;
+        }
+        float lane[THREADS];
+        for (int t = 0; t < THREADS; ++t) {
+            float local = 0.0f;
+            for (int i = t; i < hidden; i += THREADS) {
+                float v = h2f(row[i]);
+                local += v * v;
+            }
+            lane[t] = local;
+        }
+        float total = 0.0f;
+        for (int w = 0; w < THREADS / 32; ++w) {
+            float* l = lane + 32 * w;
+            for (int off = 16; off > 0; off >>= 1) {
+                float next[32];
+                for (int k = 0; k < 32; ++k) next[k] = l[k] + l[k ^ off];
+                memcpy(l, next, sizeof(next));
+            }
+            total += l[0];
+        }
+        float scale = 1.0f / sqrtf(total / hidden + eps);
+        for (int i = 0; i < hidden; ++i)
+            normed[(size_t)b * hidden + i] = f2h(h2f(row[i]) * scale * h2f(weight[i]));
+    }
+    free(row);
+}
+
+/* bias_add_kernel (kernels.cu:163-166) then rope_qk_kernel (kernels.cu:40-54) at positions[b];
+ * q, k and v are written split: q [batch, NH*HD], k and v [batch, NKV*HD]. bias may be NULL. */
+void kivi_oracle_bias_rope(const uint16_t* qkv, const uint16_t* bias, const int* positions, uint16_t* q,
+                           uint16_t* k, uint16_t* v, int batch, int nh, int nkv, int hd, float rope_base) {
+    const int half = hd / 2, qkv_out = (nh + 2 * nkv) * hd;
+    for (int b = 0; b < batch; ++b) {
+        const uint16_t* in = qkv + (size_t)b * qkv_out;
+        const int pos = positions[b];
+        for (int h = 0; h < nh + nkv; ++h) {
+            uint16_t* out = h < nh ? q + ((size_t)b * nh + h) * hd : k + ((size_t)b * nkv + (h - nh)) * hd;
+            for (int i = 0; i < half; ++i) {
+                float freq = 1.0f / powf(rope_base, (2.0f * i) / hd);
+                float ang = pos * freq;
+                float c = cosf(ang), s = sinf(ang);
+                uint16_t h0 = in[h * hd + i], h1 = in[h * hd + i + half];
+                if (bias) { h0 = hadd(h0, bias[h * hd + i]); h1 = hadd(h1, bias[h * hd + i + half]); }
+                float x0 = h2f(h0), x1 = h2f(h1);
+                out[i] = f2h(x0 * c - x1 * s);
+                out[i + half] = f2h(x1 * c + x0 * s);
+            }
+        }
+        for (int e = 0; e < nkv * hd; ++e) {
+            uint16_t val = in[(nh + nkv) * hd + e];
+            if (bias) val = hadd(val, bias[(nh + nkv) * hd + e]);
+            v[(size_t)b * nkv * hd + e] = val;
+        }
+    }
+}
+
+/* silu_mul_kernel (kernels.cu:146-153) on rows [gate | up]. */
+void kivi_oracle_silu_mul(const uint16_t* gate_up, uint16_t* out, int batch, int ffn) {
+    for (int b = 0; b < batch; ++b)
+        for (int i = 0; i < ffn; ++i) {
+            float g = h2f(gate_up[(size_t)b * 2 * ffn + i]);
+            float s = g / (1.0f + expf(-g));
+            out[(size_t)b * ffn + i] = f2h(s * h2f(gate_up[(size_t)b * 2 * ffn + ffn + i]));
+        }
+}
+
+/* argmax_kernel (kernels.cu:203-227): start from (-1e30, 0), replace on a strictly larger value.
+ * The reference's choice among equal maxima depends on its thread layout; here the lowest index
+ * wins. */
+void kivi_oracle_argmax(const uint16_t* logits, int* out, int batch, int n) {
+    for (int b = 0; b < batch; ++b) {
+        float best = -1e30f;
+        int best_i = 0;
+        for (int i = 0; i < n; ++i) {
+            float v = h2f(logits[(size_t)b * n + i]);
+            if (v > best) { best = v; best_i = i; }
+        }
+        out[b] = best_i;
+    }
+}
+
 /* Exposed for the tests of the conversion helpers. */
 float kivi_oracle_h2f(uint16_t h) { return h2f(h); }
 uint16_t kivi_oracle_f2h(float f) { return f2h(f); }

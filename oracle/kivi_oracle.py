@@ -224,6 +224,48 @@ def gemv(w, x, nthreads: int = 1) -> tuple[np.ndarray, np.ndarray]:
     return y16.view(np.float16).reshape(shape), y32.reshape(shape)
 
 
+def residual_rmsnorm(x, delta, weight, eps: float) -> tuple[np.ndarray, np.ndarray]:
+    """``x_out = x + delta`` (``delta`` may be None), ``normed = RMSNorm(x_out) * weight``; rows [batch, hidden]."""
+    x = _u16(x)
+    batch, hidden = x.shape
+    d = None if delta is None else _u16(delta)
+    x_out = np.zeros_like(x)
+    normed = np.zeros_like(x)
+    lib().kivi_oracle_residual_rmsnorm(_p(x), _p(d), _p(_u16(weight)), _p(x_out), _p(normed), ctypes.c_int(batch),
+                                       ctypes.c_int(hidden), ctypes.c_float(eps))
+    return x_out.view(np.float16), normed.view(np.float16)
+
+
+def bias_rope(qkv, bias, positions, nh: int, nkv: int, hd: int, rope_base: float):
+    """Bias add, RoPE on q and k at ``positions``; returns q [batch, nh*hd], k, v [batch, nkv*hd]."""
+    qkv = _u16(qkv)
+    batch = qkv.shape[0]
+    pos = np.ascontiguousarray(positions, dtype=np.int32)
+    b = None if bias is None else _u16(bias)
+    q = np.zeros((batch, nh * hd), np.uint16)
+    k = np.zeros((batch, nkv * hd), np.uint16)
+    v = np.zeros((batch, nkv * hd), np.uint16)
+    lib().kivi_oracle_bias_rope(_p(qkv), _p(b), _p(pos), _p(q), _p(k), _p(v), ctypes.c_int(batch), ctypes.c_int(nh),
+                                ctypes.c_int(nkv), ctypes.c_int(hd), ctypes.c_float(rope_base))
+    return q.view(np.float16), k.view(np.float16), v.view(np.float16)
+
+
+def silu_mul(gate_up) -> np.ndarray:
+    gate_up = _u16(gate_up)
+    batch, two_ffn = gate_up.shape
+    out = np.zeros((batch, two_ffn // 2), np.uint16)
+    lib().kivi_oracle_silu_mul(_p(gate_up), _p(out), ctypes.c_int(batch), ctypes.c_int(two_ffn // 2))
+    return out.view(np.float16)
+
+
+def argmax(logits) -> np.ndarray:
+    logits = _u16(logits)
+    batch, n = logits.shape
+    out = np.zeros(batch, np.int32)
+    lib().kivi_oracle_argmax(_p(logits), _p(out), ctypes.c_int(batch), ctypes.c_int(n))
+    return out
+
+
 def h2f(bits: int) -> float:
     return float(lib().kivi_oracle_h2f(ctypes.c_uint16(bits)))
 
