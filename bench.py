@@ -517,6 +517,18 @@ def run_step(args):
     if world > 1:
         dist.all_reduce(torch.zeros(8, device=device, dtype=torch.float16))   # communicator up before the capture
     torch.cuda.synchronize(device)
+    if args.profile_only:
+        # eager steps inside an NVTX range: the command line ncu wraps (--nvtx --nvtx-include "kivi_step/")
+        rt.step()
+        torch.cuda.synchronize(device)
+        torch.cuda.nvtx.range_push("kivi_step")
+        for _ in range(args.steps):
+            rt.step()
+        torch.cuda.synchronize(device)
+        torch.cuda.nvtx.range_pop()
+        print(json.dumps({"profile_only": True, "workload": args.workload, "steps": args.steps,
+                          "launches_per_step": cfg.layers * 10 + 6}))
+        return
     rt.capture()
     for _ in range(warm):
         rt.step()

@@ -26,8 +26,14 @@ __device__ __forceinline__ int chunks_of(const DecodeParams& p, int old_valid) {
     return old_valid > 0 ? (old_valid + p.chunk_tokens - 1) / p.chunk_tokens : 1;
 }
 
-// Call with all threads of the CTA after the partials of this CTA were stored.
-__device__ __forceinline__ void merge_when_last(const DecodeParams& p, int i, int kv, int nchunks) {
+// Call with all threads of the CTA after the partials of this CTA were stored. `scratch` is shared
+// memory the CTA no longer needs (or nullptr). With enough of it the merge runs in two parallel
+// phases: one warp per query head turns the chunks' (max, sum) pairs into normalised weights, then
+// every thread owns up to MAXI output elements and keeps 4 x MAXI partial loads in flight. Without
+// scratch each output element walks the chunks on its own.
+template <int MAXI>
+__device__ __forceinline__ void merge_when_last(const DecodeParams& p, int i, int kv, int nchunks, float* scratch,
+                                                int scratch_floats) {
     const Geom& g = p.geom;
     __shared__ int s_last;
     __threadfence();
@@ -41,18 +47,69 @@ __device__ __forceinline__ void merge_when_last(const DecodeParams& p, int i, in
     if (!s_last) return;
     __threadfence();
     const size_t base = ((size_t)i * g.nkv + kv) * p.max_chunks;
-    for (int idx = threadIdx.x; idx < g.qpk * g.d; idx += blockDim.x) {
-        const int hq = idx / g.d, d = idx - hq * g.d;
-        float mx = -1.0e30f;
-        for (int c = 0; c < nchunks; ++c) mx = fmaxf(mx, __ldcg(p.ws_ml + ((base + c) * g.qpk + hq) * 2));
-        float l = 0.0f, acc = 0.0f;
-        for (int c = 0; c < nchunks; ++c) {
-            const size_t pi = (base + c) * g.qpk + hq;
-            const float w = fast_exp2(__ldcg(p.ws_ml + pi * 2) - mx);
-            l += w * __ldcg(p.ws_ml + pi * 2 + 1);
-            acc += w * __ldcg(p.ws_o + pi * g.d + d);
+    const int outputs = g.qpk * g.d;
+    const size_t out0 = ((size_t)i * g.nh + (size_t)kv * g.qpk) * g.d;
+    if (scratch && nchunks * g.qpk <= scratch_floats && outputs <= MAXI * (int)blockDim.x) {
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+        for (int hq = warp; hq < g.qpk; hq += nwarps) {
+            float mx = -1.0e30f;
+            for (int c = lane; c < nchunks; c += 32) mx = fmaxf(mx, __ldcg(p.ws_ml + ((base + c) * g.qpk + hq) * 2));
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+            float l = 0.0f;
+            for (int c = lane; c < nchunks; c += 32) {
+                const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.ws_ml + ((base + c) * g.qpk + hq) * 2));
+                const float w = fast_exp2(ml.x - mx);
+                scratch[c * g.qpk + hq] = w;
+                l += w * ml.y;
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
+            const float inv = 1.0f / fmaxf(l, 1.0e-30f);
+            __syncwarp();
+            for (int c = lane; c < nchunks; c += 32) scratch[c * g.qpk + hq] *= inv;
         }
-        store_out(p, ((size_t)i * g.nh + kv * g.qpk + hq) * g.d + d, acc / fmaxf(l, 1.0e-30f));
+        __syncthreads();
+        float acc[MAXI];
+        int hq_of[MAXI], d_of[MAXI];
+#pragma unroll
+        for (int k = 0; k < MAXI; ++k) {
+            const int idx = threadIdx.x + k * blockDim.x;
+            acc[k] = 0.0f;
+            hq_of[k] = idx < outputs ? idx / g.d : -1;
+            d_of[k] = idx < outputs ? idx - hq_of[k] * g.d : 0;
+        }
+        for (int c = 0; c < nchunks; c += 4) {
+            float v[4][MAXI];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int k = 0; k < MAXI; ++k)
+                    v[u][k] = (c + u < nchunks && hq_of[k] >= 0)
+                                  ? __ldcg(p.ws_o + ((base + c + u) * g.qpk + hq_of[k]) * g.d + d_of[k]) : 0.0f;
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int k = 0; k < MAXI; ++k)
+                    if (c + u < nchunks && hq_of[k] >= 0) acc[k] += scratch[(c + u) * g.qpk + hq_of[k]] * v[u][k];
+        }
+#pragma unroll
+        for (int k = 0; k < MAXI; ++k)
+            if (hq_of[k] >= 0) store_out(p, out0 + (size_t)hq_of[k] * g.d + d_of[k], acc[k]);
+    } else {
+        for (int idx = threadIdx.x; idx < outputs; idx += blockDim.x) {
+            const int hq = idx / g.d, d = idx - hq * g.d;
+            float mx = -1.0e30f;
+            for (int c = 0; c < nchunks; ++c) mx = fmaxf(mx, __ldcg(p.ws_ml + ((base + c) * g.qpk + hq) * 2));
+            float l = 0.0f, acc = 0.0f;
+            for (int c = 0; c < nchunks; ++c) {
+                const size_t pi = (base + c) * g.qpk + hq;
+                const float w = fast_exp2(__ldcg(p.ws_ml + pi * 2) - mx);
+                l += w * __ldcg(p.ws_ml + pi * 2 + 1);
+                acc += w * __ldcg(p.ws_o + pi * g.d + d);
+            }
+            store_out(p, out0 + (size_t)hq * g.d + d, acc / fmaxf(l, 1.0e-30f));
+        }
     }
     if (threadIdx.x == 0) *counter = 0u;  // leave the workspace ready for the next launch
 }

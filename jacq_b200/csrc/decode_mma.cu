@@ -142,6 +142,7 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
 
     const Geom& g = p.geom;
     const int i = blockIdx.z, kv = blockIdx.y, chunk = blockIdx.x;
+    pdl_trigger();   // a projection launched behind this kernel may start streaming its weights
     // the warp index through a broadcast, so that everything derived from it is known to be warp-uniform
     const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
     const int r = lane >> 2, t = lane & 3;
@@ -619,7 +620,8 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
             if (d == 0) { p.ws_ml[part * 2] = mx; p.ws_ml[part * 2 + 1] = l; }
         }
     }
-    if (nchunks > 1) merge_when_last(p, i, kv, nchunks);
+    // the merge reuses the ring (the warp states in it were consumed above, behind its first barrier)
+    if (nchunks > 1) merge_when_last<8>(p, i, kv, nchunks, reinterpret_cast<float*>(ring), W * C::STATE_FLOATS);
 }
 
 template <int D, int G, int LOGB, int W, int CTAS>

@@ -9,11 +9,13 @@
 #include <cooperative_groups.h>
 
 #include "kivi_common.cuh"
+#include "step_math.cuh"
 
 namespace kivi {
 namespace {
 
-constexpr int kGemvThreads = 256;
+constexpr int kGemvThreads = kNormThreads;   // the fused RMSNorm prologue needs exactly this many
+constexpr int kGemvCtasPerSm = 3;
 constexpr int kRowsPerWarp = 2;
 constexpr int kUnroll = 4;
 
@@ -44,21 +46,72 @@ __device__ __forceinline__ void fma_chunk(float (&acc)[BT], const uint4& w, cons
     }
 }
 
-template <int BT>
-__global__ void __launch_bounds__(kGemvThreads) gemv_kernel(const __half* __restrict__ w, const __half* __restrict__ x,
+template <int BT, int PRO>
+__global__ void __launch_bounds__(kGemvThreads, kGemvCtasPerSm) gemv_kernel(const __half* __restrict__ w, const GemvPrologue pro,
                                                             __half* __restrict__ y16, float* __restrict__ y32,
                                                             int out_dim, int in_dim, int ldy) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
+    __shared__ float warp_sums[32];
     uint4* xs = reinterpret_cast<uint4*>(smem_raw);  // [BT, in_dim / 8]
     const int chunks = in_dim / 8;
-    for (int c = threadIdx.x; c < BT * chunks; c += kGemvThreads) xs[c] = reinterpret_cast<const uint4*>(x)[c];
-    __syncthreads();
-
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int warps_total = gridDim.x * (kGemvThreads / 32);
     const int gwarp = blockIdx.x * (kGemvThreads / 32) + warp;
+    pdl_trigger();
 
-    for (int row0 = gwarp * kRowsPerWarp; row0 < out_dim; row0 += warps_total * kRowsPerWarp) {
+    // The weights do not depend on the kernel before this one: the first loads of W go out before
+    // waiting for it, so they are in flight while the predecessor drains and the input is prepared.
+    uint4 v[kRowsPerWarp][kUnroll];
+    const int first_row = gwarp * kRowsPerWarp;
+    bool have = false;
+    if (first_row < out_dim && lane + 32 * (kUnroll - 1) < chunks) {
+#pragma unroll
+        for (int r = 0; r < kRowsPerWarp; ++r) {
+            const int row = first_row + r < out_dim ? first_row + r : out_dim - 1;
+            const uint4* wr = reinterpret_cast<const uint4*>(w + (size_t)row * in_dim);
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) v[r][u] = ld_stream(wr + lane + 32 * u);
+        }
+        have = true;
+    }
+    pdl_wait();
+
+    if (PRO == kGemvPlain) {
+        for (int c = threadIdx.x; c < BT * chunks; c += kGemvThreads) xs[c] = reinterpret_cast<const uint4*>(pro.x)[c];
+        __syncthreads();
+    } else if (PRO == kGemvSiluMul) {
+        for (int c = threadIdx.x; c < BT * chunks; c += kGemvThreads) {
+            const int b = c / chunks, cc = c - b * chunks;
+            const uint4* row = reinterpret_cast<const uint4*>(pro.x + (size_t)b * 2 * in_dim);
+            xs[c] = silu_mul8(row[cc], row[chunks + cc]);
+        }
+        __syncthreads();
+    } else {
+        for (int c = threadIdx.x; c < BT * chunks; c += kGemvThreads) {
+            const int b = c / chunks, cc = c - b * chunks;
+            const size_t src = pro.tokens ? (size_t)pro.tokens[b] : (size_t)b;
+            uint4 a = reinterpret_cast<const uint4*>(pro.x + src * in_dim)[cc];
+            if (pro.delta) a = hadd8(a, reinterpret_cast<const uint4*>(pro.delta + (size_t)b * in_dim)[cc]);
+            if (pro.x_out && blockIdx.x == 0) reinterpret_cast<uint4*>(pro.x_out + (size_t)b * in_dim)[cc] = a;
+            xs[c] = a;
+        }
+        __syncthreads();
+        float scale[BT];
+#pragma unroll
+        for (int b = 0; b < BT; ++b)
+            scale[b] = rms_scale(reinterpret_cast<const __half*>(xs + b * chunks), in_dim, pro.eps, warp_sums);
+        __syncthreads();
+        for (int c = threadIdx.x; c < BT * chunks; c += kGemvThreads) {
+            const int b = c / chunks, cc = c - b * chunks;
+            float sc = scale[0];
+#pragma unroll
+            for (int k = 1; k < BT; ++k) sc = b == k ? scale[k] : sc;
+            xs[c] = norm_apply8(xs[c], reinterpret_cast<const uint4*>(pro.weight)[cc], sc);
+        }
+        __syncthreads();
+    }
+
+    for (int row0 = first_row; row0 < out_dim; row0 += warps_total * kRowsPerWarp) {
         float acc[kRowsPerWarp][BT];
 #pragma unroll
         for (int r = 0; r < kRowsPerWarp; ++r)
@@ -72,11 +125,13 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_kernel(const __half* __rest
         }
         int c = lane;
         for (; c + 32 * (kUnroll - 1) < chunks; c += 32 * kUnroll) {
-            uint4 v[kRowsPerWarp][kUnroll];
+            if (!have) {
 #pragma unroll
-            for (int r = 0; r < kRowsPerWarp; ++r)
+                for (int r = 0; r < kRowsPerWarp; ++r)
 #pragma unroll
-                for (int u = 0; u < kUnroll; ++u) v[r][u] = ld_stream(wr[r] + c + 32 * u);
+                    for (int u = 0; u < kUnroll; ++u) v[r][u] = ld_stream(wr[r] + c + 32 * u);
+            }
+            have = false;
 #pragma unroll
             for (int r = 0; r < kRowsPerWarp; ++r)
 #pragma unroll
@@ -85,8 +140,8 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_kernel(const __half* __rest
         for (; c < chunks; c += 32) {
 #pragma unroll
             for (int r = 0; r < kRowsPerWarp; ++r) {
-                uint4 v = ld_stream(wr[r] + c);
-                fma_chunk<BT>(acc[r], v, xs, c, chunks);
+                uint4 t = ld_stream(wr[r] + c);
+                fma_chunk<BT>(acc[r], t, xs, c, chunks);
             }
         }
 #pragma unroll
@@ -104,37 +159,65 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_kernel(const __half* __rest
     }
 }
 
-template <int BT>
-cudaError_t launch_bt(const __half* w, const __half* x, __half* y16, float* y32, int out_dim, int in_dim,
+template <int BT, int PRO>
+cudaError_t launch_bt(const __half* w, const GemvPrologue& pro, __half* y16, float* y32, int out_dim, int in_dim,
                       cudaStream_t stream) {
     const size_t smem = (size_t)BT * in_dim * sizeof(__half);
     if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_kernel<BT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(gemv_kernel<BT, PRO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
-    // Enough CTAs to fill the 148 SMs a few times over, never more warps than row pairs.
+    // Enough CTAs to fill the 148 SMs, never more warps than row pairs; all of them
+    // resident at once, so a kernel launched behind this one can start as soon as they have.
     const int warps_needed = (out_dim + kRowsPerWarp - 1) / kRowsPerWarp;
     int blocks = (warps_needed + kGemvThreads / 32 - 1) / (kGemvThreads / 32);
-    if (blocks > 148 * 4) blocks = 148 * 4;
-    gemv_kernel<BT><<<blocks, kGemvThreads, smem, stream>>>(w, x, y16, y32, out_dim, in_dim, out_dim);
-    return cudaGetLastError();
+    if (blocks > 148 * kGemvCtasPerSm) blocks = 148 * kGemvCtasPerSm;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(blocks, 1, 1);
+    cfg.blockDim = dim3(kGemvThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, gemv_kernel<BT, PRO>, w, pro, y16, y32, out_dim, in_dim, out_dim);
+}
+
+template <int PRO>
+cudaError_t launch_pro(const __half* w, const GemvPrologue& pro, __half* y16, float* y32, int out_dim, int in_dim,
+                       int batch, cudaStream_t stream) {
+    switch (batch) {
+        case 1: return launch_bt<1, PRO>(w, pro, y16, y32, out_dim, in_dim, stream);
+        case 2: return launch_bt<2, PRO>(w, pro, y16, y32, out_dim, in_dim, stream);
+        case 3: return launch_bt<3, PRO>(w, pro, y16, y32, out_dim, in_dim, stream);
+        default: return launch_bt<4, PRO>(w, pro, y16, y32, out_dim, in_dim, stream);
+    }
 }
 
 }  // namespace
 
+// y[b, :] = W prologue(x)[b, :] for 1 <= batch <= 4 in one pass over W.
+cudaError_t launch_gemv_fused(const __half* w, int kind, const GemvPrologue& pro, __half* y16, float* y32, int out_dim,
+                              int in_dim, int batch, cudaStream_t stream) {
+    if (batch < 1 || batch > 4) return cudaErrorInvalidValue;
+    if (kind == kGemvAddNorm) return launch_pro<kGemvAddNorm>(w, pro, y16, y32, out_dim, in_dim, batch, stream);
+    if (kind == kGemvSiluMul) return launch_pro<kGemvSiluMul>(w, pro, y16, y32, out_dim, in_dim, batch, stream);
+    return launch_pro<kGemvPlain>(w, pro, y16, y32, out_dim, in_dim, batch, stream);
+}
+
 cudaError_t launch_gemv(const __half* w, const __half* x, __half* y16, float* y32, int out_dim, int in_dim,
                         int batch, cudaStream_t stream) {
     int b = 0;
-    while (b < batch) {
-        const int left = batch - b;
-        const __half* xb = x + (size_t)b * in_dim;
-        __half* y16b = y16 ? y16 + (size_t)b * out_dim : nullptr;
-        float* y32b = y32 ? y32 + (size_t)b * out_dim : nullptr;
-        cudaError_t e;
-        if (left >= 4) { e = launch_bt<4>(w, xb, y16b, y32b, out_dim, in_dim, stream); b += 4; }
-        else if (left >= 2) { e = launch_bt<2>(w, xb, y16b, y32b, out_dim, in_dim, stream); b += 2; }
-        else { e = launch_bt<1>(w, xb, y16b, y32b, out_dim, in_dim, stream); b += 1; }
+    while (b < batch) {   // groups of up to four columns share a pass over W
+        const int take = batch - b >= 4 ? 4 : batch - b;
+        GemvPrologue pro = {};
+        pro.x = x + (size_t)b * in_dim;
+        cudaError_t e = launch_gemv_fused(w, kGemvPlain, pro, y16 ? y16 + (size_t)b * out_dim : nullptr,
+                                          y32 ? y32 + (size_t)b * out_dim : nullptr, out_dim, in_dim, take, stream);
         if (e != cudaSuccess) return e;
+        b += take;
     }
     return cudaSuccess;
 }

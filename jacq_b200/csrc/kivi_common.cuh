@@ -233,6 +233,12 @@ __device__ __forceinline__ void ldmatrix_x4_32(uint32_t (&r)[4], uint32_t a) {
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
 }
 
+// Programmatic dependent launch: a kernel launched with the stream-serialisation attribute may start
+// while its predecessor drains; it must call pdl_wait() before touching anything the predecessor
+// wrote. pdl_trigger() lets the successor start early; it is harmless when nothing depends on it.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // D(16x8, f32) += A(16x16, f16, row) * B(16x8, f16, col)
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
@@ -282,6 +288,9 @@ cudaError_t launch_decode_mma(const DecodeParams& p, cudaStream_t stream);
 bool decode_mma_supports(const Geom& g, int retained_pages);
 cudaError_t launch_gemv(const __half* w, const __half* x, __half* y16, float* y32, int out_dim, int in_dim,
                         int batch, cudaStream_t stream);
+struct GemvPrologue;   // step_math.cuh
+cudaError_t launch_gemv_fused(const __half* w, int kind, const GemvPrologue& pro, __half* y16, float* y32, int out_dim,
+                              int in_dim, int batch, cudaStream_t stream);
 bool skinny_gemm_supports(int in_dim, int batch);
 cudaError_t launch_skinny_gemm(const __half* w, const __half* x, __half* y16, float* y32, int out_dim, int in_dim,
                                int batch, cudaStream_t stream);

@@ -18,11 +18,10 @@
 //   SiLU*up   g / (1 + expf(-g)) * up                                            (kernels.cu:146-153)
 //   add, bias fp16 __hadd                                                        (kernels.cu:156-166)
 #include "kivi_common.cuh"
+#include "step_math.cuh"
 
 namespace kivi {
 namespace {
-
-constexpr int kNormThreads = 256;   // the reduction order of the reference depends on this value
 
 // x_out = x (+ delta); normed = RMSNorm(x_out) * weight. One CTA per row. `tokens` (optional)
 // makes row i of x the embedding row tokens[i] (kernels.cu:4-7).
@@ -30,9 +29,10 @@ __global__ void __launch_bounds__(kNormThreads) residual_rmsnorm_kernel(
     const __half* __restrict__ x, const int* __restrict__ tokens, const __half* __restrict__ delta,
     const __half* __restrict__ weight, __half* __restrict__ x_out, __half* __restrict__ normed, int hidden, float eps) {
     extern __shared__ __align__(16) unsigned char step_smem[];
-    __half* row = reinterpret_cast<__half*>(step_smem);
+    uint4* row = reinterpret_cast<uint4*>(step_smem);
     __shared__ float warp_sums[32];
     const int tid = threadIdx.x;
+    pdl_trigger();
     const size_t src_row = tokens ? (size_t)tokens[blockIdx.x] : (size_t)blockIdx.x;
     const uint4* xs = reinterpret_cast<const uint4*>(x + src_row * hidden);
     const uint4* ds = delta ? reinterpret_cast<const uint4*>(delta + (size_t)blockIdx.x * hidden) : nullptr;
@@ -40,79 +40,44 @@ __global__ void __launch_bounds__(kNormThreads) residual_rmsnorm_kernel(
     const int vecs = hidden >> 3;
     for (int v = tid; v < vecs; v += kNormThreads) {
         uint4 a = xs[v];
-        if (ds) {
-            const uint4 d = ds[v];
-            __half2* ah = reinterpret_cast<__half2*>(&a);
-            const __half2* dh = reinterpret_cast<const __half2*>(&d);
-#pragma unroll
-            for (int k = 0; k < 4; ++k) ah[k] = __hadd2(ah[k], dh[k]);
-        }
+        if (ds) a = hadd8(a, ds[v]);
         if (xo) xo[v] = a;
-        reinterpret_cast<uint4*>(row)[v] = a;
+        row[v] = a;
     }
     __syncthreads();
-    float local = 0.0f;
-    for (int i = tid; i < hidden; i += kNormThreads) {
-        const float v = __half2float(row[i]);
-        local += v * v;
-    }
-    for (int off = 16; off > 0; off >>= 1) local += __shfl_xor_sync(0xffffffffu, local, off);
-    if ((tid & 31) == 0) warp_sums[tid >> 5] = local;
-    __syncthreads();
-    if (tid == 0) {
-        float total = 0.0f;
-        for (int w = 0; w < kNormThreads / 32; ++w) total += warp_sums[w];
-        warp_sums[0] = total;
-    }
-    __syncthreads();
-    const float scale = rsqrtf(warp_sums[0] / hidden + eps);
+    const float scale = rms_scale(reinterpret_cast<const __half*>(row), hidden, eps, warp_sums);
     uint4* no = reinterpret_cast<uint4*>(normed + (size_t)blockIdx.x * hidden);
     const uint4* wv = reinterpret_cast<const uint4*>(weight);
-    for (int v = tid; v < vecs; v += kNormThreads) {
-        const uint4 a = reinterpret_cast<const uint4*>(row)[v];
-        const uint4 w = wv[v];
-        const __half* ah = reinterpret_cast<const __half*>(&a);
-        const __half* wh = reinterpret_cast<const __half*>(&w);
-        uint4 o;
-        __half* oh = reinterpret_cast<__half*>(&o);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) oh[k] = __float2half(__half2float(ah[k]) * scale * __half2float(wh[k]));
-        no[v] = o;
-    }
+    for (int v = tid; v < vecs; v += kNormThreads) no[v] = norm_apply8(row[v], wv[v], scale);
 }
 
 // qkv row [q heads | k heads | v heads] (+ bias) -> q and k rotated at positions[row], v copied.
-// Thread (i, lane group) owns pair index i of every head it visits, so the angle is computed once
-// per (row, i) and not once per head.
-__global__ void __launch_bounds__(256) bias_rope_kernel(
+// One CTA per (row, head), one thread per rotated pair, like the reference's launch
+// (<<<NH + NKV, 64>>>, runtime.cu:159) with the value heads added.
+__global__ void __launch_bounds__(128) bias_rope_kernel(
     const __half* __restrict__ qkv, const __half* __restrict__ bias, const int* __restrict__ positions,
     __half* __restrict__ q, __half* __restrict__ k, __half* __restrict__ v, int nh, int nkv, int hd, float rope_base) {
-    const int rowi = blockIdx.x;
+    const int rowi = blockIdx.y, h = blockIdx.x;
     const int half_dim = hd >> 1;
-    const int qkv_out = (nh + 2 * nkv) * hd;
-    const __half* in = qkv + (size_t)rowi * qkv_out;
+    pdl_trigger();
+    const __half* in = qkv + (size_t)rowi * (nh + 2 * nkv) * hd + (size_t)h * hd;
+    const __half* bh = bias ? bias + (size_t)h * hd : nullptr;
+    if (h >= nh + nkv) {   // a value head: bias add only
+        __half* out = v + ((size_t)rowi * nkv + (h - nh - nkv)) * hd;
+        for (int e = threadIdx.x; e < hd; e += blockDim.x) out[e] = bh ? __hadd(in[e], bh[e]) : in[e];
+        return;
+    }
     const int pos = positions[rowi];
-    const int groups = blockDim.x / half_dim;            // head lanes working in parallel
-    const int i = threadIdx.x % half_dim, grp = threadIdx.x / half_dim;
-    if (grp < groups) {
+    __half* out = h < nh ? q + ((size_t)rowi * nh + h) * hd : k + ((size_t)rowi * nkv + (h - nh)) * hd;
+    for (int i = threadIdx.x; i < half_dim; i += blockDim.x) {
         const float freq = 1.0f / powf(rope_base, (2.0f * i) / hd);
         const float ang = pos * freq;
         const float c = cosf(ang), s = sinf(ang);
-        for (int h = grp; h < nh + nkv; h += groups) {
-            const int base = h * hd;
-            __half h0 = in[base + i], h1 = in[base + i + half_dim];
-            if (bias) { h0 = __hadd(h0, bias[base + i]); h1 = __hadd(h1, bias[base + i + half_dim]); }
-            const float x0 = __half2float(h0), x1 = __half2float(h1);
-            __half* out = h < nh ? q + ((size_t)rowi * nh + h) * hd : k + ((size_t)rowi * nkv + (h - nh)) * hd;
-            out[i] = __float2half(x0 * c - x1 * s);
-            out[i + half_dim] = __float2half(x1 * c + x0 * s);
-        }
-    }
-    const int voff = (nh + nkv) * hd;
-    for (int e = threadIdx.x; e < nkv * hd; e += blockDim.x) {
-        __half val = in[voff + e];
-        if (bias) val = __hadd(val, bias[voff + e]);
-        v[(size_t)rowi * nkv * hd + e] = val;
+        __half h0 = in[i], h1 = in[i + half_dim];
+        if (bh) { h0 = __hadd(h0, bh[i]); h1 = __hadd(h1, bh[i + half_dim]); }
+        const float x0 = __half2float(h0), x1 = __half2float(h1);
+        out[i] = __float2half(x0 * c - x1 * s);
+        out[i + half_dim] = __float2half(x1 * c + x0 * s);
     }
 }
 
@@ -121,20 +86,10 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const __half* __restrict_
                                                         int ffn) {
     const int rowi = blockIdx.y;
     const int v = blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_trigger();
     if (v >= (ffn >> 3)) return;
-    const uint4 g = reinterpret_cast<const uint4*>(gate_up + (size_t)rowi * 2 * ffn)[v];
-    const uint4 u = reinterpret_cast<const uint4*>(gate_up + (size_t)rowi * 2 * ffn + ffn)[v];
-    const __half* gh = reinterpret_cast<const __half*>(&g);
-    const __half* uh = reinterpret_cast<const __half*>(&u);
-    uint4 o;
-    __half* oh = reinterpret_cast<__half*>(&o);
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-        const float gv = __half2float(gh[k]);
-        const float sv = gv / (1.0f + expf(-gv));
-        oh[k] = __float2half(sv * __half2float(uh[k]));
-    }
-    reinterpret_cast<uint4*>(out + (size_t)rowi * ffn)[v] = o;
+    const uint4* row = reinterpret_cast<const uint4*>(gate_up + (size_t)rowi * 2 * ffn);
+    reinterpret_cast<uint4*>(out + (size_t)rowi * ffn)[v] = silu_mul8(row[v], row[(ffn >> 3) + v]);
 }
 
 // Arg-max, first pass: block (chunk, row) scans its slice of the row. A candidate is (value, index);
@@ -226,7 +181,9 @@ int launch_residual_rmsnorm(const __half* x, const int* tokens, const __half* de
 
 int launch_bias_rope(const __half* qkv, const __half* bias, const int* positions, __half* q, __half* k, __half* v,
                      int batch, int nh, int nkv, int hd, float rope_base, cudaStream_t stream) {
-    bias_rope_kernel<<<batch, 256, 0, stream>>>(qkv, bias, positions, q, k, v, nh, nkv, hd, rope_base);
+    const int threads = hd / 2 <= 32 ? 32 : (hd / 2 <= 64 ? 64 : 128);
+    bias_rope_kernel<<<dim3(nh + 2 * nkv, batch), threads, 0, stream>>>(qkv, bias, positions, q, k, v, nh, nkv, hd,
+                                                                         rope_base);
     return ok(cudaGetLastError());
 }
 
@@ -242,6 +199,35 @@ int project(const __half* w, const __half* x, __half* y, int out_dim, int in_dim
     if (skinny_gemm_supports(in_dim, batch))
         return ok(launch_skinny_gemm(w, x, y, nullptr, out_dim, in_dim, batch, stream));
     return ok(launch_gemv(w, x, y, nullptr, out_dim, in_dim, batch, stream));
+}
+
+// Up to four sequences: the step's element-wise kernels ride in the prologue of the GEMV that
+// consumes them (one launch instead of two, and the weights start streaming before the input is
+// ready). Larger batches run the stand-alone kernel and then the skinny GEMM.
+bool fuse_prologues(int batch) { return batch <= 4; }
+
+// y = W RMSNorm(x (+ delta)); the updated residual rows go to x_out.
+int project_add_norm(const __half* w, const __half* x, const int* tokens, const __half* delta, const __half* weight,
+                     __half* x_out, __half* normed_scratch, __half* y, int out_dim, int hidden, int batch, float eps,
+                     cudaStream_t stream) {
+    if (fuse_prologues(batch)) {
+        GemvPrologue pro = {x, tokens, delta, weight, x_out, eps};
+        return ok(launch_gemv_fused(w, kGemvAddNorm, pro, y, nullptr, out_dim, hidden, batch, stream));
+    }
+    const int rc = launch_residual_rmsnorm(x, tokens, delta, weight, x_out, normed_scratch, batch, hidden, eps, stream);
+    return rc != KIVI_OK ? rc : project(w, normed_scratch, y, out_dim, hidden, batch, stream);
+}
+
+// y = W (SiLU(gate) * up) for rows [gate | up].
+int project_silu_mul(const __half* w, const __half* gate_up, __half* mid_scratch, __half* y, int out_dim, int ffn,
+                     int batch, cudaStream_t stream) {
+    if (fuse_prologues(batch)) {
+        GemvPrologue pro = {};
+        pro.x = gate_up;
+        return ok(launch_gemv_fused(w, kGemvSiluMul, pro, y, nullptr, out_dim, ffn, batch, stream));
+    }
+    const int rc = launch_silu_mul(gate_up, mid_scratch, batch, ffn, stream);
+    return rc != KIVI_OK ? rc : project(w, mid_scratch, y, out_dim, ffn, batch, stream);
 }
 
 size_t up256(size_t v) { return (v + 255) / 256 * 256; }
@@ -386,11 +372,11 @@ extern "C" int kivi_b200_decode_step(const kivi_step_config* cfg, const kivi_ste
     for (int l = 0; l < c.layers; ++l) {
         const kivi_layer_weights& lw = weights->layers[l];
         // attention block
-        KIVI_STEP_TRY(launch_residual_rmsnorm(embed_tokens ? H(weights->embed) : x_cur, embed_tokens, delta, H(lw.attn_norm),
-                                              x_nxt, normed, batch, c.hidden, c.norm_eps, stream));
+        KIVI_STEP_TRY(project_add_norm(H(lw.qkv), embed_tokens ? H(weights->embed) : x_cur, embed_tokens, delta,
+                                       H(lw.attn_norm), x_nxt, normed, qkv, qkv_rows(c), c.hidden, batch, c.norm_eps,
+                                       stream));
         embed_tokens = nullptr;
         { __half* t = x_cur; x_cur = x_nxt; x_nxt = t; }
-        KIVI_STEP_TRY(project(H(lw.qkv), normed, qkv, qkv_rows(c), c.hidden, batch, stream));
         KIVI_STEP_TRY(launch_bias_rope(qkv, c.attn_bias ? H(lw.qkv_bias) : nullptr, state->seq_lens, q, k, v, batch,
                                        c.num_q_heads, c.num_kv_heads, c.head_dim, c.rope_base, stream));
         WriteParams wp;
@@ -403,19 +389,18 @@ extern "C" int kivi_b200_decode_step(const kivi_step_config* cfg, const kivi_ste
         if (tp && comm->allreduce_f16(comm->user, reinterpret_cast<kivi_f16*>(proj), (size_t)batch * c.hidden, stream))
             return KIVI_ERR_CUDA;
         // feed-forward block
-        KIVI_STEP_TRY(launch_residual_rmsnorm(x_cur, nullptr, proj, H(lw.ffn_norm), x_nxt, normed, batch, c.hidden,
-                                              c.norm_eps, stream));
+        KIVI_STEP_TRY(project_add_norm(H(lw.gate_up), x_cur, nullptr, proj, H(lw.ffn_norm), x_nxt, normed, gate_up,
+                                       2 * c.ffn, c.hidden, batch, c.norm_eps, stream));
         { __half* t = x_cur; x_cur = x_nxt; x_nxt = t; }
-        KIVI_STEP_TRY(project(H(lw.gate_up), normed, gate_up, 2 * c.ffn, c.hidden, batch, stream));
-        KIVI_STEP_TRY(launch_silu_mul(gate_up, mid, batch, c.ffn, stream));
-        KIVI_STEP_TRY(project(H(lw.down), mid, proj, c.hidden, c.ffn, batch, stream));
+        // the down projection must not overwrite `proj` while a gate_up CTA may still read it as delta:
+        // it cannot, every gate_up CTA has finished its prologue before the first down CTA passes its wait
+        KIVI_STEP_TRY(project_silu_mul(H(lw.down), gate_up, mid, proj, c.hidden, c.ffn, batch, stream));
         if (tp && comm->allreduce_f16(comm->user, reinterpret_cast<kivi_f16*>(proj), (size_t)batch * c.hidden, stream))
             return KIVI_ERR_CUDA;
         delta = proj;
     }
-    KIVI_STEP_TRY(launch_residual_rmsnorm(x_cur, nullptr, delta, H(weights->final_norm), x_nxt, normed, batch, c.hidden,
-                                          c.norm_eps, stream));
-    KIVI_STEP_TRY(project(H(weights->lm_head), normed, logits, c.vocab, c.hidden, batch, stream));
+    KIVI_STEP_TRY(project_add_norm(H(weights->lm_head), x_cur, nullptr, delta, H(weights->final_norm), x_nxt, normed,
+                                   logits, c.vocab, c.hidden, batch, c.norm_eps, stream));
 
     const int chunks = argmax_chunks(c.vocab);
     float* part_val = reinterpret_cast<float*>(ws + L.part_val);

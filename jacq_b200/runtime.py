@@ -285,21 +285,14 @@ class DecodeRuntime:
         _native.check(rc, "kivi_b200_decode_step")
 
     def capture(self) -> None:
-        """Record the step into a CUDA graph; later ``step`` calls replay it. The graph stays valid
-        while every sequence is shorter than ``max_seq_len``. The warm-up step run before the
-        capture is undone (sequence lengths restored; its cache write is overwritten by the next
-        real step at the same position)."""
-        lens = self.seq_lens.clone()
-        toks = self.tokens.clone()
-        self._launch()
-        torch.cuda.synchronize(self.device)
-        self.seq_lens.copy_(lens)
-        self.tokens.copy_(toks)
+        """Record the step into a CUDA graph; later ``step`` calls replay it. Nothing runs during the
+        capture, so the caches and lengths are untouched; the graph stays valid while every sequence
+        is shorter than ``max_seq_len``. With tensor parallelism the process group must have
+        communicated once before (NCCL sets itself up on first use, which cannot be captured)."""
         graph = torch.cuda.CUDAGraph()
+        torch.cuda.synchronize(self.device)
         with torch.cuda.graph(graph):
             self._launch()
-        self.seq_lens.copy_(lens)
-        self.tokens.copy_(toks)
         self._graph = graph
 
     def step(self, tokens: torch.Tensor | None = None) -> torch.Tensor:
