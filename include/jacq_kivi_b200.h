@@ -192,8 +192,7 @@ int kivi_b200_gemv_f16(const kivi_f16* w, const kivi_f16* x, kivi_f16* y_f16, fl
  * query/key/value rows of its KV heads, the matching columns of `o`, FFN/tp_size gate and up rows,
  * the matching columns of `down` and VOCAB/tp_size rows of lm_head; the head, FFN and vocabulary
  * counts in kivi_step_config are those LOCAL sizes. The two partial projections per layer are
- * summed across ranks by the caller's all-reduce hook (fp16 sum, in place), the per-rank arg-max
- * candidates by its all-gather hook.
+ * summed across ranks, and the per-rank arg-max candidates gathered, through kivi_step_comm.
  * --------------------------------------------------------------------------------------------- */
 typedef struct kivi_step_config {
     int32_t layers;
@@ -241,7 +240,22 @@ typedef struct kivi_step_state {
     size_t workspace_bytes;
 } kivi_step_state;
 
-/* Collective hooks for tp_size > 1; both run on `stream` and return 0 on success. */
+/* Collectives for tp_size > 1, one of two forms.
+ *
+ * Hooks: the caller's all-reduce (fp16 sum, in place) and all-gather, run on `stream`, 0 on success
+ * (an NCCL communicator, torch.distributed, ...).
+ *
+ * Peer memory (peer_regions != NULL; the hooks are then unused): the library's own exchange over
+ * NVLink. Every rank creates one region of kivi_b200_p2p_region_bytes() bytes with
+ * kivi_b200_p2p_region_create(), hands the returned handle to the other ranks (any host channel),
+ * opens theirs with kivi_b200_p2p_region_open() and passes the tp_size pointers, own region at
+ * index tp_rank, in rank order. A rank pushes its partial projection into its slot in every
+ * region with plain peer stores and raises a flag there; the kernel that consumes the sum (residual
+ * add + RMSNorm) waits for the tp_size flags and adds the slots up in rank order in fp32, so every
+ * rank gets the same bits and the reduction has no launch of its own. Waits are bounded: a rank
+ * that never delivers ends the wait after about a second and sets its bit in the region's status
+ * word (kivi_b200_p2p_status), the step's result is then undefined but nothing hangs. All ranks
+ * must have opened all regions before the first step, and must step in lockstep (same batch). */
 typedef int (*kivi_allreduce_f16_fn)(void* user, kivi_f16* buf, size_t count, cudaStream_t stream);
 typedef int (*kivi_allgather_fn)(void* user, const void* send, void* recv, size_t bytes_per_rank,
                                  cudaStream_t stream);
@@ -249,7 +263,20 @@ typedef struct kivi_step_comm {
     kivi_allreduce_f16_fn allreduce_f16;
     kivi_allgather_fn allgather;
     void* user;
+    void* const* peer_regions;   /* host array [tp_size] of device pointers, or NULL for the hooks */
+    size_t region_bytes;         /* size every region was created with */
+    uint32_t spin_limit;         /* polls before a wait gives up; 0 = the library's default */
 } kivi_step_comm;
+
+#define KIVI_B200_P2P_HANDLE_BYTES 64
+size_t kivi_b200_p2p_region_bytes(const kivi_step_config* cfg, int batch);
+/* cudaMalloc + zero fill on the current device; handle_out receives KIVI_B200_P2P_HANDLE_BYTES bytes. */
+int kivi_b200_p2p_region_create(size_t bytes, void** region, unsigned char* handle_out);
+int kivi_b200_p2p_region_open(const unsigned char* handle, void** peer_region);
+int kivi_b200_p2p_region_close(void* peer_region);
+int kivi_b200_p2p_region_destroy(void* region);
+/* Copies the region's status word to the host (synchronises `stream`): 0 = every wait was served. */
+int kivi_b200_p2p_status(const void* region, uint32_t* status_out, cudaStream_t stream);
 
 size_t kivi_b200_decode_step_workspace_bytes(const kivi_step_config* cfg, int batch, int max_seq_len);
 

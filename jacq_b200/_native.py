@@ -6,7 +6,7 @@ shared object has not been built (``python -m jacq_b200.build``).
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_float, c_int, c_int32, c_size_t, c_void_p
+from ctypes import c_float, c_int, c_int32, c_size_t, c_uint32, c_void_p
 from pathlib import Path
 
 LIB_PATH = Path(__file__).resolve().parent / "_lib" / "libjacq_kivi_b200.so"
@@ -61,7 +61,11 @@ ALLGATHER_FN = ctypes.CFUNCTYPE(c_int, c_void_p, c_void_p, c_void_p, c_size_t, c
 
 
 class KiviStepComm(ctypes.Structure):
-    _fields_ = [("allreduce_f16", ALLREDUCE_F16_FN), ("allgather", ALLGATHER_FN), ("user", c_void_p)]
+    _fields_ = [("allreduce_f16", ALLREDUCE_F16_FN), ("allgather", ALLGATHER_FN), ("user", c_void_p),
+                ("peer_regions", ctypes.POINTER(c_void_p)), ("region_bytes", c_size_t), ("spin_limit", c_uint32)]
+
+
+P2P_HANDLE_BYTES = 64
 
 
 STATUS_NAMES = {
@@ -90,6 +94,12 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "kivi_b200_decode_step": (c_int, [ctypes.POINTER(KiviStepConfig), ctypes.POINTER(KiviStepWeights),
                                       ctypes.POINTER(KiviStepState), _P, c_int, c_int, _P, _P,
                                       ctypes.POINTER(KiviStepComm), _P]),
+    "kivi_b200_p2p_region_bytes": (c_size_t, [ctypes.POINTER(KiviStepConfig), c_int]),
+    "kivi_b200_p2p_region_create": (c_int, [c_size_t, ctypes.POINTER(c_void_p), _P]),
+    "kivi_b200_p2p_region_open": (c_int, [_P, ctypes.POINTER(c_void_p)]),
+    "kivi_b200_p2p_region_close": (c_int, [_P]),
+    "kivi_b200_p2p_region_destroy": (c_int, [_P]),
+    "kivi_b200_p2p_status": (c_int, [_P, ctypes.POINTER(c_uint32), _P]),
     "kivi_b200_residual_rmsnorm": (c_int, [_P, _P, _P, _P, _P, c_int, c_int, c_float, _P]),
     "kivi_b200_bias_rope": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_float, _P]),
     "kivi_b200_silu_mul": (c_int, [_P, _P, c_int, c_int, _P]),

@@ -43,6 +43,8 @@ V2_SYMBOLS = (
     "kivi_b200_decode_workspace_bytes", "kivi_b200_decode_workspace_init", "kivi_b200_decode", "kivi_b200_decode_noalloc", "kivi_b200_gemv_f16",
     "kivi_b200_decode_step_workspace_bytes", "kivi_b200_decode_step", "kivi_b200_residual_rmsnorm",
     "kivi_b200_bias_rope", "kivi_b200_silu_mul", "kivi_b200_argmax",
+    "kivi_b200_p2p_region_bytes", "kivi_b200_p2p_region_create", "kivi_b200_p2p_region_open",
+    "kivi_b200_p2p_region_close", "kivi_b200_p2p_region_destroy", "kivi_b200_p2p_status",
 )
 
 

@@ -68,6 +68,7 @@ SplitPlan plan_split(const Geom& g, int n, int max_old_tokens) {
     chunk = ((chunk + gran - 1) / gran) * gran;
     sp.chunk_tokens = (int)chunk;
     sp.max_chunks = max_old_tokens > 0 ? (int)((max_old_tokens + chunk - 1) / chunk) : 1;
+    if (sp.max_chunks > 1) sp.max_chunks += 1;   // a split context gives the fp16 residual a CTA of its own
     return sp;
 }
 

@@ -24,11 +24,11 @@ __global__ void __launch_bounds__(256) decode_generic_kernel(const DecodeParams 
     const int seq_len = seq_len_of(p.seq, i);
     const DecodeBounds bnd = effective_bounds(p, seq_len);
     const int old_valid = bnd.old_valid;
-    const int nchunks = chunks_of(p, old_valid);
+    const ChunkWork work = chunk_work(p, bnd, chunk);
+    const int nchunks = work.nchunks;
     if (chunk >= nchunks) return;
-    const int t0 = chunk * p.chunk_tokens;
-    const int t1 = min(old_valid, t0 + p.chunk_tokens);
-    const bool with_residual = chunk == nchunks - 1;
+    const int t0 = work.tok0, t1 = work.tok1;
+    const bool with_residual = work.with_residual;
 
     const int* bt = p.seq.block_tables + (size_t)i * p.seq.bt_stride;
     const int slot = slot_of(p.seq, i);

@@ -149,12 +149,12 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
 
     const int seq_len = seq_len_of(p.seq, i);
     const DecodeBounds bnd = effective_bounds(p, seq_len);
-    const int nchunks = chunks_of(p, bnd.old_valid);
+    const ChunkWork work = chunk_work(p, bnd, chunk);
+    const int nchunks = work.nchunks;
     if (chunk >= nchunks) return;
-    const int tok0 = chunk * p.chunk_tokens;
-    const int tok1 = min(bnd.old_valid, tok0 + p.chunk_tokens);
+    const int tok0 = work.tok0, tok1 = work.tok1;
     const int ngroups = (tok1 - tok0) / G;
-    const int nres = (chunk == nchunks - 1) ? (bnd.res_valid + kResTile - 1) / kResTile : 0;
+    const int nres = work.with_residual ? (bnd.res_valid + kResTile - 1) / kResTile : 0;
 
     const int* bt = p.seq.block_tables + (size_t)i * p.seq.bt_stride;
     const int slot = slot_of(p.seq, i);

@@ -87,11 +87,13 @@ __global__ void __launch_bounds__(kGemvThreads, kGemvCtasPerSm) gemv_kernel(cons
         }
         __syncthreads();
     } else {
+        const unsigned char* slots = pro.gather.tp > 0 ? p2p_wait(pro.gather) : nullptr;   // every rank has delivered
         for (int c = threadIdx.x; c < BT * chunks; c += kGemvThreads) {
             const int b = c / chunks, cc = c - b * chunks;
             const size_t src = pro.tokens ? (size_t)pro.tokens[b] : (size_t)b;
             uint4 a = reinterpret_cast<const uint4*>(pro.x + src * in_dim)[cc];
-            if (pro.delta) a = hadd8(a, reinterpret_cast<const uint4*>(pro.delta + (size_t)b * in_dim)[cc]);
+            if (slots) a = hadd8(a, p2p_sum8(slots, pro.gather.slot_bytes, pro.gather.tp, (size_t)c));
+            else if (pro.delta) a = hadd8(a, reinterpret_cast<const uint4*>(pro.delta + (size_t)b * in_dim)[cc]);
             if (pro.x_out && blockIdx.x == 0) reinterpret_cast<uint4*>(pro.x_out + (size_t)b * in_dim)[cc] = a;
             xs[c] = a;
         }

@@ -27,12 +27,14 @@ namespace {
 // makes row i of x the embedding row tokens[i] (kernels.cu:4-7).
 __global__ void __launch_bounds__(kNormThreads) residual_rmsnorm_kernel(
     const __half* __restrict__ x, const int* __restrict__ tokens, const __half* __restrict__ delta,
-    const __half* __restrict__ weight, __half* __restrict__ x_out, __half* __restrict__ normed, int hidden, float eps) {
+    const __half* __restrict__ weight, __half* __restrict__ x_out, __half* __restrict__ normed, int hidden, float eps,
+    const P2pGather gather) {
     extern __shared__ __align__(16) unsigned char step_smem[];
     uint4* row = reinterpret_cast<uint4*>(step_smem);
     __shared__ float warp_sums[32];
     const int tid = threadIdx.x;
     pdl_trigger();
+    const unsigned char* slots = gather.tp > 0 ? p2p_wait(gather) : nullptr;
     const size_t src_row = tokens ? (size_t)tokens[blockIdx.x] : (size_t)blockIdx.x;
     const uint4* xs = reinterpret_cast<const uint4*>(x + src_row * hidden);
     const uint4* ds = delta ? reinterpret_cast<const uint4*>(delta + (size_t)blockIdx.x * hidden) : nullptr;
@@ -40,7 +42,8 @@ __global__ void __launch_bounds__(kNormThreads) residual_rmsnorm_kernel(
     const int vecs = hidden >> 3;
     for (int v = tid; v < vecs; v += kNormThreads) {
         uint4 a = xs[v];
-        if (ds) a = hadd8(a, ds[v]);
+        if (slots) a = hadd8(a, p2p_sum8(slots, gather.slot_bytes, gather.tp, (size_t)blockIdx.x * vecs + v));
+        else if (ds) a = hadd8(a, ds[v]);
         if (xo) xo[v] = a;
         row[v] = a;
     }
@@ -129,19 +132,22 @@ __global__ void __launch_bounds__(kArgmaxThreads) argmax_partial_kernel(
     }
 }
 
-// Second pass: one warp per row over `parts` candidates laid out [rank][row][chunk]
-// (rank stride = rows * chunks); the winner goes to out[row].
-__global__ void argmax_merge_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx, int chunks,
-                                    int ranks, int rows, int* __restrict__ out) {
+// Second pass: one warp per row over the candidates of every rank. Rank r's candidates start at
+// base + r * rank_stride: [rows][chunks] values, then at idx_off [rows][chunks] indices. With
+// gather.tp > 0 the candidates are the ranks' slots of that exchange site.
+__global__ void argmax_merge_kernel(const unsigned char* __restrict__ base, size_t rank_stride, size_t idx_off, int chunks,
+                                    int ranks, int rows, int* __restrict__ out, const P2pGather gather) {
+    if (gather.tp > 0) base = p2p_wait(gather);
     const int rowi = blockIdx.x;
     float best = -1e30f;
     int best_i = 0;
     const int total = chunks * ranks;
     for (int e = threadIdx.x; e < total; e += 32) {
         const int rk = e / chunks, ch = e - rk * chunks;
-        const size_t at = ((size_t)rk * rows + rowi) * chunks + ch;
-        const float v = part_val[at];
-        const int i = part_idx[at];
+        const unsigned char* rb = base + (size_t)rk * rank_stride;
+        const size_t at = (size_t)rowi * chunks + ch;
+        const float v = __ldcg(reinterpret_cast<const float*>(rb) + at);
+        const int i = __ldcg(reinterpret_cast<const int*>(rb + idx_off) + at);
         if (better(v, i, best, best_i)) { best = v; best_i = i; }
     }
     for (int off = 16; off > 0; off >>= 1) {
@@ -153,9 +159,11 @@ __global__ void argmax_merge_kernel(const float* __restrict__ part_val, const in
 }
 
 // Bookkeeping of a step: the decode sees the lengths after the append, the writer those before it.
-__global__ void step_begin_kernel(const int* __restrict__ seq_lens, int* __restrict__ lens_after, int n) {
+__global__ void step_begin_kernel(const int* __restrict__ seq_lens, int* __restrict__ lens_after, int n,
+                                  P2pHeader* header) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) lens_after[i] = seq_lens[i] + 1;
+    if (header && i == 0) header->step_no += 1u;   // the exchanges of this step carry this number
 }
 __global__ void step_end_kernel(int* __restrict__ seq_lens, int n) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -169,13 +177,15 @@ __half* H(kivi_f16* p) { return reinterpret_cast<__half*>(p); }
 int ok(cudaError_t e) { return e == cudaSuccess ? KIVI_OK : KIVI_ERR_CUDA; }
 
 int launch_residual_rmsnorm(const __half* x, const int* tokens, const __half* delta, const __half* weight,
-                            __half* x_out, __half* normed, int batch, int hidden, float eps, cudaStream_t stream) {
+                            __half* x_out, __half* normed, int batch, int hidden, float eps, const P2pGather& gather,
+                            cudaStream_t stream) {
     const size_t smem = (size_t)hidden * sizeof(__half);
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(residual_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return KIVI_ERR_CUDA;
     }
-    residual_rmsnorm_kernel<<<batch, kNormThreads, smem, stream>>>(x, tokens, delta, weight, x_out, normed, hidden, eps);
+    residual_rmsnorm_kernel<<<batch, kNormThreads, smem, stream>>>(x, tokens, delta, weight, x_out, normed, hidden, eps,
+                                                                   gather);
     return ok(cudaGetLastError());
 }
 
@@ -193,6 +203,9 @@ int launch_silu_mul(const __half* gate_up, __half* out, int batch, int ffn, cuda
 }
 
 int argmax_chunks(int n) { return (n + kArgmaxChunk - 1) / kArgmaxChunk; }
+size_t argmax_payload_bytes(int batch, int vocab) {
+    return ((size_t)batch * argmax_chunks(vocab) * (sizeof(float) + sizeof(int)) + 15) / 16 * 16;
+}
 
 // Projection y[b, :] = W x[b, :].
 int project(const __half* w, const __half* x, __half* y, int out_dim, int in_dim, int batch, cudaStream_t stream) {
@@ -207,14 +220,15 @@ int project(const __half* w, const __half* x, __half* y, int out_dim, int in_dim
 bool fuse_prologues(int batch) { return batch <= 4; }
 
 // y = W RMSNorm(x (+ delta)); the updated residual rows go to x_out.
-int project_add_norm(const __half* w, const __half* x, const int* tokens, const __half* delta, const __half* weight,
-                     __half* x_out, __half* normed_scratch, __half* y, int out_dim, int hidden, int batch, float eps,
-                     cudaStream_t stream) {
+int project_add_norm(const __half* w, const __half* x, const int* tokens, const __half* delta, const P2pGather& gather,
+                     const __half* weight, __half* x_out, __half* normed_scratch, __half* y, int out_dim, int hidden,
+                     int batch, float eps, cudaStream_t stream) {
     if (fuse_prologues(batch)) {
-        GemvPrologue pro = {x, tokens, delta, weight, x_out, eps};
+        GemvPrologue pro = {x, tokens, delta, gather, weight, x_out, eps};
         return ok(launch_gemv_fused(w, kGemvAddNorm, pro, y, nullptr, out_dim, hidden, batch, stream));
     }
-    const int rc = launch_residual_rmsnorm(x, tokens, delta, weight, x_out, normed_scratch, batch, hidden, eps, stream);
+    const int rc = launch_residual_rmsnorm(x, tokens, delta, weight, x_out, normed_scratch, batch, hidden, eps, gather,
+                                           stream);
     return rc != KIVI_OK ? rc : project(w, normed_scratch, y, out_dim, hidden, batch, stream);
 }
 
@@ -233,9 +247,8 @@ int project_silu_mul(const __half* w, const __half* gate_up, __half* mid_scratch
 size_t up256(size_t v) { return (v + 255) / 256 * 256; }
 
 struct StepLayout {
-    size_t x0, x1, normed, qkv, q, k, v, attn, proj, gate_up, mid, logits, lens_after, part_val, part_idx,
-        gather_val, gather_idx, decode_ws, total;
-    size_t decode_ws_bytes;
+    size_t x0, x1, normed, qkv, q, k, v, attn, proj, gate_up, mid, logits, lens_after, parts, gathered, decode_ws, total;
+    size_t decode_ws_bytes, parts_bytes;
 };
 
 int qkv_rows(const kivi_step_config& c) { return (c.num_q_heads + 2 * c.num_kv_heads) * c.head_dim; }
@@ -262,13 +275,18 @@ StepLayout step_layout(const kivi_step_config& c, const Geom& g, int batch, int 
     L.mid = take(n * c.ffn * h2);
     L.logits = take(n * c.vocab * h2);
     L.lens_after = take(n * sizeof(int));
-    const size_t parts = n * argmax_chunks(c.vocab);
-    L.part_val = take(parts * sizeof(float));
-    L.part_idx = take(parts * sizeof(int));
-    L.gather_val = take(parts * tp * sizeof(float));
-    L.gather_idx = take(parts * tp * sizeof(int));
+    L.parts_bytes = argmax_payload_bytes(batch, c.vocab);   // [values | indices] of this rank's arg-max candidates
+    L.parts = take(L.parts_bytes);
+    L.gathered = take(L.parts_bytes * tp);
     L.total = at;
     return L;
+}
+
+// Largest payload one rank delivers at an exchange site: a projection [batch, H] or its arg-max candidates.
+size_t step_exchange_payload(const kivi_step_config& c, int batch) {
+    const size_t proj = (size_t)batch * c.hidden * sizeof(__half);
+    const size_t cand = argmax_payload_bytes(batch, c.vocab);
+    return proj > cand ? proj : cand;
 }
 
 int check_step_config(const kivi_step_config* c) {
@@ -314,6 +332,11 @@ extern "C" size_t kivi_b200_decode_step_workspace_bytes(const kivi_step_config* 
     return step_layout(*cfg, make_geom(gs), batch, max_seq_len).total;
 }
 
+extern "C" size_t kivi_b200_p2p_region_bytes(const kivi_step_config* cfg, int batch) {
+    if (check_step_config(cfg) != KIVI_OK || batch <= 0 || batch > 64 || cfg->tp_size > kMaxTp) return 0;
+    return p2p_layout(cfg->tp_size, 2 * cfg->layers + 1, step_exchange_payload(*cfg, batch)).total;
+}
+
 extern "C" int kivi_b200_decode_step(const kivi_step_config* cfg, const kivi_step_weights* weights,
                                      const kivi_step_state* state, const int32_t* tokens_in, int batch, int max_seq_len,
                                      int32_t* tokens_out, kivi_f16* logits_out, const kivi_step_comm* comm,
@@ -326,7 +349,10 @@ extern "C" int kivi_b200_decode_step(const kivi_step_config* cfg, const kivi_ste
     if (batch < 1 || batch > 64 || max_seq_len < 1 || max_seq_len > 0x3fffffff) return KIVI_ERR_RANGE;
     const kivi_step_config& c = *cfg;
     const bool tp = c.tp_size > 1;
-    if (tp && (!comm || !comm->allreduce_f16 || !comm->allgather)) return KIVI_ERR_NULL_POINTER;
+    if (tp && !comm) return KIVI_ERR_NULL_POINTER;
+    const bool p2p = tp && comm->peer_regions != nullptr;
+    if (tp && !p2p && (!comm->allreduce_f16 || !comm->allgather)) return KIVI_ERR_NULL_POINTER;
+    if (c.tp_size > kMaxTp && p2p) return KIVI_ERR_GEOMETRY;
     kivi_geometry gs = step_geometry(c);
     rc = kivi_b200_validate_geometry(&gs, nullptr);
     if (rc != KIVI_OK) return rc;
@@ -357,7 +383,50 @@ extern "C" int kivi_b200_decode_step(const kivi_step_config* cfg, const kivi_ste
 
 #define KIVI_STEP_TRY(expr) do { const int rc__ = (expr); if (rc__ != KIVI_OK) return rc__; } while (0)
 
-    step_begin_kernel<<<(batch + 127) / 128, 128, 0, stream>>>(state->seq_lens, lens_after, batch);
+    // ---- exchange between ranks: sites 2l (after o_proj), 2l + 1 (after down_proj), 2L (arg-max) ----
+    const P2pLayout pl = p2p_layout(c.tp_size, 2 * c.layers + 1, step_exchange_payload(c, batch));
+    unsigned char* own = p2p ? static_cast<unsigned char*>(comm->peer_regions[c.tp_rank]) : nullptr;
+    if (p2p) {
+        if (comm->region_bytes < pl.total) return KIVI_ERR_WORKSPACE;
+        for (int r = 0; r < c.tp_size; ++r)
+            if (!comm->peer_regions[r] || !aligned16(comm->peer_regions[r])) return KIVI_ERR_NULL_POINTER;
+    }
+    P2pHeader* header = reinterpret_cast<P2pHeader*>(own);
+    auto gather_at = [&](int site) {
+        P2pGather ga = {};
+        if (!p2p) return ga;            // tp = 0: the consumer reads its plain local input
+        ga.flags = reinterpret_cast<const unsigned*>(own + pl.flags_off) + (size_t)site * c.tp_size;
+        ga.header = header;
+        ga.status = &header->status;
+        ga.slots = own + pl.slots_off;
+        ga.slot_bytes = pl.slot_bytes;
+        ga.tp = c.tp_size;
+        ga.site = site;
+        ga.spin_limit = comm->spin_limit ? comm->spin_limit : kP2pSpinLimit;
+        return ga;
+    };
+    // all-reduce of `buf` at `site`: hooks reduce in place now; peer memory pushes now and sums in the consumer
+    auto exchange = [&](__half* buf, size_t bytes, int site) -> int {
+        if (!tp) return KIVI_OK;
+        if (!p2p)
+            return comm->allreduce_f16(comm->user, reinterpret_cast<kivi_f16*>(buf), bytes / 2, stream) ? KIVI_ERR_CUDA
+                                                                                                          : KIVI_OK;
+        P2pPush ps = {};
+        for (int r = 0; r < c.tp_size; ++r) {
+            unsigned char* peer = static_cast<unsigned char*>(comm->peer_regions[r]);
+            ps.slot[r] = peer + pl.slots_off + (size_t)c.tp_rank * pl.slot_bytes;
+            ps.flag[r] = reinterpret_cast<unsigned*>(peer + pl.flags_off) + (size_t)site * c.tp_size + c.tp_rank;
+        }
+        ps.header = header;
+        ps.arrive = &header->arrive;
+        ps.half_stride = (size_t)c.tp_size * pl.slot_bytes;
+        ps.tp = c.tp_size;
+        ps.site = site;
+        return ok(launch_p2p_push(buf, bytes, ps, stream));
+    };
+    const size_t proj_bytes = (size_t)batch * c.hidden * sizeof(__half);
+
+    step_begin_kernel<<<(batch + 127) / 128, 128, 0, stream>>>(state->seq_lens, lens_after, batch, p2p ? header : nullptr);
     KIVI_STEP_TRY(ok(cudaGetLastError()));
 
     SeqAddressing wa;   // writer: lengths before the append
@@ -368,13 +437,14 @@ extern "C" int kivi_b200_decode_step(const kivi_step_config* cfg, const kivi_ste
     da.seq_lens = lens_after;
 
     const __half* delta = nullptr;           // projection waiting to be added to the residual stream
+    int delta_site = -1;                     // ... and, with peer memory, the exchange site its partials went to
     const int* embed_tokens = tokens_in;     // layer 0 reads its rows from the embedding table
     for (int l = 0; l < c.layers; ++l) {
         const kivi_layer_weights& lw = weights->layers[l];
         // attention block
         KIVI_STEP_TRY(project_add_norm(H(lw.qkv), embed_tokens ? H(weights->embed) : x_cur, embed_tokens, delta,
-                                       H(lw.attn_norm), x_nxt, normed, qkv, qkv_rows(c), c.hidden, batch, c.norm_eps,
-                                       stream));
+                                       delta_site >= 0 ? gather_at(delta_site) : P2pGather{}, H(lw.attn_norm), x_nxt,
+                                       normed, qkv, qkv_rows(c), c.hidden, batch, c.norm_eps, stream));
         embed_tokens = nullptr;
         { __half* t = x_cur; x_cur = x_nxt; x_nxt = t; }
         KIVI_STEP_TRY(launch_bias_rope(qkv, c.attn_bias ? H(lw.qkv_bias) : nullptr, state->seq_lens, q, k, v, batch,
@@ -386,40 +456,45 @@ extern "C" int kivi_b200_decode_step(const kivi_step_config* cfg, const kivi_ste
         KIVI_STEP_TRY(run_decode(g, wp.cache, da, q, nullptr, attn, batch, max_seq_len, max_old, -1, decode_ws,
                                  L.decode_ws_bytes, stream));
         KIVI_STEP_TRY(project(H(lw.o), attn, proj, c.hidden, q_dim, batch, stream));
-        if (tp && comm->allreduce_f16(comm->user, reinterpret_cast<kivi_f16*>(proj), (size_t)batch * c.hidden, stream))
-            return KIVI_ERR_CUDA;
+        KIVI_STEP_TRY(exchange(proj, proj_bytes, 2 * l));
         // feed-forward block
-        KIVI_STEP_TRY(project_add_norm(H(lw.gate_up), x_cur, nullptr, proj, H(lw.ffn_norm), x_nxt, normed, gate_up,
-                                       2 * c.ffn, c.hidden, batch, c.norm_eps, stream));
+        KIVI_STEP_TRY(project_add_norm(H(lw.gate_up), x_cur, nullptr, proj, gather_at(2 * l), H(lw.ffn_norm), x_nxt,
+                                       normed, gate_up, 2 * c.ffn, c.hidden, batch, c.norm_eps, stream));
         { __half* t = x_cur; x_cur = x_nxt; x_nxt = t; }
         // the down projection must not overwrite `proj` while a gate_up CTA may still read it as delta:
         // it cannot, every gate_up CTA has finished its prologue before the first down CTA passes its wait
         KIVI_STEP_TRY(project_silu_mul(H(lw.down), gate_up, mid, proj, c.hidden, c.ffn, batch, stream));
-        if (tp && comm->allreduce_f16(comm->user, reinterpret_cast<kivi_f16*>(proj), (size_t)batch * c.hidden, stream))
-            return KIVI_ERR_CUDA;
+        KIVI_STEP_TRY(exchange(proj, proj_bytes, 2 * l + 1));
         delta = proj;
+        delta_site = p2p ? 2 * l + 1 : -1;
     }
-    KIVI_STEP_TRY(project_add_norm(H(weights->lm_head), x_cur, nullptr, delta, H(weights->final_norm), x_nxt, normed,
-                                   logits, c.vocab, c.hidden, batch, c.norm_eps, stream));
+    KIVI_STEP_TRY(project_add_norm(H(weights->lm_head), x_cur, nullptr, delta,
+                                   delta_site >= 0 ? gather_at(delta_site) : P2pGather{}, H(weights->final_norm), x_nxt,
+                                   normed, logits, c.vocab, c.hidden, batch, c.norm_eps, stream));
 
+    // arg-max: candidates per 8192-entry slice on every rank, [values | indices]; the ranks' candidates meet
+    // through the hook's all-gather or through the last exchange site, and every rank picks the same winner
     const int chunks = argmax_chunks(c.vocab);
-    float* part_val = reinterpret_cast<float*>(ws + L.part_val);
-    int* part_idx = reinterpret_cast<int*>(ws + L.part_idx);
-    argmax_partial_kernel<<<dim3(chunks, batch), kArgmaxThreads, 0, stream>>>(logits, c.vocab, c.vocab_offset, part_val,
-                                                                             part_idx);
+    unsigned char* parts = ws + L.parts;
+    const size_t idx_off = (size_t)batch * chunks * sizeof(float);
+    argmax_partial_kernel<<<dim3(chunks, batch), kArgmaxThreads, 0, stream>>>(
+        logits, c.vocab, c.vocab_offset, reinterpret_cast<float*>(parts), reinterpret_cast<int*>(parts + idx_off));
     KIVI_STEP_TRY(ok(cudaGetLastError()));
-    const float* all_val = part_val;
-    const int* all_idx = part_idx;
-    if (tp) {
-        float* gv = reinterpret_cast<float*>(ws + L.gather_val);
-        int* gi = reinterpret_cast<int*>(ws + L.gather_idx);
-        const size_t per_rank = (size_t)batch * chunks;
-        if (comm->allgather(comm->user, part_val, gv, per_rank * sizeof(float), stream)) return KIVI_ERR_CUDA;
-        if (comm->allgather(comm->user, part_idx, gi, per_rank * sizeof(int), stream)) return KIVI_ERR_CUDA;
-        all_val = gv;
-        all_idx = gi;
+    const unsigned char* cand = parts;
+    size_t rank_stride = 0;
+    P2pGather cand_gather = {};
+    if (p2p) {
+        KIVI_STEP_TRY(exchange(reinterpret_cast<__half*>(parts), L.parts_bytes, 2 * c.layers));
+        cand_gather = gather_at(2 * c.layers);
+        rank_stride = pl.slot_bytes;
+    } else if (tp) {
+        unsigned char* gathered = ws + L.gathered;
+        if (comm->allgather(comm->user, parts, gathered, L.parts_bytes, stream)) return KIVI_ERR_CUDA;
+        cand = gathered;
+        rank_stride = L.parts_bytes;
     }
-    argmax_merge_kernel<<<batch, 32, 0, stream>>>(all_val, all_idx, chunks, tp ? c.tp_size : 1, batch, tokens_out);
+    argmax_merge_kernel<<<batch, 32, 0, stream>>>(cand, rank_stride, idx_off, chunks, tp ? c.tp_size : 1, batch, tokens_out,
+                                                  cand_gather);
     KIVI_STEP_TRY(ok(cudaGetLastError()));
     step_end_kernel<<<(batch + 127) / 128, 128, 0, stream>>>(state->seq_lens, batch);
     return ok(cudaGetLastError());
@@ -436,7 +511,7 @@ extern "C" int kivi_b200_residual_rmsnorm(const kivi_f16* x, const kivi_f16* del
         return KIVI_ERR_ALIGNMENT;
     if (batch == 0) return KIVI_OK;
     return launch_residual_rmsnorm(H(x), nullptr, delta ? H(delta) : nullptr, H(weight), x_out ? H(x_out) : nullptr,
-                                   H(normed), batch, hidden, eps, stream);
+                                   H(normed), batch, hidden, eps, P2pGather{}, stream);
 }
 
 extern "C" int kivi_b200_bias_rope(const kivi_f16* qkv, const kivi_f16* bias, const int32_t* positions, kivi_f16* q,
@@ -470,6 +545,8 @@ extern "C" int kivi_b200_argmax(const kivi_f16* logits, int32_t* out_index, int 
     int* pi = reinterpret_cast<int*>(pv + (size_t)batch * chunks);
     argmax_partial_kernel<<<dim3(chunks, batch), kArgmaxThreads, 0, stream>>>(H(logits), n, 0, pv, pi);
     if (cudaGetLastError() != cudaSuccess) return KIVI_ERR_CUDA;
-    argmax_merge_kernel<<<batch, 32, 0, stream>>>(pv, pi, chunks, 1, batch, out_index);
+    argmax_merge_kernel<<<batch, 32, 0, stream>>>(reinterpret_cast<const unsigned char*>(pv), 0,
+                                                  (size_t)batch * chunks * sizeof(float), chunks, 1, batch, out_index,
+                                                  P2pGather{});
     return ok(cudaGetLastError());
 }

@@ -3,6 +3,7 @@
 // (crates/jac-codegen-cuda/src/templates/kernels.cu) so that both forms give the reference's bits.
 #pragma once
 #include "kivi_common.cuh"
+#include "p2p.cuh"
 
 namespace kivi {
 
@@ -68,6 +69,7 @@ struct GemvPrologue {
     const __half* x;        // plain: [batch, in]; add+norm: residual rows (or a table with `tokens`); silu: [batch, 2 * in] gate|up
     const int* tokens;      // add+norm: optional row gather (embedding lookup)
     const __half* delta;    // add+norm: optional [batch, in] added first
+    P2pGather gather;       // add+norm: when gather.tp > 0 the delta is the sum of the ranks' slots of that site instead
     const __half* weight;   // add+norm: [in]
     __half* x_out;          // add+norm: optional [batch, in], the updated residual rows (written once)
     float eps;

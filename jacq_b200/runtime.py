@@ -6,8 +6,10 @@ per token. ``DecodeRuntime`` is the same thing for a batch of sequences on one G
 a KV-head tensor-parallel group): it keeps the weights in the reference's file layout, one
 ``KiviCache`` page pool per layer, the block tables and sequence lengths on the device, and runs a
 whole step with one library call, optionally replayed from a CUDA graph. With ``world > 1`` the
-two all-reduces per layer and the arg-max gather go through ``torch.distributed`` (NCCL) on the
-step's stream, called back from the library.
+two all-reduces per layer and the arg-max gather go either through ``torch.distributed`` (NCCL) on
+the step's stream, called back from the library (``comm="nccl"``), or through the library's own
+peer-memory exchange over NVLink (``comm="p2p"``: plain peer stores, flags, the sum fused into the
+consuming kernel).
 
 torch is plumbing here (device memory, streams, process group); all arithmetic is in
 libjacq_kivi_b200.so.
@@ -179,7 +181,7 @@ class DecodeRuntime:
 
     def __init__(self, cfg: DecodeModelConfig, weights: dict[str, object], *, batch: int, max_seq_len: int,
                  device: torch.device | str = "cuda", rank: int = 0, world: int = 1, group=None,
-                 block_tables: torch.Tensor | None = None):
+                 block_tables: torch.Tensor | None = None, comm: str = "nccl"):
         self.cfg, self.batch, self.max_seq_len = cfg, batch, max_seq_len
         self.device = torch.device(device)
         if self.device.type != "cuda":
@@ -229,7 +231,15 @@ class DecodeRuntime:
             None, self.workspace.data_ptr(), need)
         self.tokens = torch.zeros((batch,), dtype=torch.int32, device=self.device)
         self.logits = torch.empty((batch, cfg.vocab // world), dtype=torch.float16, device=self.device)
-        self._comm = self._make_comm() if world > 1 else None
+        if comm not in ("nccl", "p2p"):
+            raise ValueError("comm must be 'nccl' (torch.distributed hooks) or 'p2p' (the library's peer-memory exchange)")
+        self.comm_kind = comm
+        self._region = None
+        self._peer_regions: list[int] = []
+        if world > 1:
+            self._comm = self._make_p2p_comm() if comm == "p2p" else self._make_comm()
+        else:
+            self._comm = None
         self._graph: torch.cuda.CUDAGraph | None = None
 
     def _to_device(self, weights: dict[str, object]) -> dict[str, object]:
@@ -272,6 +282,61 @@ class DecodeRuntime:
 
         self._callbacks = (_native.ALLREDUCE_F16_FN(allreduce), _native.ALLGATHER_FN(allgather))  # keep alive
         return _native.KiviStepComm(self._callbacks[0], self._callbacks[1], None)
+
+    def _make_p2p_comm(self) -> _native.KiviStepComm:
+        """Create this rank's exchange region, swap IPC handles over the process group (host side,
+        once) and map every peer's region. No collective library is involved in a step afterwards."""
+        import torch.distributed as dist
+
+        lib = _native.lib()
+        nbytes = int(lib.kivi_b200_p2p_region_bytes(ctypes.byref(self._cfg_struct), self.batch))
+        if nbytes == 0:
+            raise RuntimeError("kivi_b200_p2p_region_bytes rejected the configuration")
+        region = ctypes.c_void_p()
+        handle = (ctypes.c_ubyte * _native.P2P_HANDLE_BYTES)()
+        _native.check(lib.kivi_b200_p2p_region_create(nbytes, ctypes.byref(region), handle), "kivi_b200_p2p_region_create")
+        self._region = region.value
+        handles: list[bytes | None] = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle), group=self.group)
+        ptrs = (ctypes.c_void_p * self.world)()
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                ptrs[r] = self._region
+                continue
+            peer = ctypes.c_void_p()
+            buf = (ctypes.c_ubyte * _native.P2P_HANDLE_BYTES).from_buffer_copy(h)
+            _native.check(lib.kivi_b200_p2p_region_open(buf, ctypes.byref(peer)), "kivi_b200_p2p_region_open")
+            ptrs[r] = peer.value
+            self._peer_regions.append(peer.value)
+        self._peer_array = ptrs   # keep alive
+        dist.barrier(group=self.group)   # every region is mapped everywhere before anybody pushes
+        null_ar = ctypes.cast(None, _native.ALLREDUCE_F16_FN)
+        null_ag = ctypes.cast(None, _native.ALLGATHER_FN)
+        return _native.KiviStepComm(null_ar, null_ag, None, ptrs, nbytes, 0)
+
+    def exchange_status(self) -> int:
+        """0 when every wait of the peer-memory exchange was served; bit r set when a wait for
+        rank r ran out of polls (the step's result is then undefined)."""
+        if self._region is None:
+            return 0
+        out = ctypes.c_uint32(0)
+        _native.check(_native.lib().kivi_b200_p2p_status(self._region, ctypes.byref(out), _stream_ptr(self.device)),
+                      "kivi_b200_p2p_status")
+        return int(out.value)
+
+    def close(self) -> None:
+        """Unmap the peers' regions and free this rank's (call on every rank, after the last step)."""
+        lib = _native.lib()
+        torch.cuda.synchronize(self.device)
+        for p in self._peer_regions:
+            lib.kivi_b200_p2p_region_close(p)
+        self._peer_regions = []
+        if self._region is not None:
+            if self.group is not None:
+                import torch.distributed as dist
+                dist.barrier(group=self.group)   # nobody frees while a peer still has the mapping open
+            lib.kivi_b200_p2p_region_destroy(self._region)
+            self._region = None
 
     # ---- stepping -----------------------------------------------------------------------------
     def set_seq_lens(self, lens) -> None:

@@ -369,3 +369,46 @@ def test_step_tensor_parallel_two_ranks_on_one_gpu(native_lib):
         assert np.array_equal(results[0][clear], want_tok[clear])
         assert np.array_equal(single_tok[clear], want_tok[clear])
         tok = want_tok.astype(np.int32)
+
+
+def test_peer_exchange_wait_is_bounded(native_lib):
+    """Rank 0 of a two-rank peer-memory step whose peer never delivers: every wait runs out of its
+    (shortened) poll budget, the step returns, and the status word names the missing rank. Both
+    regions live on this GPU and nothing ever writes the second rank's flags."""
+    import ctypes
+    from jacq_b200 import _native
+    from jacq_b200.runtime import DecodeRuntime, shard_layer
+    from tests.gpu_utils import DEV
+    world, batch = 2, 2
+    w = so.random_weights(TINY, 31)
+    cfg, tw = _config(TINY), _torch_weights(w)
+    shard = {"embed": tw["embed"], "final_norm": tw["final_norm"], "lm_head": tw["lm_head"][: TINY.vocab // world],
+             "layers": [shard_layer(cfg, lw, 0, world) for lw in tw["layers"]]}
+    rt = DecodeRuntime.__new__(DecodeRuntime)
+    rt._make_comm = lambda: None                      # built by hand below
+    DecodeRuntime.__init__(rt, cfg, shard, batch=batch, max_seq_len=160, device=DEV, rank=0, world=world, group=object())
+    lib = native_lib
+    nbytes = int(lib.kivi_b200_p2p_region_bytes(ctypes.byref(rt._cfg_struct), batch))
+    assert nbytes > 0
+    regions = []
+    for _ in range(world):
+        region = ctypes.c_void_p()
+        handle = (ctypes.c_ubyte * _native.P2P_HANDLE_BYTES)()
+        _native.check(lib.kivi_b200_p2p_region_create(nbytes, ctypes.byref(region), handle), "region_create")
+        regions.append(region.value)
+    ptrs = (ctypes.c_void_p * world)(*regions)
+    rt._region = regions[0]
+    rt._comm = _native.KiviStepComm(ctypes.cast(None, _native.ALLREDUCE_F16_FN), ctypes.cast(None, _native.ALLGATHER_FN),
+                                    None, ptrs, nbytes, 2000)
+    assert rt.exchange_status() == 0
+    rt.step(torch.tensor([1, 2]))
+    torch.cuda.synchronize()
+    assert rt.exchange_status() == 0b10              # rank 1 never delivered; rank 0's own pushes were seen
+    assert torch.equal(rt.seq_lens.cpu(), torch.tensor([1, 1], dtype=torch.int32))
+    # a region that is too small is refused before anything is launched
+    rt._comm.region_bytes = nbytes - 256
+    with pytest.raises(_native.KiviStatusError):
+        rt.step(torch.tensor([1, 2]))
+    for r in regions:
+        lib.kivi_b200_p2p_region_destroy(r)
+    rt._region = None

@@ -1,6 +1,9 @@
-"""KV-head tensor parallelism of the decode step over NCCL: two ranks, one process per GPU.
-Skipped on a single-GPU box (the one-GPU suite covers the same library path with host-side
-collectives in tests/test_step_gpu.py)."""
+"""KV-head tensor parallelism of the decode step on two GPUs, one process per GPU: once with the
+collectives on NCCL (torch.distributed hooks), once on the library's own peer-memory exchange
+(plain peer stores over NVLink, flags, the sum fused into the consuming kernel). NVLS is off and
+no multimem instruction is used, so a rank that fails cannot fault its peer's GPU. Skipped on a
+single-GPU box; tests/test_step_gpu.py covers the same library path there with host-side
+collectives and the bounded wait of the exchange."""
 import os
 import subprocess
 import sys
@@ -14,12 +17,13 @@ pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
 
 
-def test_two_rank_step_over_nccl(native_lib):
+@pytest.mark.parametrize("comm", ["nccl", "p2p"])
+def test_two_rank_step(native_lib, comm):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
-           "127.0.0.1", "--master-port", "29611", str(ROOT / "tests" / "tp_worker.py")]
+           "127.0.0.1", "--master-port", "29611" if comm == "nccl" else "29612", str(ROOT / "tests" / "tp_worker.py"), comm]
     proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     out = proc.stdout + proc.stderr
     assert proc.returncode == 0, out[-4000:]

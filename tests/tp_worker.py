@@ -1,6 +1,6 @@
 """One rank of the tensor-parallel decode-step test (launched by tests/test_step_tp_gpu.py through
 torch.distributed.run, one process per GPU, NCCL). Each rank runs the library step on its shard with
-the all-reduce / all-gather hooks on NCCL and checks its slice of the logits against the two-rank
+the collectives on NCCL hooks ("nccl") or on the library's peer-memory exchange ("p2p") and checks its slice of the logits against the two-rank
 CPU oracle; half-way through it switches to CUDA-graph replay."""
 import os
 import sys
@@ -21,6 +21,7 @@ TINY = so.StepShape(layers=2, hidden=256, nh=4, nkv=2, hd=64, ffn=512, vocab=102
 
 
 def main():
+    comm = sys.argv[1] if len(sys.argv) > 1 else "nccl"
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     device = torch.device(f"cuda:{int(os.environ['LOCAL_RANK'])}")
     torch.cuda.set_device(device)
@@ -39,7 +40,7 @@ def main():
              "layers": [shard_layer(cfg, {k: (None if v is None else torch.from_numpy(v)) for k, v in lw.items()},
                                     rank, world) for lw in w.layers]}
     rt = DecodeRuntime(cfg, shard, batch=batch, max_seq_len=per_seq * s.block + s.residual, device=device, rank=rank,
-                       world=world, group=dist.group.WORLD, block_tables=torch.from_numpy(bt))
+                       world=world, group=dist.group.WORLD, block_tables=torch.from_numpy(bt), comm=comm)
     dist.all_reduce(torch.zeros(8, device=device, dtype=torch.float16))   # communicator up before any capture
     tok = np.array([4, 99, 512], np.int32)
     worst = 0.0
@@ -58,8 +59,10 @@ def main():
         assert np.array_equal(got_tok[clear], want_tok[clear]), f"rank {rank} step {i}"
         tok = want_tok.astype(np.int32)
     assert np.array_equal(rt.seq_lens.cpu().numpy(), np.full(batch, steps, np.int32))
+    assert rt.exchange_status() == 0, "a peer-memory wait ran out of polls"
+    rt.close()
     dist.barrier()
-    print(f"TP_WORKER_OK rank={rank} worst_abs_err={worst:.3e}", flush=True)
+    print(f"TP_WORKER_OK comm={comm} rank={rank} worst_abs_err={worst:.3e}", flush=True)
     dist.destroy_process_group()
 
 
