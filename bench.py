@@ -664,12 +664,96 @@ def run_reference_cuda_lane(args):
     }))
 
 
+def run_reference_step(args):
+    """Reference arm of the decode-step workloads. The reference's generated runtime is CUDA only, so
+    two things are timed: (1) the CPU port of the step (oracle/step_oracle.py, all host threads) on
+    a bounded sample -- 2 of the 48 layers at batch 1 and a 4096-token context, scaled to a whole step;
+    (2) where oracle/_ref holds it, the reference's own forward() (templates/runtime.cu, fp16 dense
+    KV cache, cuBLAS GEMVs, one token per call) compiled unmodified for the same model shape, at
+    the workload's context; it has no batch form, so a batch costs that many calls."""
+    import ctypes
+    from oracle import step_oracle as so
+    batch, context = STEP_WORKLOADS[args.workload]
+    _, _, world = _dist_env()
+    nthreads = os.cpu_count() or 1
+    layers_sampled, ctx_sampled = 2, 4096
+    shape = so.StepShape(layers=layers_sampled, hidden=5120, nh=40, nkv=8, hd=128, ffn=13824, vocab=8192,
+                         rope_base=1000000.0, norm_eps=1e-6, attn_bias=True, block=16, group=128, residual=128)
+    w = so.random_weights(shape, 1)
+    pages = (ctx_sampled - shape.residual) // shape.block + 2
+    oracle = so.StepOracle(shape, w, np.arange(pages, dtype=np.int32).reshape(1, pages), pages, gemv_threads=nthreads)
+    rng = np.random.default_rng(2)
+    from oracle import kivi_oracle as ko
+    for cache in oracle.caches[0]:       # synthetic context through the oracle writer
+        k = rng.standard_normal((ctx_sampled, shape.nkv, shape.hd), dtype=np.float32).astype(np.float16)
+        v = rng.standard_normal((ctx_sampled, shape.nkv, shape.hd), dtype=np.float32).astype(np.float16)
+        ko.write_batch(cache, k, v, oracle.block_tables, np.zeros(1, np.int32), np.array([0, ctx_sampled], np.int32),
+                       nthreads=nthreads)
+    oracle.seq_lens[:] = ctx_sampled
+    tok = np.array([11])
+    oracle.step(tok)
+    t0 = time.perf_counter()
+    steps = max(1, min(args.steps, 3))
+    for _ in range(steps):
+        oracle.step(tok)
+    sample_s = (time.perf_counter() - t0) / steps
+    cpu_step_s = sample_s * 48 / layers_sampled           # layers dominate; the 8192-row lm_head sample rides along
+    cpu_value = 1.0 / cpu_step_s
+    sample = (f"{layers_sampled} of 48 layers, batch 1, context {ctx_sampled}, vocab 8192, scaled by 48/{layers_sampled}; "
+              "scalar C + OpenMP")
+    ref_cuda = None
+    lib_path = ROOT / "oracle" / "_ref" / "libjacq_ref.so"
+    import torch
+    if lib_path.exists() and torch.cuda.is_available():
+        from jacq_b200.runtime import DecodeModelConfig, random_layer
+        ref = ctypes.CDLL(str(lib_path))
+        ref.ref_q14b_time_steps.restype = ctypes.c_float
+        ref.ref_q14b_set_weights.restype = ctypes.c_int
+        device = torch.device("cuda:0")
+        torch.cuda.set_device(device)
+        cfg = DecodeModelConfig.qwen25_14b()
+        gen = torch.Generator(device=device).manual_seed(1234)
+        big = lambda r, c: (torch.randn((r, c), generator=gen, device=device, dtype=torch.float32) * 0.02).half()
+        keep = [big(cfg.vocab, cfg.hidden), (1.0 + 0.1 * torch.randn((cfg.hidden,), generator=gen, device=device)).half(),
+                big(cfg.vocab, cfg.hidden)]
+        ptrs = (ctypes.c_void_p * (7 * cfg.layers))()
+        for l in range(cfg.layers):
+            lw = random_layer(cfg, gen, device)
+            for j, kname in enumerate(("attn_norm", "qkv", "qkv_bias", "o", "ffn_norm", "gate_up", "down")):
+                keep.append(lw[kname])
+                ptrs[7 * l + j] = lw[kname].data_ptr()
+        torch.cuda.synchronize()
+        if ref.ref_q14b_set_weights(ctypes.c_void_p(keep[0].data_ptr()), ctypes.c_void_p(keep[1].data_ptr()),
+                                    ctypes.c_void_p(keep[2].data_ptr()), ptrs) == 0:
+            warm = max(1, min(args.warmup, 3))
+            k_steps = max(1, min(args.steps, 20))
+            pos = context - warm - k_steps - 1
+            ref.ref_q14b_time_steps(ctypes.c_int(11), ctypes.c_int(pos), ctypes.c_int(warm))
+            ms = float(ref.ref_q14b_time_steps(ctypes.c_int(11), ctypes.c_int(pos + warm), ctypes.c_int(k_steps))) / k_steps
+            ref_cuda = {"ms_per_token": ms, "tokens_per_s": 1000.0 / ms, "context": context,
+                        "what": "reference forward() + argmax_kernel, fp16 dense KV cache, cuBLAS GEMVs, one token per call"}
+    value = ref_cuda["tokens_per_s"] if ref_cuda else cpu_value
+    print(json.dumps({
+        "impl": "reference", "metric": "decode-step tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": batch * 1000.0 / value, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16" if ref_cuda else "f32 scalar", "data": "synthetic",
+        "config": {"workload": args.workload, "note": "value = the reference's own CUDA forward() on this GPU when "
+                   "oracle/_ref is present (it serves one sequence per call, so a batch is served at the same tokens/s), "
+                   "else the CPU port"},
+        "reference_cuda": ref_cuda,
+        "cpu_baseline": {"value": cpu_value, "unit": "tokens/s", "cores": nthreads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
 def run_reference(args):
     """Reference arm: the CPU port of the reference's writer + decode math, all host threads, no GPU.
     At the reference's own lane the reference's CUDA itself is timed instead."""
     rank, local_rank, world = _dist_env()
     if rank != 0:
         return
+    if args.workload in STEP_WORKLOADS:
+        return run_reference_step(args)
     if WORKLOADS[args.workload][0] == "reflane":
         return run_reference_cuda_lane(args)
     from tests import helpers

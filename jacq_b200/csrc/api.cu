@@ -4,6 +4,7 @@
 #include <cstdio>
 #include <cstdlib>
 
+#include "decode_merge.cuh"
 #include "kivi_common.cuh"
 
 namespace kivi {
@@ -113,6 +114,7 @@ int run_decode(const Geom& g, const CachePtrs& cache, const SeqAddressing& seq, 
     p.ws_o = base ? reinterpret_cast<float*>(base + wl.o_off) : nullptr;
     cudaError_t e = decode_mma_supports(g, retained_pages) ? launch_decode_mma(p, stream)
                                                            : launch_decode_generic(p, stream);
+    if (e == cudaSuccess) e = launch_decode_merge(p, stream);   // nothing to do unless the plan splits the context
     return e == cudaSuccess ? KIVI_OK : KIVI_ERR_CUDA;
 }
 

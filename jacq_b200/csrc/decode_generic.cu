@@ -167,7 +167,6 @@ __global__ void __launch_bounds__(256) decode_generic_kernel(const DecodeParams 
             }
         }
     }
-    if (nchunks > 1) merge_when_last<1>(p, i, kv, nchunks, nullptr, 0);
 }
 
 }  // namespace

@@ -99,6 +99,23 @@ struct Cfg {
     static_assert(NMMA == UNITS * MPU, "value MMA bookkeeping");
 };
 
+#ifdef KIVI_DECODE_TRACE
+// Debug builds only: per-CTA time stamps (globaltimer, ns) of the kernel's phases, read back by a
+// tuning script through kivi_debug_decode_trace(). Not compiled into the product library.
+__device__ unsigned long long g_decode_trace[4096 * 8];
+__device__ __forceinline__ void trace_mark(int slot) {
+    if (threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+        if (cta < 4096) g_decode_trace[cta * 8 + slot] = t;
+    }
+}
+#define KIVI_TRACE(slot) trace_mark(slot)
+#else
+#define KIVI_TRACE(slot)
+#endif
+
 // MMA row rho (0..7) of a 16-token tile holds token rho ^ ((rho >> 1) & 1); rows 8..15 add 8.
 // With this pair swap the 16-byte key loads of a quarter warp touch rows of both parities.
 __device__ __forceinline__ int row_token(int rho) { return rho ^ ((rho >> 1) & 1); }
@@ -143,6 +160,7 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
     const Geom& g = p.geom;
     const int i = blockIdx.z, kv = blockIdx.y, chunk = blockIdx.x;
     pdl_trigger();   // a projection launched behind this kernel may start streaming its weights
+    KIVI_TRACE(0);
     // the warp index through a broadcast, so that everything derived from it is known to be warp-uniform
     const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
     const int r = lane >> 2, t = lane & 3;
@@ -304,6 +322,7 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
     auto advance_consumer = [&]() { if (++c_slot == per_warp) { c_slot = 0; c_phase ^= 1u; } };
 
     for (int s = 0; s < per_warp; ++s) issue_next();
+    KIVI_TRACE(1);
 
     // ---- per-warp state --------------------------------------------------------------------------
     uint32_t qs[4 * C::KW];   // query fragment times the key scales of the current group (residual: natural pairs)
@@ -487,6 +506,7 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
         }
     }
 
+    KIVI_TRACE(2);
     // accumulators leave the code scale: channels masked at bits 0-3 carry 2^-24, at bits 4-7 2^-20
 #pragma unroll
     for (int m = 0; m < C::NMMA; ++m) {
@@ -565,6 +585,7 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
 
     if (failed && p.status && lane == 0) atomicExch(p.status, 1);
 
+    KIVI_TRACE(3);
     // ---- finish the lane-partial sums ----
 #pragma unroll
     for (int off = 4; off < 32; off <<= 1) {
@@ -598,6 +619,7 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
     }
     __syncthreads();
 
+    KIVI_TRACE(4);
     const float* all = reinterpret_cast<const float*>(ring);
     for (int idx = threadIdx.x; idx < g.qpk * D; idx += W * 32) {
         const int hq = idx / D, d = idx - hq * D;
@@ -620,8 +642,8 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
             if (d == 0) { p.ws_ml[part * 2] = mx; p.ws_ml[part * 2 + 1] = l; }
         }
     }
-    // the merge reuses the ring (the warp states in it were consumed above, behind its first barrier)
-    if (nchunks > 1) merge_when_last<8>(p, i, kv, nchunks, reinterpret_cast<float*>(ring), W * C::STATE_FLOATS);
+    KIVI_TRACE(5);
+    KIVI_TRACE(6);
 }
 
 template <int D, int G, int LOGB, int W, int CTAS>
@@ -690,3 +712,9 @@ cudaError_t launch_decode_mma(const DecodeParams& p, cudaStream_t stream) {
 }
 
 }  // namespace kivi
+
+#ifdef KIVI_DECODE_TRACE
+extern "C" int kivi_debug_decode_trace(unsigned long long* host_out, int ctas) {
+    return (int)cudaMemcpyFromSymbol(host_out, kivi::g_decode_trace, sizeof(unsigned long long) * 8 * ctas);
+}
+#endif
