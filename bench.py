@@ -493,7 +493,7 @@ def run_step(args):
                "layers": [random_layer(cfg, gen, device, rank=rank, world=world) for _ in range(cfg.layers)]}
     tables = torch.randperm(batch * (-(-(context - cfg.residual) // cfg.block_size)), generator=gen, device=device)
     rt = DecodeRuntime(cfg, weights, batch=batch, max_seq_len=context, device=device, rank=rank, world=world,
-                       group=group, block_tables=tables.to(torch.int32).reshape(batch, -1))
+                       group=group, block_tables=tables.to(torch.int32).reshape(batch, -1), comm=args.comm)
     # synthetic context: fill layer 0 through the library's writer, then give every layer the same pages
     c0 = rt.caches[0]
     c0.set_block_tables(rt.block_tables)
@@ -573,6 +573,8 @@ def run_step(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
     final_lens = rt.seq_lens.cpu().tolist()
+    exchange_ok = rt.exchange_status() == 0
+    rt.close()
 
     if rank == 0:
         peak, peak_kind = _peaks()
@@ -587,10 +589,10 @@ def run_step(args):
             "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f16/u4", "data": "synthetic",
             "config": {"workload": args.workload, "model_shape": cfg.name, "layers": cfg.layers, "batch": batch,
                        "context": context, "block": cfg.block_size, "group": cfg.group_size, "residual": cfg.residual,
-                       "parallelism": f"tp{world} over kv heads" if world > 1 else "1 gpu",
+                       "parallelism": f"tp{world} over kv heads, {args.comm} exchange" if world > 1 else "1 gpu",
                        "weights": "random-init fp16 N(0, 0.02)", "step": "CUDA-graph replay of kivi_b200_decode_step",
                        "l2": "29.5 GB of weights and the KV pages exceed the 126 MB L2",
-                       "final_seq_lens_ok": final_lens == [context - 2] * batch},
+                       "final_seq_lens_ok": final_lens == [context - 2] * batch, "exchange_ok": exchange_ok},
             "e2e": {"value": batch / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 4 * batch,
                     "d2h_bytes_per_step": 4 * batch, "ms_per_step": e2e_ms},
             "gpu_launches": launches_per_step * (warm + 2 * args.steps),
@@ -602,7 +604,10 @@ def run_step(args):
             "clocks": clocks,
         }))
     if world > 1:
-        dist.destroy_process_group()
+        # no destroy_process_group(): with NCCL collectives inside a captured graph it can block for minutes
+        dist.barrier()
+        sys.stdout.flush()
+        os._exit(0)
 
 
 def run_reference_cuda_lane(args):
@@ -802,6 +807,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + sorted(SECONDARY) + sorted(STEP_WORKLOADS))
+    ap.add_argument("--comm", default="p2p", choices=["p2p", "nccl"],
+                    help="decode-step workloads on several GPUs: the library's peer-memory exchange or NCCL hooks")
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
     ap.add_argument("--profile-only", action="store_true",
                     help="build the cache, run warmup+steps decode launches and exit (for ncu)")

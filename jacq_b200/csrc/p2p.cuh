@@ -21,7 +21,8 @@
 // for which every rank pushed k + 1, which each did after consuming k.
 //
 // Every wait is bounded: after kP2pSpinLimit polls the waiting thread records the peer in `status`
-// and goes on (the step's result is then meaningless, but the kernel ends and the host can read why).
+// and goes on (the step's result is then meaningless, but the kernel ends and the host can read why);
+// once `status` is non-zero no later wait polls at all.
 #pragma once
 #include "kivi_common.cuh"
 
@@ -97,7 +98,9 @@ __device__ __forceinline__ unsigned p2p_half(unsigned step_no, int site) { retur
 // delivered this step's data (or the poll limit ran out, recorded in status).
 __device__ __forceinline__ const unsigned char* p2p_wait(const P2pGather& g) {
     const unsigned step_no = ld_step_no(g.header);
-    if ((int)threadIdx.x < g.tp) {
+    // a wait that already gave up (this step or an earlier one) is not repeated: the error is sticky, so a
+    // lost peer costs one poll budget, not one per kernel
+    if ((int)threadIdx.x < g.tp && *reinterpret_cast<volatile unsigned*>(g.status) == 0u) {
         unsigned spins = 0;
         while ((int)(ld_acquire_sys(g.flags + threadIdx.x) - step_no) < 0) {
             if (++spins > g.spin_limit) {

@@ -404,7 +404,10 @@ def test_peer_exchange_wait_is_bounded(native_lib):
     rt.step(torch.tensor([1, 2]))
     torch.cuda.synchronize()
     assert rt.exchange_status() == 0b10              # rank 1 never delivered; rank 0's own pushes were seen
-    assert torch.equal(rt.seq_lens.cpu(), torch.tensor([1, 1], dtype=torch.int32))
+    rt.step(torch.tensor([3, 4]))                    # the error is sticky: later waits do not poll again
+    torch.cuda.synchronize()
+    assert rt.exchange_status() == 0b10
+    assert torch.equal(rt.seq_lens.cpu(), torch.tensor([2, 2], dtype=torch.int32))
     # a region that is too small is refused before anything is launched
     rt._comm.region_bytes = nbytes - 256
     with pytest.raises(_native.KiviStatusError):

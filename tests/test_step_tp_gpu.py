@@ -24,7 +24,7 @@ def test_two_rank_step(native_lib, comm):
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
            "127.0.0.1", "--master-port", "29611" if comm == "nccl" else "29612", str(ROOT / "tests" / "tp_worker.py"), comm]
-    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
     out = proc.stdout + proc.stderr
     assert proc.returncode == 0, out[-4000:]
     assert out.count("TP_WORKER_OK") == 2, out[-4000:]

@@ -2,6 +2,7 @@
 torch.distributed.run, one process per GPU, NCCL). Each rank runs the library step on its shard with
 the collectives on NCCL hooks ("nccl") or on the library's peer-memory exchange ("p2p") and checks its slice of the logits against the two-rank
 CPU oracle; half-way through it switches to CUDA-graph replay."""
+import datetime
 import os
 import sys
 from pathlib import Path
@@ -25,7 +26,7 @@ def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     device = torch.device(f"cuda:{int(os.environ['LOCAL_RANK'])}")
     torch.cuda.set_device(device)
-    dist.init_process_group("nccl", device_id=device)
+    dist.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(seconds=90))
     s = TINY
     cfg = DecodeModelConfig("test", s.layers, s.hidden, s.nh, s.nkv, s.hd, s.ffn, s.vocab, rope_base=s.rope_base,
                             norm_eps=s.norm_eps, attn_bias=s.attn_bias, block_size=s.block, group_size=s.group,
@@ -62,8 +63,12 @@ def main():
     assert rt.exchange_status() == 0, "a peer-memory wait ran out of polls"
     rt.close()
     dist.barrier()
+    torch.cuda.synchronize()
     print(f"TP_WORKER_OK comm={comm} rank={rank} worst_abs_err={worst:.3e}", flush=True)
-    dist.destroy_process_group()
+    # leave without tearing the communicator down: destroying a process group whose collectives sit in a
+    # captured CUDA graph has been seen to block for minutes
+    sys.stdout.flush()
+    os._exit(0)
 
 
 if __name__ == "__main__":
