@@ -147,17 +147,17 @@ __global__ void __launch_bounds__(kThreads) pack_groups_kernel(const WriteParams
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const Shape g(p.geom);
     const int nkv = p.geom.nkv;
-    const int i = blockIdx.z, h = blockIdx.y, j = blockIdx.x;
+    // keys and values of a group are quantised independently (per channel / per token): one CTA each,
+    // so a tile's worth of shared memory per CTA and twice the loads in flight per SM
+    const int i = blockIdx.z, h = blockIdx.y, j = blockIdx.x >> 1;
+    const bool values = blockIdx.x & 1;
     const SeqWrite s = seq_write(p, i);
     const int ngroups = (s.next_old - s.prev_old) / g.g;
     if (j >= ngroups) return;
 
     const int nparam = g.d > g.g * g.hg ? g.d : g.g * g.hg;
-    // both tiles are requested up front (asynchronous copies), so the value rows stream in while
-    // the keys are being quantised
-    __half* tile = reinterpret_cast<__half*>(smem_raw);                  // keys   [G, D]
-    __half* tile_v = tile + (size_t)g.g * g.d;                           // values [G, D]
-    float* p_min = reinterpret_cast<float*>(tile_v + (size_t)g.g * g.d); // [nparam] each
+    __half* tile = reinterpret_cast<__half*>(smem_raw);                  // keys or values [G, D]
+    float* p_min = reinterpret_cast<float*>(tile + (size_t)g.g * g.d);   // [nparam] each
     float* p_scale = p_min + nparam;
     float* p_rcp = p_scale + nparam;
     float* part_min = p_rcp + nparam;                                    // [parts, D]
@@ -170,11 +170,13 @@ __global__ void __launch_bounds__(kThreads) pack_groups_kernel(const WriteParams
     if (lp0 + g.pages_per_group > p.seq.bt_width) return;  // table too narrow: host validation failed
     const int words_per_row = g.d / 8;
 
-    // ---------------- keys: per channel over the G tokens ----------------
-    stage_tile(g, p, s, p.cache.k_scratch, p.new_k, h, pos0, tile);
-    stage_tile(g, p, s, p.cache.v_scratch, p.new_v, h, pos0, tile_v);
-    asm volatile("cp.async.wait_group 1;" ::: "memory");
+    if (values) stage_tile(g, p, s, p.cache.v_scratch, p.new_v, h, pos0, tile);
+    else stage_tile(g, p, s, p.cache.k_scratch, p.new_k, h, pos0, tile);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
+
+    // ---------------- keys: per channel over the G tokens ----------------
+    if (!values) {
     {
         // thread = (channel pair, slice of the rows); fminf/fmaxf drop NaN and order -0 below +0, so
         // any reduction order gives the reference's serial result
@@ -225,13 +227,10 @@ __global__ void __launch_bounds__(kThreads) pack_groups_kernel(const WriteParams
         uint32_t* dst = reinterpret_cast<uint32_t*>(p.cache.k_code + ((page * nkv + h) * g.b + (t % g.b)) * (g.d / 2));
         dst[w] = pack_word(v, mn, sc, rc, s_exact != 0);
     }
-    __syncthreads();
-    if (threadIdx.x == 0) s_exact = 0;
+    return;
+    }
 
     // ---------------- values: per token over each channel group ----------------
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    __syncthreads();
-    tile = tile_v;
     {
         // two adjacent lanes share one (token, channel group); each starts at a different word to
         // spread the shared-memory banks
@@ -322,7 +321,7 @@ __global__ void __launch_bounds__(kThreads) scratch_update_kernel(const WritePar
 
 size_t pack_smem_bytes(const Geom& g) {
     size_t params = (size_t)(g.d > g.g * g.hg ? g.d : g.g * g.hg);
-    return 2 * (size_t)g.g * g.d * sizeof(__half) + (3 * params + 4 * kThreads) * sizeof(float);
+    return (size_t)g.g * g.d * sizeof(__half) + (3 * params + 4 * kThreads) * sizeof(float);
 }
 
 template <class Shape>
@@ -351,7 +350,7 @@ cudaError_t launch_cache_write(const WriteParams& p, int max_new_per_seq, cudaSt
     if (p.n <= 0 || max_new_per_seq <= 0) return cudaSuccess;
     const size_t smem = pack_smem_bytes(g);
     const int max_groups = max_new_per_seq / g.g + 1;
-    const dim3 grid(max_groups, g.nkv, p.n);
+    const dim3 grid(2 * max_groups, g.nkv, p.n);   // (group, keys | values)
     bool done = false;
     cudaError_t e = cudaSuccess;
     if (g.d == 128 && g.g == 128) e = launch_pack_for_block<128, 128>(p, grid, smem, stream, &done);

@@ -58,7 +58,6 @@ __global__ void __launch_bounds__(kGemvThreads, kGemvCtasPerSm) gemv_kernel(cons
     const int warps_total = gridDim.x * (kGemvThreads / 32);
     const int gwarp = blockIdx.x * (kGemvThreads / 32) + warp;
     pdl_trigger();
-    l2_prefetch_ranges(pro);
 
     // The weights do not depend on the kernel before this one: the first loads of W go out before
     // waiting for it, so they are in flight while the predecessor drains and the input is prepared.

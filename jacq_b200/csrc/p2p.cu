@@ -13,6 +13,8 @@ constexpr int kPushThreads = 256;
 // (its own included), then the last CTA to finish publishes the step number in every peer's flag.
 __global__ void __launch_bounds__(kPushThreads) p2p_push_kernel(const uint4* __restrict__ src, size_t vecs,
                                                                  const P2pPush push) {
+    pdl_trigger();   // the projection that consumes this exchange may start streaming its weights now
+    pdl_wait();      // the producer of `src` has finished
     const unsigned step_no = ld_step_no(push.header);
     const size_t half_off = (size_t)p2p_half(step_no, push.site) * push.half_stride;
     for (size_t v = (size_t)blockIdx.x * kPushThreads + threadIdx.x; v < vecs; v += (size_t)gridDim.x * kPushThreads) {
@@ -38,8 +40,16 @@ cudaError_t launch_p2p_push(const void* src, size_t bytes, const P2pPush& push, 
     int blocks = (int)((vecs + kPushThreads - 1) / kPushThreads);
     if (blocks < 1) blocks = 1;
     if (blocks > 64) blocks = 64;
-    p2p_push_kernel<<<blocks, kPushThreads, 0, stream>>>(static_cast<const uint4*>(src), vecs, push);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(blocks, 1, 1);
+    cfg.blockDim = dim3(kPushThreads, 1, 1);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, p2p_push_kernel, static_cast<const uint4*>(src), vecs, push);
 }
 
 }  // namespace kivi

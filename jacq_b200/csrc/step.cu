@@ -17,8 +17,6 @@
 //                                                                                (kernels.cu:40-54)
 //   SiLU*up   g / (1 + expf(-g)) * up                                            (kernels.cu:146-153)
 //   add, bias fp16 __hadd                                                        (kernels.cu:156-166)
-#include <cstdlib>
-
 #include "kivi_common.cuh"
 #include "step_math.cuh"
 
@@ -209,37 +207,11 @@ size_t argmax_payload_bytes(int batch, int vocab) {
     return ((size_t)batch * argmax_chunks(vocab) * (sizeof(float) + sizeof(int)) + 15) / 16 * 16;
 }
 
-// Projection y[b, :] = W x[b, :]. `next_w` (optional): weights of the projection after this one, whose
-// first `next_bytes` are pulled into the L2 together with W while the kernel waits for its input.
-int project(const __half* w, const __half* x, __half* y, int out_dim, int in_dim, int batch, cudaStream_t stream,
-            const void* next_w = nullptr, size_t next_bytes = 0) {
+// Projection y[b, :] = W x[b, :].
+int project(const __half* w, const __half* x, __half* y, int out_dim, int in_dim, int batch, cudaStream_t stream) {
     if (skinny_gemm_supports(in_dim, batch))
         return ok(launch_skinny_gemm(w, x, y, nullptr, out_dim, in_dim, batch, stream));
-    if (batch <= 4 && next_w) {
-        GemvPrologue pro = {};
-        pro.x = x;
-        pro.l2_ptr[0] = w; pro.l2_bytes[0] = (size_t)out_dim * in_dim * sizeof(__half);
-        pro.l2_ptr[1] = next_w; pro.l2_bytes[1] = next_bytes;
-        return ok(launch_gemv_fused(w, kGemvPlain, pro, y, nullptr, out_dim, in_dim, batch, stream));
-    }
     return ok(launch_gemv(w, x, y, nullptr, out_dim, in_dim, batch, stream));
-}
-
-// Bytes of the projection after the O projection worth prefetching next to O's own `own` bytes: what
-// an L2 of 126 MB holds beside them and the KV stream of the attention. KIVI_STEP_L2_MB overrides.
-// 0 switches the prefetch off.
-long long l2_prefetch_cap_mb() {
-    static const long long cap_mb = [] {
-        const char* e = getenv("KIVI_STEP_L2_MB");
-        return e ? atoll(e) : 96LL;
-    }();
-    return cap_mb < 0 ? 0 : cap_mb;
-}
-size_t l2_prefetch_budget(size_t own, size_t next) {
-    const size_t cap = (size_t)l2_prefetch_cap_mb() << 20;
-    if (cap <= own) return 0;
-    const size_t room = cap - own;
-    return next < room ? next : room;
 }
 
 // Up to four sequences: the step's element-wise kernels ride in the prologue of the GEMV that
@@ -485,12 +457,7 @@ extern "C" int kivi_b200_decode_step(const kivi_step_config* cfg, const kivi_ste
         KIVI_STEP_TRY(ok(launch_cache_write(wp, 1, stream)));
         KIVI_STEP_TRY(run_decode(g, wp.cache, da, q, nullptr, attn, batch, max_seq_len, max_old, -1, decode_ws,
                                  L.decode_ws_bytes, stream));
-        // the attention kernels of a few sequences leave HBM mostly idle: the O projection, resident behind
-        // them, uses that time to pull its own weights and the head of gate_up's into the L2
-        KIVI_STEP_TRY(project(H(lw.o), attn, proj, c.hidden, q_dim, batch, stream,
-                              l2_prefetch_cap_mb() > 0 ? lw.gate_up : nullptr,
-                              l2_prefetch_budget((size_t)c.hidden * q_dim * sizeof(__half),
-                                                 (size_t)2 * c.ffn * c.hidden * sizeof(__half))));
+        KIVI_STEP_TRY(project(H(lw.o), attn, proj, c.hidden, q_dim, batch, stream));
         KIVI_STEP_TRY(exchange(proj, proj_bytes, 2 * l));
         // feed-forward block
         KIVI_STEP_TRY(project_add_norm(H(lw.gate_up), x_cur, nullptr, proj, gather_at(2 * l), H(lw.ffn_norm), x_nxt,

@@ -73,32 +73,6 @@ struct GemvPrologue {
     const __half* weight;   // add+norm: [in]
     __half* x_out;          // add+norm: optional [batch, in], the updated residual rows (written once)
     float eps;
-    // Weights to pull into the L2 while this kernel waits for its predecessor (a kernel that leaves
-    // HBM mostly idle, like the attention of a few sequences): up to two ranges, usually this
-    // GEMV's own matrix and the head of the next one. 0 bytes = none.
-    const void* l2_ptr[2];
-    size_t l2_bytes[2];
 };
-
-// Asynchronous prefetch of [p, p + bytes) into the L2; p 16-byte aligned, bytes a multiple of 16.
-__device__ __forceinline__ void l2_prefetch(const void* p, uint32_t bytes) {
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
-}
-
-// The first CTAs of the grid (the ones resident first) share the ranges out among their threads.
-__device__ __forceinline__ void l2_prefetch_ranges(const GemvPrologue& pro) {
-    const unsigned ctas = gridDim.x < 148u ? gridDim.x : 148u;
-    if (blockIdx.x >= ctas) return;
-    const size_t workers = (size_t)ctas * blockDim.x, me = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-#pragma unroll
-    for (int k = 0; k < 2; ++k) {
-        const size_t total = pro.l2_bytes[k] & ~(size_t)15;
-        if (total == 0) continue;
-        const size_t seg = ((total + workers - 1) / workers + 15) & ~(size_t)15;
-        const size_t lo = me * seg;
-        if (lo < total)
-            l2_prefetch(static_cast<const unsigned char*>(pro.l2_ptr[k]) + lo, (uint32_t)(total - lo < seg ? total - lo : seg));
-    }
-}
 
 }  // namespace kivi
