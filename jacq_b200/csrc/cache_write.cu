@@ -151,6 +151,8 @@ __global__ void __launch_bounds__(kThreads) pack_groups_kernel(const WriteParams
     // so a tile's worth of shared memory per CTA and twice the loads in flight per SM
     const int i = blockIdx.z, h = blockIdx.y, j = blockIdx.x >> 1;
     const bool values = blockIdx.x & 1;
+    pdl_trigger();
+    pdl_wait();   // new rows, lengths and tables may come from the kernel before this one
     const SeqWrite s = seq_write(p, i);
     const int ngroups = (s.next_old - s.prev_old) / g.g;
     if (j >= ngroups) return;
@@ -284,6 +286,8 @@ __global__ void __launch_bounds__(kThreads) pack_groups_kernel(const WriteParams
 __global__ void __launch_bounds__(kThreads) scratch_update_kernel(const WriteParams p) {
     const Geom& g = p.geom;
     const int i = blockIdx.y, h = blockIdx.x;
+    pdl_trigger();
+    pdl_wait();   // the pack kernel has read the rows this kernel moves
     const SeqWrite s = seq_write(p, i);
     if (s.num_new == 0) return;
     const int delta = s.next_old - s.prev_old;
@@ -330,8 +334,7 @@ cudaError_t launch_pack(const WriteParams& p, dim3 grid, size_t smem, cudaStream
         cudaError_t e = cudaFuncSetAttribute(pack_groups_kernel<Shape>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
-    pack_groups_kernel<Shape><<<grid, kThreads, smem, stream>>>(p);
-    return cudaSuccess;
+    return launch_pdl(pack_groups_kernel<Shape>, grid, dim3(kThreads), smem, stream, p);
 }
 
 template <int D, int G>
@@ -364,8 +367,7 @@ cudaError_t launch_cache_write(const WriteParams& p, int max_new_per_seq, cudaSt
         e = launch_pack<DynamicShape>(p, grid, smem, stream);
         if (e != cudaSuccess) return e;
     }
-    scratch_update_kernel<<<dim3(g.nkv, p.n), kThreads, 0, stream>>>(p);
-    return cudaGetLastError();
+    return launch_pdl(scratch_update_kernel, dim3(g.nkv, p.n), dim3(kThreads), 0, stream, p);
 }
 
 }  // namespace kivi

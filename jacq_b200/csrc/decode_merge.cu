@@ -25,8 +25,10 @@ __global__ void __launch_bounds__(kMergeThreads) decode_merge_kernel(const Decod
     const int seq_len = seq_len_of(p.seq, i);
     const DecodeBounds bnd = effective_bounds(p, seq_len);
     const int nchunks = chunk_work(p, bnd, 0).nchunks;
-    if (nchunks <= 1) return;   // the decode kernel wrote O itself
+    // Every CTA waits, also the ones with nothing to merge: a kernel launched behind this one only waits
+    // for THIS grid, so a CTA that left early would let it overtake the decode kernel.
     pdl_wait();                 // the partials are complete and visible
+    if (nchunks <= 1) return;   // the decode kernel wrote O itself
 
     const int quads = g.d / 4;                     // runs of four channels
     const int lanes = kMergeThreads / quads;       // chunk lanes

@@ -160,6 +160,7 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
     const Geom& g = p.geom;
     const int i = blockIdx.z, kv = blockIdx.y, chunk = blockIdx.x;
     pdl_trigger();   // a projection launched behind this kernel may start streaming its weights
+    pdl_wait();      // queries, lengths and the cache may come from the kernel before this one
     KIVI_TRACE(0);
     // the warp index through a broadcast, so that everything derived from it is known to be warp-uniform
     const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
@@ -661,8 +662,8 @@ cudaError_t launch(const DecodeParams& p, cudaStream_t stream) {
     const int smem = kFixed + per_warp * W * C::SLOT;
     cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<D, G, LOGB, W, CTAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    decode_mma_kernel<D, G, LOGB, W, CTAS><<<dim3(p.max_chunks, p.geom.nkv, p.n), W * 32, smem, stream>>>(p, per_warp);
-    return cudaGetLastError();
+    return launch_pdl(decode_mma_kernel<D, G, LOGB, W, CTAS>, dim3(p.max_chunks, p.geom.nkv, p.n), dim3(W * 32), smem, stream,
+                      p, per_warp);
 }
 
 // Warps per CTA and CTAs per SM. Twelve warps per SM leave each thread about 170 registers, which

@@ -87,12 +87,14 @@ __global__ void __launch_bounds__(kGemvThreads, kGemvCtasPerSm) gemv_kernel(cons
         }
         __syncthreads();
     } else {
-        const unsigned char* slots = pro.gather.tp > 0 ? p2p_wait(pro.gather) : nullptr;   // every rank has delivered
+        const bool gathered = pro.gather.tp > 0;
+        P2pView view = {};
+        if (gathered) view = p2p_view(pro.gather);
         for (int c = threadIdx.x; c < BT * chunks; c += kGemvThreads) {
             const int b = c / chunks, cc = c - b * chunks;
             const size_t src = pro.tokens ? (size_t)pro.tokens[b] : (size_t)b;
             uint4 a = reinterpret_cast<const uint4*>(pro.x + src * in_dim)[cc];
-            if (slots) a = hadd8(a, p2p_sum8(slots, pro.gather.slot_bytes, pro.gather.tp, (size_t)c));
+            if (gathered) a = hadd8(a, p2p_sum8(view, (size_t)c));   // polls until every rank's words have arrived
             else if (pro.delta) a = hadd8(a, reinterpret_cast<const uint4*>(pro.delta + (size_t)b * in_dim)[cc]);
             if (pro.x_out && blockIdx.x == 0) reinterpret_cast<uint4*>(pro.x_out + (size_t)b * in_dim)[cc] = a;
             xs[c] = a;
@@ -113,6 +115,8 @@ __global__ void __launch_bounds__(kGemvThreads, kGemvCtasPerSm) gemv_kernel(cons
         __syncthreads();
     }
 
+    P2pTarget target = {};
+    if (pro.push.tp > 0) target = p2p_target(pro.push);
     for (int row0 = first_row; row0 < out_dim; row0 += warps_total * kRowsPerWarp) {
         float acc[kRowsPerWarp][BT];
 #pragma unroll
@@ -147,17 +151,22 @@ __global__ void __launch_bounds__(kGemvThreads, kGemvCtasPerSm) gemv_kernel(cons
             }
         }
 #pragma unroll
-        for (int r = 0; r < kRowsPerWarp; ++r)
+        for (int b = 0; b < BT; ++b) {
+            float s[kRowsPerWarp];
 #pragma unroll
-            for (int b = 0; b < BT; ++b) {
-                float s = acc[r][b];
+            for (int r = 0; r < kRowsPerWarp; ++r) {
+                s[r] = acc[r][b];
 #pragma unroll
-                for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+                for (int o = 16; o > 0; o >>= 1) s[r] += __shfl_xor_sync(0xffffffffu, s[r], o);
                 if (lane == 0 && row0 + r < out_dim) {
-                    if (y32) y32[(size_t)b * ldy + row0 + r] = s;
-                    if (y16) y16[(size_t)b * ldy + row0 + r] = __float2half_rn(s);
+                    if (y32) y32[(size_t)b * ldy + row0 + r] = s[r];
+                    if (y16) y16[(size_t)b * ldy + row0 + r] = __float2half_rn(s[r]);
                 }
             }
+            // tensor parallel: the row pair goes straight into every rank's slot (out_dim is even)
+            if (pro.push.tp > 0 && lane == 0 && row0 + 1 < out_dim)
+                p2p_write1(pro.push, target, ((size_t)b * out_dim + row0) >> 1, pack_half2(s[0], s[1]));
+        }
     }
 }
 

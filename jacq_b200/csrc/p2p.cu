@@ -9,47 +9,27 @@ namespace {
 
 constexpr int kPushThreads = 256;
 
-// Copies `vecs` 16-byte vectors from local memory into this rank's slot in every peer's region
-// (its own included), then the last CTA to finish publishes the step number in every peer's flag.
-__global__ void __launch_bounds__(kPushThreads) p2p_push_kernel(const uint4* __restrict__ src, size_t vecs,
+// Delivers `pairs` pairs of 32-bit payload words from local memory into this rank's slot in every
+// peer's region (its own included), each pair as one 16-byte store of two {data, sequence} words.
+__global__ void __launch_bounds__(kPushThreads) p2p_push_kernel(const uint2* __restrict__ src, size_t pairs,
                                                                  const P2pPush push) {
-    pdl_trigger();   // the projection that consumes this exchange may start streaming its weights now
-    pdl_wait();      // the producer of `src` has finished
-    const unsigned step_no = ld_step_no(push.header);
-    const size_t half_off = (size_t)p2p_half(step_no, push.site) * push.half_stride;
-    for (size_t v = (size_t)blockIdx.x * kPushThreads + threadIdx.x; v < vecs; v += (size_t)gridDim.x * kPushThreads) {
-        const uint4 a = src[v];
-        for (int r = 0; r < push.tp; ++r) reinterpret_cast<uint4*>(push.slot[r] + half_off)[v] = a;
-    }
-    __threadfence_system();   // this thread's stores are visible to every GPU before the CTA reports in
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const unsigned prev = atomicAdd(push.arrive, 1u);
-        if (prev == gridDim.x - 1) {
-            *push.arrive = 0u;           // ready for the next launch on this stream
-            __threadfence_system();      // orders every CTA's stores (seen through the counter) before the flags
-            for (int r = 0; r < push.tp; ++r) st_release_sys(push.flag[r], step_no);
-        }
+    const P2pTarget t = p2p_target(push);
+    for (size_t i = (size_t)blockIdx.x * kPushThreads + threadIdx.x; i < pairs; i += (size_t)gridDim.x * kPushThreads) {
+        const uint2 a = src[i];
+        p2p_write2(push, t, i, a.x, a.y);
     }
 }
 
 }  // namespace
 
+// bytes is rounded up to whole pairs of words; src must be readable that far and 8-byte aligned.
 cudaError_t launch_p2p_push(const void* src, size_t bytes, const P2pPush& push, cudaStream_t stream) {
-    const size_t vecs = (bytes + 15) / 16;
-    int blocks = (int)((vecs + kPushThreads - 1) / kPushThreads);
+    const size_t pairs = (bytes + 7) / 8;
+    int blocks = (int)((pairs + kPushThreads - 1) / kPushThreads);
     if (blocks < 1) blocks = 1;
-    if (blocks > 64) blocks = 64;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(blocks, 1, 1);
-    cfg.blockDim = dim3(kPushThreads, 1, 1);
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, p2p_push_kernel, static_cast<const uint4*>(src), vecs, push);
+    if (blocks > 296) blocks = 296;
+    p2p_push_kernel<<<blocks, kPushThreads, 0, stream>>>(static_cast<const uint2*>(src), pairs, push);
+    return cudaGetLastError();
 }
 
 }  // namespace kivi

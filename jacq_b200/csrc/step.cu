@@ -34,7 +34,9 @@ __global__ void __launch_bounds__(kNormThreads) residual_rmsnorm_kernel(
     __shared__ float warp_sums[32];
     const int tid = threadIdx.x;
     pdl_trigger();
-    const unsigned char* slots = gather.tp > 0 ? p2p_wait(gather) : nullptr;
+    const bool gathered = gather.tp > 0;
+    P2pView view = {};
+    if (gathered) view = p2p_view(gather);
     const size_t src_row = tokens ? (size_t)tokens[blockIdx.x] : (size_t)blockIdx.x;
     const uint4* xs = reinterpret_cast<const uint4*>(x + src_row * hidden);
     const uint4* ds = delta ? reinterpret_cast<const uint4*>(delta + (size_t)blockIdx.x * hidden) : nullptr;
@@ -42,7 +44,7 @@ __global__ void __launch_bounds__(kNormThreads) residual_rmsnorm_kernel(
     const int vecs = hidden >> 3;
     for (int v = tid; v < vecs; v += kNormThreads) {
         uint4 a = xs[v];
-        if (slots) a = hadd8(a, p2p_sum8(slots, gather.slot_bytes, gather.tp, (size_t)blockIdx.x * vecs + v));
+        if (gathered) a = hadd8(a, p2p_sum8(view, (size_t)blockIdx.x * vecs + v));
         else if (ds) a = hadd8(a, ds[v]);
         if (xo) xo[v] = a;
         row[v] = a;
@@ -63,6 +65,7 @@ __global__ void __launch_bounds__(128) bias_rope_kernel(
     const int rowi = blockIdx.y, h = blockIdx.x;
     const int half_dim = hd >> 1;
     pdl_trigger();
+    pdl_wait();   // the projection that wrote qkv
     const __half* in = qkv + (size_t)rowi * (nh + 2 * nkv) * hd + (size_t)h * hd;
     const __half* bh = bias ? bias + (size_t)h * hd : nullptr;
     if (h >= nh + nkv) {   // a value head: bias add only
@@ -134,20 +137,32 @@ __global__ void __launch_bounds__(kArgmaxThreads) argmax_partial_kernel(
 
 // Second pass: one warp per row over the candidates of every rank. Rank r's candidates start at
 // base + r * rank_stride: [rows][chunks] values, then at idx_off [rows][chunks] indices. With
-// gather.tp > 0 the candidates are the ranks' slots of that exchange site.
+// gather.tp > 0 the candidates are the ranks' slots of that exchange site (payload words in the same
+// order, read through the exchange).
 __global__ void argmax_merge_kernel(const unsigned char* __restrict__ base, size_t rank_stride, size_t idx_off, int chunks,
                                     int ranks, int rows, int* __restrict__ out, const P2pGather gather) {
-    if (gather.tp > 0) base = p2p_wait(gather);
+    const bool gathered = gather.tp > 0;
+    P2pView view = {};
+    if (gathered) view = p2p_view(gather);
     const int rowi = blockIdx.x;
     float best = -1e30f;
     int best_i = 0;
     const int total = chunks * ranks;
     for (int e = threadIdx.x; e < total; e += 32) {
         const int rk = e / chunks, ch = e - rk * chunks;
-        const unsigned char* rb = base + (size_t)rk * rank_stride;
         const size_t at = (size_t)rowi * chunks + ch;
-        const float v = __ldcg(reinterpret_cast<const float*>(rb) + at);
-        const int i = __ldcg(reinterpret_cast<const int*>(rb + idx_off) + at);
+        float v;
+        int i;
+        if (gathered) {
+            const size_t wv = at, wi = idx_off / 4 + at;   // payload word numbers of the value and of the index
+            const uint2 pv = p2p_read2(view, rk, wv >> 1), pi = p2p_read2(view, rk, wi >> 1);
+            v = __uint_as_float((wv & 1) ? pv.y : pv.x);
+            i = (int)((wi & 1) ? pi.y : pi.x);
+        } else {
+            const unsigned char* rb = base + (size_t)rk * rank_stride;
+            v = __ldcg(reinterpret_cast<const float*>(rb) + at);
+            i = __ldcg(reinterpret_cast<const int*>(rb + idx_off) + at);
+        }
         if (better(v, i, best, best_i)) { best = v; best_i = i; }
     }
     for (int off = 16; off > 0; off >>= 1) {
@@ -192,9 +207,8 @@ int launch_residual_rmsnorm(const __half* x, const int* tokens, const __half* de
 int launch_bias_rope(const __half* qkv, const __half* bias, const int* positions, __half* q, __half* k, __half* v,
                      int batch, int nh, int nkv, int hd, float rope_base, cudaStream_t stream) {
     const int threads = hd / 2 <= 32 ? 32 : (hd / 2 <= 64 ? 64 : 128);
-    bias_rope_kernel<<<dim3(nh + 2 * nkv, batch), threads, 0, stream>>>(qkv, bias, positions, q, k, v, nh, nkv, hd,
-                                                                         rope_base);
-    return ok(cudaGetLastError());
+    return ok(launch_pdl(bias_rope_kernel, dim3(nh + 2 * nkv, batch), dim3(threads), 0, stream, qkv, bias, positions, q, k, v,
+                         nh, nkv, hd, rope_base));
 }
 
 int launch_silu_mul(const __half* gate_up, __half* out, int batch, int ffn, cudaStream_t stream) {
@@ -207,11 +221,21 @@ size_t argmax_payload_bytes(int batch, int vocab) {
     return ((size_t)batch * argmax_chunks(vocab) * (sizeof(float) + sizeof(int)) + 15) / 16 * 16;
 }
 
-// Projection y[b, :] = W x[b, :].
-int project(const __half* w, const __half* x, __half* y, int out_dim, int in_dim, int batch, cudaStream_t stream) {
-    if (skinny_gemm_supports(in_dim, batch))
-        return ok(launch_skinny_gemm(w, x, y, nullptr, out_dim, in_dim, batch, stream));
-    return ok(launch_gemv(w, x, y, nullptr, out_dim, in_dim, batch, stream));
+// Projection y[b, :] = W x[b, :]. `push` (tensor parallel over peer memory, may be nullptr): the result is
+// a partial sum that every rank needs; up to four sequences deliver it from the GEMV's own epilogue,
+// larger batches through the copy kernel behind the skinny GEMM.
+int project(const __half* w, const __half* x, __half* y, int out_dim, int in_dim, int batch, cudaStream_t stream,
+            const P2pPush* push = nullptr) {
+    if (batch <= 4 && push) {
+        GemvPrologue pro = {};
+        pro.x = x;
+        pro.push = *push;
+        return ok(launch_gemv_fused(w, kGemvPlain, pro, y, nullptr, out_dim, in_dim, batch, stream));
+    }
+    int rc = skinny_gemm_supports(in_dim, batch) ? ok(launch_skinny_gemm(w, x, y, nullptr, out_dim, in_dim, batch, stream))
+                                                 : ok(launch_gemv(w, x, y, nullptr, out_dim, in_dim, batch, stream));
+    if (rc == KIVI_OK && push) rc = ok(launch_p2p_push(y, (size_t)batch * out_dim * sizeof(__half), *push, stream));
+    return rc;
 }
 
 // Up to four sequences: the step's element-wise kernels ride in the prologue of the GEMV that
@@ -236,14 +260,15 @@ int project_add_norm(const __half* w, const __half* x, const int* tokens, const 
 
 // y = W (SiLU(gate) * up) for rows [gate | up].
 int project_silu_mul(const __half* w, const __half* gate_up, __half* mid_scratch, __half* y, int out_dim, int ffn,
-                     int batch, cudaStream_t stream) {
+                     int batch, cudaStream_t stream, const P2pPush* push = nullptr) {
     if (fuse_prologues(batch)) {
         GemvPrologue pro = {};
         pro.x = gate_up;
+        if (push) pro.push = *push;
         return ok(launch_gemv_fused(w, kGemvSiluMul, pro, y, nullptr, out_dim, ffn, batch, stream));
     }
     const int rc = launch_silu_mul(gate_up, mid_scratch, batch, ffn, stream);
-    return rc != KIVI_OK ? rc : project(w, mid_scratch, y, out_dim, ffn, batch, stream);
+    return rc != KIVI_OK ? rc : project(w, mid_scratch, y, out_dim, ffn, batch, stream, push);
 }
 
 size_t up256(size_t v) { return (v + 255) / 256 * 256; }
@@ -354,7 +379,7 @@ extern "C" int kivi_b200_decode_step(const kivi_step_config* cfg, const kivi_ste
     if (tp && !comm) return KIVI_ERR_NULL_POINTER;
     const bool p2p = tp && comm->peer_regions != nullptr;
     if (tp && !p2p && (!comm->allreduce_f16 || !comm->allgather)) return KIVI_ERR_NULL_POINTER;
-    if (c.tp_size > kMaxTp && p2p) return KIVI_ERR_GEOMETRY;
+    if (p2p && (c.tp_size > kMaxTp || c.hidden % 2)) return KIVI_ERR_GEOMETRY;
     kivi_geometry gs = step_geometry(c);
     rc = kivi_b200_validate_geometry(&gs, nullptr);
     if (rc != KIVI_OK) return rc;
@@ -394,37 +419,36 @@ extern "C" int kivi_b200_decode_step(const kivi_step_config* cfg, const kivi_ste
             if (!comm->peer_regions[r] || !aligned16(comm->peer_regions[r])) return KIVI_ERR_NULL_POINTER;
     }
     P2pHeader* header = reinterpret_cast<P2pHeader*>(own);
+    const int sites = 2 * c.layers + 1;
     auto gather_at = [&](int site) {
         P2pGather ga = {};
         if (!p2p) return ga;            // tp = 0: the consumer reads its plain local input
-        ga.flags = reinterpret_cast<const unsigned*>(own + pl.flags_off) + (size_t)site * c.tp_size;
         ga.header = header;
         ga.status = &header->status;
         ga.slots = own + pl.slots_off;
         ga.slot_bytes = pl.slot_bytes;
         ga.tp = c.tp_size;
         ga.site = site;
+        ga.sites = sites;
         ga.spin_limit = comm->spin_limit ? comm->spin_limit : kP2pSpinLimit;
         return ga;
     };
-    // all-reduce of `buf` at `site`: hooks reduce in place now; peer memory pushes now and sums in the consumer
-    auto exchange = [&](__half* buf, size_t bytes, int site) -> int {
-        if (!tp) return KIVI_OK;
-        if (!p2p)
-            return comm->allreduce_f16(comm->user, reinterpret_cast<kivi_f16*>(buf), bytes / 2, stream) ? KIVI_ERR_CUDA
-                                                                                                          : KIVI_OK;
+    auto push_at = [&](int site) {
         P2pPush ps = {};
-        for (int r = 0; r < c.tp_size; ++r) {
-            unsigned char* peer = static_cast<unsigned char*>(comm->peer_regions[r]);
-            ps.slot[r] = peer + pl.slots_off + (size_t)c.tp_rank * pl.slot_bytes;
-            ps.flag[r] = reinterpret_cast<unsigned*>(peer + pl.flags_off) + (size_t)site * c.tp_size + c.tp_rank;
-        }
+        for (int r = 0; r < c.tp_size; ++r)
+            ps.slot[r] = static_cast<unsigned char*>(comm->peer_regions[r]) + pl.slots_off + (size_t)c.tp_rank * pl.slot_bytes;
         ps.header = header;
-        ps.arrive = &header->arrive;
         ps.half_stride = (size_t)c.tp_size * pl.slot_bytes;
         ps.tp = c.tp_size;
         ps.site = site;
-        return ok(launch_p2p_push(buf, bytes, ps, stream));
+        ps.sites = sites;
+        return ps;
+    };
+    // all-reduce through the hooks: in place, now (peer memory delivers from the projection itself and sums
+    // in the consumer)
+    auto allreduce_hook = [&](__half* buf, size_t bytes) -> int {
+        if (!tp || p2p) return KIVI_OK;
+        return comm->allreduce_f16(comm->user, reinterpret_cast<kivi_f16*>(buf), bytes / 2, stream) ? KIVI_ERR_CUDA : KIVI_OK;
     };
     const size_t proj_bytes = (size_t)batch * c.hidden * sizeof(__half);
 
@@ -457,16 +481,19 @@ extern "C" int kivi_b200_decode_step(const kivi_step_config* cfg, const kivi_ste
         KIVI_STEP_TRY(ok(launch_cache_write(wp, 1, stream)));
         KIVI_STEP_TRY(run_decode(g, wp.cache, da, q, nullptr, attn, batch, max_seq_len, max_old, -1, decode_ws,
                                  L.decode_ws_bytes, stream));
-        KIVI_STEP_TRY(project(H(lw.o), attn, proj, c.hidden, q_dim, batch, stream));
-        KIVI_STEP_TRY(exchange(proj, proj_bytes, 2 * l));
+        P2pPush push_o = p2p ? push_at(2 * l) : P2pPush{};
+        KIVI_STEP_TRY(project(H(lw.o), attn, proj, c.hidden, q_dim, batch, stream, p2p ? &push_o : nullptr));
+        KIVI_STEP_TRY(allreduce_hook(proj, proj_bytes));
         // feed-forward block
         KIVI_STEP_TRY(project_add_norm(H(lw.gate_up), x_cur, nullptr, proj, gather_at(2 * l), H(lw.ffn_norm), x_nxt,
                                        normed, gate_up, 2 * c.ffn, c.hidden, batch, c.norm_eps, stream));
         { __half* t = x_cur; x_cur = x_nxt; x_nxt = t; }
         // the down projection must not overwrite `proj` while a gate_up CTA may still read it as delta:
         // it cannot, every gate_up CTA has finished its prologue before the first down CTA passes its wait
-        KIVI_STEP_TRY(project_silu_mul(H(lw.down), gate_up, mid, proj, c.hidden, c.ffn, batch, stream));
-        KIVI_STEP_TRY(exchange(proj, proj_bytes, 2 * l + 1));
+        P2pPush push_down = p2p ? push_at(2 * l + 1) : P2pPush{};
+        KIVI_STEP_TRY(project_silu_mul(H(lw.down), gate_up, mid, proj, c.hidden, c.ffn, batch, stream,
+                                       p2p ? &push_down : nullptr));
+        KIVI_STEP_TRY(allreduce_hook(proj, proj_bytes));
         delta = proj;
         delta_site = p2p ? 2 * l + 1 : -1;
     }
@@ -486,7 +513,8 @@ extern "C" int kivi_b200_decode_step(const kivi_step_config* cfg, const kivi_ste
     size_t rank_stride = 0;
     P2pGather cand_gather = {};
     if (p2p) {
-        KIVI_STEP_TRY(exchange(reinterpret_cast<__half*>(parts), L.parts_bytes, 2 * c.layers));
+        const P2pPush push_cand = push_at(2 * c.layers);
+        KIVI_STEP_TRY(ok(launch_p2p_push(parts, L.parts_bytes, push_cand, stream)));
         cand_gather = gather_at(2 * c.layers);
         rank_stride = pl.slot_bytes;
     } else if (tp) {

@@ -70,6 +70,7 @@ struct GemvPrologue {
     const int* tokens;      // add+norm: optional row gather (embedding lookup)
     const __half* delta;    // add+norm: optional [batch, in] added first
     P2pGather gather;       // add+norm: when gather.tp > 0 the delta is the sum of the ranks' slots of that site instead
+    P2pPush push;           // any kind: when push.tp > 0 the result goes to every rank's slot of that site (fp16 pairs)
     const __half* weight;   // add+norm: [in]
     __half* x_out;          // add+norm: optional [batch, in], the updated residual rows (written once)
     float eps;
