@@ -122,8 +122,8 @@ int kivi_b200_cache_write(const kivi_geometry* geom, const kivi_cache* cache,
 /* Bytes of caller-owned workspace the decode needs for this batch and longest sequence. */
 size_t kivi_b200_decode_workspace_bytes(const kivi_geometry* geom, int batch, int max_seq_len);
 
-/* Zero the workspace's arrival counters. Call once after allocating (or re-purposing) a
- * workspace; every decode leaves them zero again. */
+/* Zero the workspace. Kept for callers of earlier versions: the decode reads only what the same call
+ * wrote, so the workspace needs no initial contents. */
 int kivi_b200_decode_workspace_init(void* workspace, size_t workspace_bytes, cudaStream_t stream);
 
 /* Paged decode attention for `batch` independent sequences, one query token each
@@ -149,7 +149,8 @@ int kivi_b200_decode(const kivi_geometry* geom, const kivi_cache* cache, const k
  *   - the first call on each device, made with that device current, looks the array's device
  *     address up; make that first call before any stream capture begins;
  *   - every call uses the same array: two calls whose kernels can overlap on the GPU (different
- *     streams, different host threads) race on it. Calls on one stream are safe back to back.
+ *     streams, different host threads) race on it. Calls on one stream are safe back to back;
+ *     nothing in the array has to be cleared between them (a call reads only partials it wrote).
  * Arguments and results are those of kivi_b200_decode. */
 #define KIVI_B200_NOALLOC_SCRATCH_BYTES (1u << 20)
 int kivi_b200_decode_noalloc(const kivi_geometry* geom, const kivi_cache* cache, const kivi_f16* q,

@@ -76,15 +76,15 @@ SplitPlan plan_split(const Geom& g, int n, int max_old_tokens) {
 constexpr size_t kWsAlign = 256;
 size_t align_up(size_t x) { return (x + kWsAlign - 1) / kWsAlign * kWsAlign; }
 
-struct WsLayout { size_t count_off, ml_off, o_off, total; };
+struct WsLayout { size_t ml_off, o_off, total; };
 WsLayout ws_layout(const Geom& g, int n, const SplitPlan& sp) {
     WsLayout w;
     const size_t units = (size_t)n * g.nkv;
-    w.count_off = 0;
-    w.ml_off = align_up(units * sizeof(unsigned int));
+    w.ml_off = 0;
     const size_t parts = sp.max_chunks > 1 ? units * sp.max_chunks * g.qpk : 0;
     w.o_off = w.ml_off + align_up(parts * 2 * sizeof(float));
     w.total = w.o_off + align_up(parts * g.d * sizeof(float));
+    if (w.total < kWsAlign) w.total = kWsAlign;   // never 0, which the size query returns for invalid arguments
     return w;
 }
 
@@ -109,7 +109,6 @@ int run_decode(const Geom& g, const CachePtrs& cache, const SeqAddressing& seq, 
         if (!aligned16(ws)) return KIVI_ERR_ALIGNMENT;
     }
     unsigned char* base = static_cast<unsigned char*>(ws);
-    p.ws_count = base ? reinterpret_cast<unsigned int*>(base + wl.count_off) : nullptr;
     p.ws_ml = base ? reinterpret_cast<float*>(base + wl.ml_off) : nullptr;
     p.ws_o = base ? reinterpret_cast<float*>(base + wl.o_off) : nullptr;
     cudaError_t e = decode_mma_supports(g, retained_pages) ? launch_decode_mma(p, stream)
@@ -352,10 +351,7 @@ extern "C" int kivi_b200_decode_noalloc(const kivi_geometry* geom, const kivi_ca
         g_noalloc_ptr[dev] = ptr;
     }
     void* scratch = g_noalloc_ptr[dev];
-    // the array keeps whatever the previous call left: the arrival counters must start at zero
-    if (cudaMemsetAsync(static_cast<unsigned char*>(scratch) + wl.count_off, 0, wl.ml_off - wl.count_off, stream) !=
-        cudaSuccess)
-        return KIVI_ERR_CUDA;
+    // nothing in the array has to start from a known value: a launch reads only the partials it wrote itself
     SeqAddressing a;
     a.seq_lens = seq_lens; a.seq_len_scalar = 0;
     a.block_tables = block_tables; a.bt_stride = max_blocks_per_seq; a.bt_width = max_blocks_per_seq;

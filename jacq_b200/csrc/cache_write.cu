@@ -21,6 +21,7 @@
 // else from the new rows; that indirection is what lets one call cross several boundaries and
 // still equal the token-by-token writer.
 #include "kivi_common.cuh"
+#include "step_math.cuh"
 
 namespace kivi {
 namespace {
@@ -142,20 +143,12 @@ __device__ __forceinline__ unsigned pack_word(const uint4& v, const float* mn, c
     return word;
 }
 
+// Quantises the keys (values == false) or the values of aged-out group j of (sequence s, kv head h) into
+// its pages. Called by every thread of a CTA of kThreads threads; smem_raw holds pack_smem_bytes().
 template <class Shape>
-__global__ void __launch_bounds__(kThreads) pack_groups_kernel(const WriteParams p) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    const Shape g(p.geom);
+__device__ __forceinline__ void pack_group(const WriteParams& p, const Shape& g, const SeqWrite& s, int h, int j,
+                                           bool values, unsigned char* smem_raw) {
     const int nkv = p.geom.nkv;
-    // keys and values of a group are quantised independently (per channel / per token): one CTA each,
-    // so a tile's worth of shared memory per CTA and twice the loads in flight per SM
-    const int i = blockIdx.z, h = blockIdx.y, j = blockIdx.x >> 1;
-    const bool values = blockIdx.x & 1;
-    pdl_trigger();
-    pdl_wait();   // new rows, lengths and tables may come from the kernel before this one
-    const SeqWrite s = seq_write(p, i);
-    const int ngroups = (s.next_old - s.prev_old) / g.g;
-    if (j >= ngroups) return;
 
     const int nparam = g.d > g.g * g.hg ? g.d : g.g * g.hg;
     __half* tile = reinterpret_cast<__half*>(smem_raw);                  // keys or values [G, D]
@@ -282,14 +275,26 @@ __global__ void __launch_bounds__(kThreads) pack_groups_kernel(const WriteParams
     }
 }
 
-// Move-to-front of the rows that stay in the scratch, then append of the new rows that stay.
-__global__ void __launch_bounds__(kThreads) scratch_update_kernel(const WriteParams p) {
-    const Geom& g = p.geom;
-    const int i = blockIdx.y, h = blockIdx.x;
+// keys and values of a group are quantised independently (per channel / per token): one CTA each, so a
+// tile's worth of shared memory per CTA and twice the loads in flight per SM
+template <class Shape>
+__global__ void __launch_bounds__(kThreads) pack_groups_kernel(const WriteParams p) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const Shape g(p.geom);
+    const int i = blockIdx.z, h = blockIdx.y, j = blockIdx.x >> 1;
+    const bool values = blockIdx.x & 1;
     pdl_trigger();
-    pdl_wait();   // the pack kernel has read the rows this kernel moves
+    pdl_wait();   // new rows, lengths and tables may come from the kernel before this one
     const SeqWrite s = seq_write(p, i);
-    if (s.num_new == 0) return;
+    const int ngroups = (s.next_old - s.prev_old) / g.g;
+    if (j >= ngroups) return;
+    pack_group(p, g, s, h, j, values, smem_raw);
+}
+
+// Move-to-front of the rows of (sequence s, kv head h) that stay in the scratch, then append of the new
+// rows that stay. Called by every thread of a CTA of kThreads threads.
+__device__ __forceinline__ void scratch_update(const WriteParams& p, const SeqWrite& s, int h) {
+    const Geom& g = p.geom;
     const int delta = s.next_old - s.prev_old;
     const int chunks_per_row = g.d / 8;
     uint4* ks = reinterpret_cast<uint4*>(p.cache.k_scratch + ((size_t)s.slot * g.nkv + h) * g.scratch_rows * g.d);
@@ -323,6 +328,55 @@ __global__ void __launch_bounds__(kThreads) scratch_update_kernel(const WritePar
     }
 }
 
+__global__ void __launch_bounds__(kThreads) scratch_update_kernel(const WriteParams p) {
+    const int i = blockIdx.y, h = blockIdx.x;
+    pdl_trigger();
+    pdl_wait();   // the pack kernel has read the rows this kernel moves
+    const SeqWrite s = seq_write(p, i);
+    if (s.num_new == 0) return;
+    scratch_update(p, s, h);
+}
+
+// One decode step's worth of the path between the QKV projection and the attention, in one launch:
+// bias add + RoPE + q/k/v split of sequence i for kv head h and the query heads of its group
+// (bias_rope_kernel of step.cu, same arithmetic), then the cache write of that one new token for
+// (i, h): quantise the group that ages out, if one does (every G-th step), move the scratch and
+// append. One CTA per (kv head, sequence); the rows it appends are the ones it has just rotated.
+template <class Shape>
+__global__ void __launch_bounds__(kThreads) rope_write_kernel(const RopeParams rp, const WriteParams p) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const Shape g(p.geom);
+    const int h = blockIdx.x, i = blockIdx.y;
+    const int nh = p.geom.nh, nkv = p.geom.nkv, qpk = p.geom.qpk, hd = g.d, half_dim = hd >> 1;
+    pdl_trigger();
+    const __half* row = rp.qkv + (size_t)i * (nh + 2 * nkv) * hd;
+    const int pos = rp.positions[i];
+    // heads 0..qpk-1: the query heads of this kv head; head qpk: its key head
+    for (int idx = threadIdx.x; idx < (qpk + 1) * half_dim; idx += kThreads) {
+        const int hl = idx / half_dim, e = idx - hl * half_dim;
+        const int head = hl < qpk ? h * qpk + hl : nh + h;            // position in the qkv row
+        const __half* in = row + (size_t)head * hd;
+        __half* out = hl < qpk ? rp.q + ((size_t)i * nh + head) * hd : rp.k + ((size_t)i * nkv + h) * hd;
+        rope_pair(in[e], in[e + half_dim], rp.bias ? rp.bias + (size_t)head * hd : nullptr, e, hd, pos, rp.rope_base, out);
+    }
+    {   // value head: bias add only
+        const size_t voff = (size_t)(nh + nkv + h) * hd;
+        __half* out = rp.v + ((size_t)i * nkv + h) * hd;
+        for (int e = threadIdx.x; e < hd; e += kThreads) out[e] = rp.bias ? __hadd(row[voff + e], rp.bias[voff + e]) : row[voff + e];
+    }
+    __threadfence();   // the rows just written are read back below, partly by asynchronous copies
+    __syncthreads();
+    const SeqWrite s = seq_write(p, i);
+    const int ngroups = (s.next_old - s.prev_old) / g.g;
+    for (int j = 0; j < ngroups; ++j) {
+        pack_group(p, g, s, h, j, false, smem_raw);
+        __syncthreads();
+        pack_group(p, g, s, h, j, true, smem_raw);
+        __syncthreads();
+    }
+    if (s.num_new > 0) scratch_update(p, s, h);
+}
+
 size_t pack_smem_bytes(const Geom& g) {
     size_t params = (size_t)(g.d > g.g * g.hg ? g.d : g.g * g.hg);
     return (size_t)g.g * g.d * sizeof(__half) + (3 * params + 4 * kThreads) * sizeof(float);
@@ -346,7 +400,47 @@ cudaError_t launch_pack_for_block(const WriteParams& p, dim3 grid, size_t smem, 
     return cudaSuccess;
 }
 
+template <class Shape>
+cudaError_t launch_rope_write_shape(const RopeParams& rp, const WriteParams& p, size_t smem, cudaStream_t stream) {
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(rope_write_kernel<Shape>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+    }
+    rope_write_kernel<Shape><<<dim3(p.geom.nkv, p.n), kThreads, smem, stream>>>(rp, p);
+    return cudaGetLastError();
+}
+
+template <int D, int G>
+cudaError_t launch_rope_write_for_block(const RopeParams& rp, const WriteParams& p, size_t smem, cudaStream_t stream,
+                                        bool* done) {
+    *done = true;
+    if (p.geom.b == 16) return launch_rope_write_shape<StaticShape<D, G, 16>>(rp, p, smem, stream);
+    if (p.geom.b == 32) return launch_rope_write_shape<StaticShape<D, G, 32>>(rp, p, smem, stream);
+    *done = false;
+    return cudaSuccess;
+}
+
 }  // namespace
+
+// RoPE of one new token per sequence fused with its cache write. p.new_k / p.new_v must be rp.k / rp.v,
+// one row per sequence (new_offsets == nullptr, num_new_scalar == 1).
+cudaError_t launch_rope_write(const RopeParams& rp, const WriteParams& p, cudaStream_t stream) {
+    const Geom& g = p.geom;
+    if (p.n <= 0) return cudaSuccess;
+    if (p.new_k != rp.k || p.new_v != rp.v || p.new_offsets || p.num_new_scalar != 1) return cudaErrorInvalidValue;
+    const size_t smem = pack_smem_bytes(g);
+    bool done = false;
+    cudaError_t e = cudaSuccess;
+    if (g.d == 128 && g.g == 128) e = launch_rope_write_for_block<128, 128>(rp, p, smem, stream, &done);
+    else if (g.d == 128 && g.g == 64) e = launch_rope_write_for_block<128, 64>(rp, p, smem, stream, &done);
+    else if (g.d == 128 && g.g == 32) e = launch_rope_write_for_block<128, 32>(rp, p, smem, stream, &done);
+    else if (g.d == 64 && g.g == 128) e = launch_rope_write_for_block<64, 128>(rp, p, smem, stream, &done);
+    else if (g.d == 64 && g.g == 64) e = launch_rope_write_for_block<64, 64>(rp, p, smem, stream, &done);
+    else if (g.d == 64 && g.g == 32) e = launch_rope_write_for_block<64, 32>(rp, p, smem, stream, &done);
+    if (e != cudaSuccess) return e;
+    if (!done) e = launch_rope_write_shape<DynamicShape>(rp, p, smem, stream);
+    return e;
+}
 
 cudaError_t launch_cache_write(const WriteParams& p, int max_new_per_seq, cudaStream_t stream) {
     const Geom& g = p.geom;

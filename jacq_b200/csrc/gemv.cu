@@ -54,20 +54,28 @@ __global__ void __launch_bounds__(kGemvThreads, kGemvCtasPerSm) gemv_kernel(cons
     __shared__ float warp_sums[32];
     uint4* xs = reinterpret_cast<uint4*>(smem_raw);  // [BT, in_dim / 8]
     const int chunks = in_dim / 8;
+    uint4* ws = xs + BT * chunks;                    // [in_dim / 8] norm weight (add+norm prologues only)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int warps_total = gridDim.x * (kGemvThreads / 32);
     const int gwarp = blockIdx.x * (kGemvThreads / 32) + warp;
+    // A warp owns two rows at a time: neighbours (2k, 2k + 1), or with the SwiGLU epilogue gate row k and up
+    // row k + out_dim of a matrix with 2 * out_dim rows.
+    constexpr bool kSiluOut = PRO == kGemvAddNormSiluOut;
+    constexpr bool kNorm = PRO == kGemvAddNorm || kSiluOut;
+    const int row_step = kSiluOut ? 1 : kRowsPerWarp;
+    const int pair_stride = kSiluOut ? out_dim : 1;
+    const int last_row = kSiluOut ? 2 * out_dim - 1 : out_dim - 1;
     pdl_trigger();
 
     // The weights do not depend on the kernel before this one: the first loads of W go out before
     // waiting for it, so they are in flight while the predecessor drains and the input is prepared.
     uint4 v[kRowsPerWarp][kUnroll];
-    const int first_row = gwarp * kRowsPerWarp;
+    const int first_row = gwarp * row_step;
     bool have = false;
     if (first_row < out_dim && lane + 32 * (kUnroll - 1) < chunks) {
 #pragma unroll
         for (int r = 0; r < kRowsPerWarp; ++r) {
-            const int row = first_row + r < out_dim ? first_row + r : out_dim - 1;
+            const int row = min(first_row + r * pair_stride, last_row);
             const uint4* wr = reinterpret_cast<const uint4*>(w + (size_t)row * in_dim);
 #pragma unroll
             for (int u = 0; u < kUnroll; ++u) v[r][u] = ld_stream(wr + lane + 32 * u);
@@ -79,14 +87,7 @@ __global__ void __launch_bounds__(kGemvThreads, kGemvCtasPerSm) gemv_kernel(cons
     if (PRO == kGemvPlain) {
         for (int c = threadIdx.x; c < BT * chunks; c += kGemvThreads) xs[c] = reinterpret_cast<const uint4*>(pro.x)[c];
         __syncthreads();
-    } else if (PRO == kGemvSiluMul) {
-        for (int c = threadIdx.x; c < BT * chunks; c += kGemvThreads) {
-            const int b = c / chunks, cc = c - b * chunks;
-            const uint4* row = reinterpret_cast<const uint4*>(pro.x + (size_t)b * 2 * in_dim);
-            xs[c] = silu_mul8(row[cc], row[chunks + cc]);
-        }
-        __syncthreads();
-    } else {
+    } else if (kNorm) {
         const bool gathered = pro.gather.tp > 0;
         P2pView view = {};
         if (gathered) view = p2p_view(pro.gather);
@@ -98,6 +99,7 @@ __global__ void __launch_bounds__(kGemvThreads, kGemvCtasPerSm) gemv_kernel(cons
             else if (pro.delta) a = hadd8(a, reinterpret_cast<const uint4*>(pro.delta + (size_t)b * in_dim)[cc]);
             if (pro.x_out && blockIdx.x == 0) reinterpret_cast<uint4*>(pro.x_out + (size_t)b * in_dim)[cc] = a;
             xs[c] = a;
+            if (b == 0) ws[cc] = reinterpret_cast<const uint4*>(pro.weight)[cc];   // needed after the reduction: fetch it now
         }
         __syncthreads();
         float scale[BT];
@@ -110,14 +112,14 @@ __global__ void __launch_bounds__(kGemvThreads, kGemvCtasPerSm) gemv_kernel(cons
             float sc = scale[0];
 #pragma unroll
             for (int k = 1; k < BT; ++k) sc = b == k ? scale[k] : sc;
-            xs[c] = norm_apply8(xs[c], reinterpret_cast<const uint4*>(pro.weight)[cc], sc);
+            xs[c] = norm_apply8(xs[c], ws[cc], sc);
         }
         __syncthreads();
     }
 
     P2pTarget target = {};
     if (pro.push.tp > 0) target = p2p_target(pro.push);
-    for (int row0 = first_row; row0 < out_dim; row0 += warps_total * kRowsPerWarp) {
+    for (int row0 = first_row; row0 < out_dim; row0 += warps_total * row_step) {
         float acc[kRowsPerWarp][BT];
 #pragma unroll
         for (int r = 0; r < kRowsPerWarp; ++r)
@@ -125,10 +127,8 @@ __global__ void __launch_bounds__(kGemvThreads, kGemvCtasPerSm) gemv_kernel(cons
             for (int b = 0; b < BT; ++b) acc[r][b] = 0.0f;
         const uint4* wr[kRowsPerWarp];
 #pragma unroll
-        for (int r = 0; r < kRowsPerWarp; ++r) {
-            int row = row0 + r < out_dim ? row0 + r : out_dim - 1;
-            wr[r] = reinterpret_cast<const uint4*>(w + (size_t)row * in_dim);
-        }
+        for (int r = 0; r < kRowsPerWarp; ++r)
+            wr[r] = reinterpret_cast<const uint4*>(w + (size_t)min(row0 + r * pair_stride, last_row) * in_dim);
         int c = lane;
         for (; c + 32 * (kUnroll - 1) < chunks; c += 32 * kUnroll) {
             if (!have) {
@@ -158,13 +158,16 @@ __global__ void __launch_bounds__(kGemvThreads, kGemvCtasPerSm) gemv_kernel(cons
                 s[r] = acc[r][b];
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) s[r] += __shfl_xor_sync(0xffffffffu, s[r], o);
-                if (lane == 0 && row0 + r < out_dim) {
+                if (!kSiluOut && lane == 0 && row0 + r < out_dim) {
                     if (y32) y32[(size_t)b * ldy + row0 + r] = s[r];
                     if (y16) y16[(size_t)b * ldy + row0 + r] = __float2half_rn(s[r]);
                 }
             }
+            // SwiGLU epilogue: gate and up pass through fp16 like the reference's gate_up buffer, then SiLU(g) * u
+            if (kSiluOut && lane == 0)
+                y16[(size_t)b * ldy + row0] = silu_mul1(__float2half_rn(s[0]), __float2half_rn(s[1]));
             // tensor parallel: the row pair goes straight into every rank's slot (out_dim is even)
-            if (pro.push.tp > 0 && lane == 0 && row0 + 1 < out_dim)
+            if (!kSiluOut && pro.push.tp > 0 && lane == 0 && row0 + 1 < out_dim)
                 p2p_write1(pro.push, target, ((size_t)b * out_dim + row0) >> 1, pack_half2(s[0], s[1]));
         }
     }
@@ -173,14 +176,15 @@ __global__ void __launch_bounds__(kGemvThreads, kGemvCtasPerSm) gemv_kernel(cons
 template <int BT, int PRO>
 cudaError_t launch_bt(const __half* w, const GemvPrologue& pro, __half* y16, float* y32, int out_dim, int in_dim,
                       cudaStream_t stream) {
-    const size_t smem = (size_t)BT * in_dim * sizeof(__half);
+    const bool norm = PRO == kGemvAddNorm || PRO == kGemvAddNormSiluOut;
+    const size_t smem = (size_t)(BT + (norm ? 1 : 0)) * in_dim * sizeof(__half);
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(gemv_kernel<BT, PRO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
     // Enough CTAs to fill the 148 SMs, never more warps than row pairs; all of them
     // resident at once, so a kernel launched behind this one can start as soon as they have.
-    const int warps_needed = (out_dim + kRowsPerWarp - 1) / kRowsPerWarp;
+    const int warps_needed = PRO == kGemvAddNormSiluOut ? out_dim : (out_dim + kRowsPerWarp - 1) / kRowsPerWarp;
     int blocks = (warps_needed + kGemvThreads / 32 - 1) / (kGemvThreads / 32);
     if (blocks > 148 * kGemvCtasPerSm) blocks = 148 * kGemvCtasPerSm;
     cudaLaunchConfig_t cfg = {};
@@ -214,7 +218,10 @@ cudaError_t launch_gemv_fused(const __half* w, int kind, const GemvPrologue& pro
                               int in_dim, int batch, cudaStream_t stream) {
     if (batch < 1 || batch > 4) return cudaErrorInvalidValue;
     if (kind == kGemvAddNorm) return launch_pro<kGemvAddNorm>(w, pro, y16, y32, out_dim, in_dim, batch, stream);
-    if (kind == kGemvSiluMul) return launch_pro<kGemvSiluMul>(w, pro, y16, y32, out_dim, in_dim, batch, stream);
+    if (kind == kGemvAddNormSiluOut) {   // out_dim = gate rows = up rows; fp16 output only
+        if (!y16 || y32) return cudaErrorInvalidValue;
+        return launch_pro<kGemvAddNormSiluOut>(w, pro, y16, y32, out_dim, in_dim, batch, stream);
+    }
     return launch_pro<kGemvPlain>(w, pro, y16, y32, out_dim, in_dim, batch, stream);
 }
 
@@ -264,7 +271,7 @@ __device__ __forceinline__ uint32_t sg_offset(int row, int chunk) {
 template <int NT>   // batch columns padded to 8 * NT
 __global__ void __launch_bounds__(kSgThreads, kSgCtasPerSm) skinny_gemm_kernel(
     const __half* __restrict__ w, const __half* __restrict__ x, __half* __restrict__ y16, float* __restrict__ y32,
-    int out_dim, int in_dim, int batch, int chunks_per_split) {
+    int out_dim, int in_dim, int batch, int chunks_per_split, const P2pPush push) {
     extern __shared__ __align__(128) unsigned char smem[];
     constexpr int XROWS = 8 * NT;
     constexpr int W_BYTES = kSgRows * kSgRowBytes, X_BYTES = XROWS * kSgRowBytes, STAGE = W_BYTES + X_BYTES;
@@ -351,7 +358,11 @@ __global__ void __launch_bounds__(kSgThreads, kSgCtasPerSm) skinny_gemm_kernel(
     }
 
     // acc[m][j] = rows (row0 + 32 warp + 16 m + r, +8) x batch columns (8j + 2t, +1)
+    // tensor parallel (push.tp > 0, out_dim a multiple of 4): the result also goes straight into every
+    // rank's exchange slot, two fp16 rows per 8-byte word
     const int splits = gridDim.y;
+    P2pTarget target = {};
+    if (push.tp > 0) target = p2p_target(push);
     if (splits == 1) {
 #pragma unroll
         for (int m = 0; m < 2; ++m)
@@ -363,6 +374,11 @@ __global__ void __launch_bounds__(kSgThreads, kSgCtasPerSm) skinny_gemm_kernel(
                     if (row < out_dim && col < batch) {
                         if (y32) y32[(size_t)col * out_dim + row] = acc[m][j][e];
                         if (y16) y16[(size_t)col * out_dim + row] = __float2half_rn(acc[m][j][e]);
+                    }
+                    if (push.tp > 0) {   // the lane four up holds the next row of the same column
+                        const float next = __shfl_xor_sync(0xffffffffu, acc[m][j][e], 4);
+                        if ((r & 1) == 0 && row + 1 < out_dim && col < batch)
+                            p2p_write1(push, target, ((size_t)col * out_dim + row) >> 1, pack_half2(acc[m][j][e], next));
                     }
                 }
         return;
@@ -403,6 +419,9 @@ __global__ void __launch_bounds__(kSgThreads, kSgCtasPerSm) skinny_gemm_kernel(
                 if (y16) y16[(size_t)col * out_dim + row] = __float2half_rn(vals[k]);
             }
         }
+        if (push.tp > 0 && row0 + rr + 3 < out_dim)
+            p2p_write2(push, target, ((size_t)col * out_dim + row0 + rr) >> 2, pack_half2(vals[0], vals[1]),
+                       pack_half2(vals[2], vals[3]));
     }
     cluster.sync();   // nobody leaves while a peer may still read its tile
 }
@@ -428,7 +447,7 @@ SkinnyPlan plan_skinny(int out_dim, int in_dim, int batch) {
 
 template <int NT>
 cudaError_t launch_skinny_nt(const __half* w, const __half* x, __half* y16, float* y32, int out_dim, int in_dim, int batch,
-                             const SkinnyPlan& p, cudaStream_t stream) {
+                             const SkinnyPlan& p, const P2pPush& push, cudaStream_t stream) {
     const int smem = kSgStages * (kSgRows + 8 * NT) * kSgRowBytes;
     cudaError_t e = cudaFuncSetAttribute(skinny_gemm_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
@@ -444,25 +463,28 @@ cudaError_t launch_skinny_nt(const __half* w, const __half* x, __half* y16, floa
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, skinny_gemm_kernel<NT>, w, x, y16, y32, out_dim, in_dim, batch, p.chunks_per_split);
+    return cudaLaunchKernelEx(&cfg, skinny_gemm_kernel<NT>, w, x, y16, y32, out_dim, in_dim, batch, p.chunks_per_split, push);
 }
 
 }  // namespace
 
 bool skinny_gemm_supports(int in_dim, int batch) { return batch > 4 && batch <= 64 && in_dim % kSgK == 0; }
 
+// push (may be nullptr): deliver the fp16 result into every rank's exchange slot as well; needs out_dim % 4 == 0.
 cudaError_t launch_skinny_gemm(const __half* w, const __half* x, __half* y16, float* y32, int out_dim, int in_dim,
-                               int batch, cudaStream_t stream) {
+                               int batch, cudaStream_t stream, const P2pPush* push_or_null) {
+    if (push_or_null && out_dim % 4) return cudaErrorInvalidValue;
+    const P2pPush push = push_or_null ? *push_or_null : P2pPush{};
     const SkinnyPlan p = plan_skinny(out_dim, in_dim, batch);
     switch (p.nt) {
-        case 1: return launch_skinny_nt<1>(w, x, y16, y32, out_dim, in_dim, batch, p, stream);
-        case 2: return launch_skinny_nt<2>(w, x, y16, y32, out_dim, in_dim, batch, p, stream);
-        case 3: return launch_skinny_nt<3>(w, x, y16, y32, out_dim, in_dim, batch, p, stream);
-        case 4: return launch_skinny_nt<4>(w, x, y16, y32, out_dim, in_dim, batch, p, stream);
-        case 5: return launch_skinny_nt<5>(w, x, y16, y32, out_dim, in_dim, batch, p, stream);
-        case 6: return launch_skinny_nt<6>(w, x, y16, y32, out_dim, in_dim, batch, p, stream);
-        case 7: return launch_skinny_nt<7>(w, x, y16, y32, out_dim, in_dim, batch, p, stream);
-        default: return launch_skinny_nt<8>(w, x, y16, y32, out_dim, in_dim, batch, p, stream);
+        case 1: return launch_skinny_nt<1>(w, x, y16, y32, out_dim, in_dim, batch, p, push, stream);
+        case 2: return launch_skinny_nt<2>(w, x, y16, y32, out_dim, in_dim, batch, p, push, stream);
+        case 3: return launch_skinny_nt<3>(w, x, y16, y32, out_dim, in_dim, batch, p, push, stream);
+        case 4: return launch_skinny_nt<4>(w, x, y16, y32, out_dim, in_dim, batch, p, push, stream);
+        case 5: return launch_skinny_nt<5>(w, x, y16, y32, out_dim, in_dim, batch, p, push, stream);
+        case 6: return launch_skinny_nt<6>(w, x, y16, y32, out_dim, in_dim, batch, p, push, stream);
+        case 7: return launch_skinny_nt<7>(w, x, y16, y32, out_dim, in_dim, batch, p, push, stream);
+        default: return launch_skinny_nt<8>(w, x, y16, y32, out_dim, in_dim, batch, p, push, stream);
     }
 }
 

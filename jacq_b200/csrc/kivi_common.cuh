@@ -107,7 +107,6 @@ struct DecodeParams {
     int max_chunks;
     float* ws_o;          // [n, NKV, max_chunks, QPK, D]
     float* ws_ml;         // [n, NKV, max_chunks, QPK, 2]  (running max in log2 units, sum)
-    unsigned int* ws_count;  // [n, NKV] arrival counters, zero between launches
     int* status;          // device status word (0 = ok), may be nullptr
 };
 
@@ -306,6 +305,8 @@ __device__ __forceinline__ float fast_exp2(float x) {
 
 // Host-side launchers implemented in the .cu files.
 cudaError_t launch_cache_write(const WriteParams& p, int max_new_per_seq, cudaStream_t stream);
+struct RopeParams;     // step_math.cuh
+cudaError_t launch_rope_write(const RopeParams& rp, const WriteParams& p, cudaStream_t stream);
 // Plans the split over the context, binds the workspace and launches the decode kernel; returns a
 // kivi_status. `out_h` (fp16) replaces `out` (fp32) when non-null.
 int run_decode(const Geom& g, const CachePtrs& cache, const SeqAddressing& seq, const __half* q, float* out,
@@ -321,7 +322,8 @@ struct GemvPrologue;   // step_math.cuh
 cudaError_t launch_gemv_fused(const __half* w, int kind, const GemvPrologue& pro, __half* y16, float* y32, int out_dim,
                               int in_dim, int batch, cudaStream_t stream);
 bool skinny_gemm_supports(int in_dim, int batch);
+struct P2pPush;        // p2p.cuh
 cudaError_t launch_skinny_gemm(const __half* w, const __half* x, __half* y16, float* y32, int out_dim, int in_dim,
-                               int batch, cudaStream_t stream);
+                               int batch, cudaStream_t stream, const P2pPush* push_or_null = nullptr);
 
 }  // namespace kivi

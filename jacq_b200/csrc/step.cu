@@ -75,16 +75,7 @@ __global__ void __launch_bounds__(128) bias_rope_kernel(
     }
     const int pos = positions[rowi];
     __half* out = h < nh ? q + ((size_t)rowi * nh + h) * hd : k + ((size_t)rowi * nkv + (h - nh)) * hd;
-    for (int i = threadIdx.x; i < half_dim; i += blockDim.x) {
-        const float freq = 1.0f / powf(rope_base, (2.0f * i) / hd);
-        const float ang = pos * freq;
-        const float c = cosf(ang), s = sinf(ang);
-        __half h0 = in[i], h1 = in[i + half_dim];
-        if (bh) { h0 = __hadd(h0, bh[i]); h1 = __hadd(h1, bh[i + half_dim]); }
-        const float x0 = __half2float(h0), x1 = __half2float(h1);
-        out[i] = __float2half(x0 * c - x1 * s);
-        out[i + half_dim] = __float2half(x1 * c + x0 * s);
-    }
+    for (int i = threadIdx.x; i < half_dim; i += blockDim.x) rope_pair(in[i], in[i + half_dim], bh, i, hd, pos, rope_base, out);
 }
 
 // out[row, i] = SiLU(gate_up[row, i]) * gate_up[row, ffn + i]; eight elements per thread.
@@ -222,8 +213,8 @@ size_t argmax_payload_bytes(int batch, int vocab) {
 }
 
 // Projection y[b, :] = W x[b, :]. `push` (tensor parallel over peer memory, may be nullptr): the result is
-// a partial sum that every rank needs; up to four sequences deliver it from the GEMV's own epilogue,
-// larger batches through the copy kernel behind the skinny GEMM.
+// a partial sum that every rank needs; the GEMV and the skinny GEMM deliver it from their own epilogue
+// (the copy kernel covers shapes neither can).
 int project(const __half* w, const __half* x, __half* y, int out_dim, int in_dim, int batch, cudaStream_t stream,
             const P2pPush* push = nullptr) {
     if (batch <= 4 && push) {
@@ -232,10 +223,19 @@ int project(const __half* w, const __half* x, __half* y, int out_dim, int in_dim
         pro.push = *push;
         return ok(launch_gemv_fused(w, kGemvPlain, pro, y, nullptr, out_dim, in_dim, batch, stream));
     }
+    if (skinny_gemm_supports(in_dim, batch) && (!push || out_dim % 4 == 0))   // delivers from its own epilogue too
+        return ok(launch_skinny_gemm(w, x, y, nullptr, out_dim, in_dim, batch, stream, push));
     int rc = skinny_gemm_supports(in_dim, batch) ? ok(launch_skinny_gemm(w, x, y, nullptr, out_dim, in_dim, batch, stream))
                                                  : ok(launch_gemv(w, x, y, nullptr, out_dim, in_dim, batch, stream));
     if (rc == KIVI_OK && push) rc = ok(launch_p2p_push(y, (size_t)batch * out_dim * sizeof(__half), *push, stream));
     return rc;
+}
+
+// KIVI_STEP_FUSED_WRITE=0 in the environment runs RoPE and the cache write as their three separate
+// kernels instead of the fused one (a tuning switch; same results).
+bool fused_rope_write() {
+    static const bool on = [] { const char* e = getenv("KIVI_STEP_FUSED_WRITE"); return !e || atoi(e) != 0; }();
+    return on;
 }
 
 // Up to four sequences: the step's element-wise kernels ride in the prologue of the GEMV that
@@ -244,13 +244,17 @@ int project(const __half* w, const __half* x, __half* y, int out_dim, int in_dim
 bool fuse_prologues(int batch) { return batch <= 4; }
 
 // y = W RMSNorm(x (+ delta)); the updated residual rows go to x_out.
+// swiglu_rows > 0: w is a fused gate|up matrix of 2 * swiglu_rows rows and y receives SiLU(gate) * up
+// [batch, swiglu_rows] (small batches only; the caller checks fuse_prologues()).
 int project_add_norm(const __half* w, const __half* x, const int* tokens, const __half* delta, const P2pGather& gather,
                      const __half* weight, __half* x_out, __half* normed_scratch, __half* y, int out_dim, int hidden,
-                     int batch, float eps, cudaStream_t stream) {
+                     int batch, float eps, cudaStream_t stream, int swiglu_rows = 0) {
     if (fuse_prologues(batch)) {
         GemvPrologue pro = {};
         pro.x = x; pro.tokens = tokens; pro.delta = delta; pro.gather = gather; pro.weight = weight; pro.x_out = x_out;
         pro.eps = eps;
+        if (swiglu_rows > 0)
+            return ok(launch_gemv_fused(w, kGemvAddNormSiluOut, pro, y, nullptr, swiglu_rows, hidden, batch, stream));
         return ok(launch_gemv_fused(w, kGemvAddNorm, pro, y, nullptr, out_dim, hidden, batch, stream));
     }
     const int rc = launch_residual_rmsnorm(x, tokens, delta, weight, x_out, normed_scratch, batch, hidden, eps, gather,
@@ -258,15 +262,9 @@ int project_add_norm(const __half* w, const __half* x, const int* tokens, const 
     return rc != KIVI_OK ? rc : project(w, normed_scratch, y, out_dim, hidden, batch, stream);
 }
 
-// y = W (SiLU(gate) * up) for rows [gate | up].
+// y = W (SiLU(gate) * up) for rows [gate | up], larger batches: the stand-alone kernel, then the projection.
 int project_silu_mul(const __half* w, const __half* gate_up, __half* mid_scratch, __half* y, int out_dim, int ffn,
                      int batch, cudaStream_t stream, const P2pPush* push = nullptr) {
-    if (fuse_prologues(batch)) {
-        GemvPrologue pro = {};
-        pro.x = gate_up;
-        if (push) pro.push = *push;
-        return ok(launch_gemv_fused(w, kGemvSiluMul, pro, y, nullptr, out_dim, ffn, batch, stream));
-    }
     const int rc = launch_silu_mul(gate_up, mid_scratch, batch, ffn, stream);
     return rc != KIVI_OK ? rc : project(w, mid_scratch, y, out_dim, ffn, batch, stream, push);
 }
@@ -286,7 +284,6 @@ StepLayout step_layout(const kivi_step_config& c, const Geom& g, int batch, int 
     auto take = [&](size_t bytes) { const size_t o = at; at += up256(bytes); return o; };
     const size_t n = (size_t)batch, h2 = sizeof(__half);
     const int tp = c.tp_size > 1 ? c.tp_size : 1;
-    // zero-initialised region first (arrival counters of the split decode)
     L.decode_ws_bytes = decode_workspace_total(g, batch, split_old(max_seq_len, g.r, g.g));
     L.decode_ws = take(L.decode_ws_bytes);
     L.x0 = take(n * c.hidden * h2);
@@ -473,26 +470,37 @@ extern "C" int kivi_b200_decode_step(const kivi_step_config* cfg, const kivi_ste
                                        normed, qkv, qkv_rows(c), c.hidden, batch, c.norm_eps, stream));
         embed_tokens = nullptr;
         { __half* t = x_cur; x_cur = x_nxt; x_nxt = t; }
-        KIVI_STEP_TRY(launch_bias_rope(qkv, c.attn_bias ? H(lw.qkv_bias) : nullptr, state->seq_lens, q, k, v, batch,
-                                       c.num_q_heads, c.num_kv_heads, c.head_dim, c.rope_base, stream));
+        // bias + RoPE + split and the cache write of the new token: one launch, one CTA per (kv head, sequence)
         WriteParams wp;
         wp.geom = g; wp.cache = to_ptrs(state->caches[l]); wp.seq = wa;
         wp.new_k = k; wp.new_v = v; wp.new_offsets = nullptr; wp.num_new_scalar = 1; wp.n = batch;   // row i = sequence i
-        KIVI_STEP_TRY(ok(launch_cache_write(wp, 1, stream)));
+        if (fused_rope_write()) {
+            RopeParams rp = {qkv, c.attn_bias ? H(lw.qkv_bias) : nullptr, state->seq_lens, q, k, v, c.rope_base};
+            KIVI_STEP_TRY(ok(launch_rope_write(rp, wp, stream)));
+        } else {
+            KIVI_STEP_TRY(launch_bias_rope(qkv, c.attn_bias ? H(lw.qkv_bias) : nullptr, state->seq_lens, q, k, v, batch,
+                                           c.num_q_heads, c.num_kv_heads, c.head_dim, c.rope_base, stream));
+            KIVI_STEP_TRY(ok(launch_cache_write(wp, 1, stream)));
+        }
         KIVI_STEP_TRY(run_decode(g, wp.cache, da, q, nullptr, attn, batch, max_seq_len, max_old, -1, decode_ws,
                                  L.decode_ws_bytes, stream));
         P2pPush push_o = p2p ? push_at(2 * l) : P2pPush{};
         KIVI_STEP_TRY(project(H(lw.o), attn, proj, c.hidden, q_dim, batch, stream, p2p ? &push_o : nullptr));
         KIVI_STEP_TRY(allreduce_hook(proj, proj_bytes));
         // feed-forward block
+        const bool swiglu_in_epilogue = fuse_prologues(batch);   // the gate_up GEMV then writes SiLU(gate) * up itself
         KIVI_STEP_TRY(project_add_norm(H(lw.gate_up), x_cur, nullptr, proj, gather_at(2 * l), H(lw.ffn_norm), x_nxt,
-                                       normed, gate_up, 2 * c.ffn, c.hidden, batch, c.norm_eps, stream));
+                                       normed, swiglu_in_epilogue ? mid : gate_up, 2 * c.ffn, c.hidden, batch, c.norm_eps,
+                                       stream, swiglu_in_epilogue ? c.ffn : 0));
         { __half* t = x_cur; x_cur = x_nxt; x_nxt = t; }
         // the down projection must not overwrite `proj` while a gate_up CTA may still read it as delta:
         // it cannot, every gate_up CTA has finished its prologue before the first down CTA passes its wait
         P2pPush push_down = p2p ? push_at(2 * l + 1) : P2pPush{};
-        KIVI_STEP_TRY(project_silu_mul(H(lw.down), gate_up, mid, proj, c.hidden, c.ffn, batch, stream,
-                                       p2p ? &push_down : nullptr));
+        if (swiglu_in_epilogue)
+            KIVI_STEP_TRY(project(H(lw.down), mid, proj, c.hidden, c.ffn, batch, stream, p2p ? &push_down : nullptr));
+        else
+            KIVI_STEP_TRY(project_silu_mul(H(lw.down), gate_up, mid, proj, c.hidden, c.ffn, batch, stream,
+                                           p2p ? &push_down : nullptr));
         KIVI_STEP_TRY(allreduce_hook(proj, proj_bytes));
         delta = proj;
         delta_site = p2p ? 2 * l + 1 : -1;

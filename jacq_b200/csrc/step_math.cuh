@@ -48,6 +48,38 @@ __device__ __forceinline__ uint4 hadd8(uint4 a, const uint4& d) {
     return a;
 }
 
+// One rotated pair of RoPE after the optional bias add (kernels.cu:40-54, :163-166): elements i and
+// i + hd/2 of a head at position pos; freq = 1 / powf(base, (2 i) / hd), angle = pos * freq.
+__device__ __forceinline__ void rope_pair(__half h0, __half h1, const __half* bias_head, int i, int hd, int pos,
+                                          float rope_base, __half* out_head) {
+    const int half_dim = hd >> 1;
+    const float freq = 1.0f / powf(rope_base, (2.0f * i) / hd);
+    const float ang = pos * freq;
+    const float c = cosf(ang), s = sinf(ang);
+    if (bias_head) { h0 = __hadd(h0, bias_head[i]); h1 = __hadd(h1, bias_head[i + half_dim]); }
+    const float x0 = __half2float(h0), x1 = __half2float(h1);
+    out_head[i] = __float2half(x0 * c - x1 * s);
+    out_head[i + half_dim] = __float2half(x1 * c + x0 * s);
+}
+
+// Input of the fused RoPE + cache-write kernel (cache_write.cu): one qkv row per sequence.
+struct RopeParams {
+    const __half* qkv;      // [n, (NH + 2 NKV) * D]
+    const __half* bias;     // [(NH + 2 NKV) * D] or nullptr
+    const int* positions;   // [n]
+    __half* q;              // [n, NH, D]
+    __half* k;              // [n, NKV, D]: the writer's new_k
+    __half* v;              // [n, NKV, D]: the writer's new_v
+    float rope_base;
+};
+
+// SiLU(gate) * up for one pair (kernels.cu:146-153).
+__device__ __forceinline__ __half silu_mul1(__half g, __half u) {
+    const float gv = __half2float(g);
+    const float sv = gv / (1.0f + expf(-gv));
+    return __float2half(sv * __half2float(u));
+}
+
 // SiLU(gate) * up for eight fp16 values: g / (1 + expf(-g)) * up   (kernels.cu:146-153).
 __device__ __forceinline__ uint4 silu_mul8(const uint4& g, const uint4& u) {
     const __half* gh = reinterpret_cast<const __half*>(&g);
@@ -64,9 +96,12 @@ __device__ __forceinline__ uint4 silu_mul8(const uint4& g, const uint4& u) {
 }
 
 // What a GEMV does to its input rows before the product.
-enum GemvPrologueKind { kGemvPlain = 0, kGemvAddNorm = 1, kGemvSiluMul = 2 };
+// kGemvAddNormSiluOut: the add+norm prologue with a SwiGLU epilogue for the fused gate|up matrix: the warp
+// that owns gate row i also owns up row i (i + out_dim) and stores SiLU(gate_i) * up_i, so the product
+// never exists unfused and the down projection reads its input as is.
+enum GemvPrologueKind { kGemvPlain = 0, kGemvAddNorm = 1, kGemvAddNormSiluOut = 2 };
 struct GemvPrologue {
-    const __half* x;        // plain: [batch, in]; add+norm: residual rows (or a table with `tokens`); silu: [batch, 2 * in] gate|up
+    const __half* x;        // plain: [batch, in]; add+norm: residual rows (or a table with `tokens`)
     const int* tokens;      // add+norm: optional row gather (embedding lookup)
     const __half* delta;    // add+norm: optional [batch, in] added first
     P2pGather gather;       // add+norm: when gather.tp > 0 the delta is the sum of the ranks' slots of that site instead

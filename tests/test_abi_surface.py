@@ -142,7 +142,7 @@ def test_v2_interface_and_host_only_calls(native_lib):
     flag = ctypes.c_int(-1)
     assert native_lib.kivi_b200_validate_geometry(ctypes.byref(odd), ctypes.byref(flag)) == 0 and flag.value == 0
     g = geometry_struct(model_layout("mistral-7b"))
-    assert native_lib.kivi_b200_decode_workspace_bytes(ctypes.byref(g), 128, 8192) >= 128 * 8 * 4
+    assert native_lib.kivi_b200_decode_workspace_bytes(ctypes.byref(g), 128, 8192) >= 256   # unsplit plan: a token amount
     assert native_lib.kivi_b200_decode_workspace_bytes(ctypes.byref(g), 1, 32768) > 8 * 8 * 4 * 130 * 4
     assert native_lib.kivi_b200_decode_workspace_bytes(ctypes.byref(bad), 1, 100) == 0
     # argument validation happens on the host, before anything is launched
