@@ -337,6 +337,13 @@ def run_b200(args):
     peak, peak_kind = _peaks()
     kernel_ms = statistics.mean(per_step_ms)
     achieved = step_bytes / (kernel_ms * 1e-3) / 1e9
+    # DRAM bytes per launch: one ncu capture of this kernel on 48 sequences of the same shape read 446.99 MB and
+    # wrote 3.93 MB against 447.58 MB of algorithmic bytes; traffic grows with the sequences, so that ratio is
+    # applied to this launch (profiles/decode_mma_kernel_mistral7b_b48_t8192.md)
+    traffic, traffic_source = None, None
+    if key == "mistral7b" and context == 8192:
+        traffic = step_bytes * (446.99 + 3.93) / 447.58
+        traffic_source = "ncu dram__bytes_read+write of a 48-sequence launch, scaled by sequences"
     line = {
         "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
@@ -354,7 +361,7 @@ def run_b200(args):
         "gpu_launches": args.steps,
         "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_source": f"{peak_kind} HBM copy bandwidth",
+                     "traffic": traffic, "traffic_source": traffic_source, "peak_source": f"{peak_kind} HBM copy bandwidth",
                      "kernel": "decode_mma_kernel", "ms_per_launch": kernel_ms},
         "writer": writer,
     }

@@ -208,6 +208,26 @@ __device__ __forceinline__ void pack_group(const WriteParams& p, const Shape& g,
         }
     }
     __syncthreads();
+    if (kThreads % words_per_row == 0) {
+        // a thread packs the same eight channels of every token it visits: their parameters stay in registers
+        const int w = threadIdx.x % words_per_row;
+        float mn[8], sc[8], rc[8];
+#pragma unroll
+        for (int e = 0; e < 8; e += 4) {
+            *reinterpret_cast<float4*>(mn + e) = *reinterpret_cast<const float4*>(p_min + w * 8 + e);
+            *reinterpret_cast<float4*>(sc + e) = *reinterpret_cast<const float4*>(p_scale + w * 8 + e);
+            *reinterpret_cast<float4*>(rc + e) = *reinterpret_cast<const float4*>(p_rcp + w * 8 + e);
+        }
+        const bool exact = s_exact != 0;
+        for (int idx = threadIdx.x; idx < g.g * words_per_row; idx += kThreads) {
+            const int t = idx / words_per_row;
+            const uint4 v = reinterpret_cast<const uint4*>(tile)[idx];
+            const size_t page = (size_t)s.bt[lp0 + t / g.b];
+            uint32_t* dst = reinterpret_cast<uint32_t*>(p.cache.k_code + ((page * nkv + h) * g.b + (t % g.b)) * (g.d / 2));
+            dst[w] = pack_word(v, mn, sc, rc, exact);
+        }
+        return;
+    }
     for (int idx = threadIdx.x; idx < g.g * words_per_row; idx += kThreads) {
         const int t = idx / words_per_row, w = idx - t * words_per_row;
         const uint4 v = reinterpret_cast<const uint4*>(tile)[idx];
