@@ -19,7 +19,7 @@ roofline        achieved = algorithmic bytes per launch / mean CUDA-event time o
 cpu_baseline    the scalar CPU oracle (test infrastructure, a port of the reference's kernel math)
                 timed on the host cores on a bounded sample of the same workload
 --impl reference  times that CPU port with all host threads (the reference's own implementation of
-                this path is CUDA-only and cannot express this geometry; see DESIGN.md)
+                this path is CUDA-only and cannot express this geometry)
 """
 from __future__ import annotations
 

@@ -92,13 +92,13 @@ __device__ __forceinline__ unsigned clamp_code(float q) {
 //   * 0 <= q <= 15 then holds by construction (mn <= x <= mx, scale = (mx-mn)/15), so no clamp;
 //   * q + 1.5*2^23 leaves rint(q), ties to even, in the low mantissa bits. A NaN element gives
 //     NaN + magic = NaN, whose low nibble the caller masks: 0x7fffffff would give 15, so NaN is
-//     squashed to 0 first, as the reference's conversion does.
+//     squashed to 0 first (fmaxf with 0), as the reference's conversion does.
 // Returns the raw bits of q + magic; the caller folds eight of them into a word.
 __device__ __forceinline__ unsigned code_bits_fast(float x, float mn, float scale, float rcp) {
     const float a = __fsub_rn(x, mn);
     float q = __fmul_rn(a, rcp);
     q = __fmaf_rn(__fmaf_rn(-scale, q, a), rcp, q);
-    q = q == q ? q : 0.0f;
+    q = fmaxf(q, 0.0f);   // NaN -> 0 in one instruction (fmaxf returns the other operand); q is never negative otherwise
     return __float_as_uint(__fadd_rn(q, 12582912.0f));
 }
 __device__ __forceinline__ unsigned code_exact(float x, float mn, float scale) {

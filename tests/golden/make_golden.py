@@ -7,7 +7,7 @@ not). Inputs are seeded; outputs are what the reference's hand-CUDA writer
 (crates/jac-codegen-cuda/tests/snapshots/kernels/decode_attention_kivi_*_library_flash.cu,
 TP=2 local-rank clones: NH/NKV 20/4) produce for them.
 
-    python tests/golden/make_golden.py --out gpurun_out/golden
+    python tests/golden/make_golden.py --out golden_out
 
 Writes reflane_tp2_writer_decode.npz and reflane_tp2_edge_values.npz.
 """

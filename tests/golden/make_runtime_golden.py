@@ -6,7 +6,7 @@ oracle/ref_runtime_shim.cu) into oracle/_ref/libjacq_ref.so. Inputs are seeded a
 outputs, except the weights of the tiny model, which tests rebuild from the seed (a checksum is
 stored).
 
-    python tests/golden/make_runtime_golden.py --out gpurun_out/golden
+    python tests/golden/make_runtime_golden.py --out golden_out
 
 Cases: rmsnorm_kernel after vadd_kernel, bias_add_kernel + rope_qk_kernel (tiny and Qwen2.5-14B
 head shapes, positions up to 32767), silu_mul_kernel, argmax_kernel, and 60 greedy tokens of the
@@ -49,7 +49,7 @@ def _p(t):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--out", default="gpurun_out/golden")
+    ap.add_argument("--out", default="golden_out")
     args = ap.parse_args()
     out_dir = Path(args.out)
     out_dir.mkdir(parents=True, exist_ok=True)
