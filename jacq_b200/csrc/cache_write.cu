@@ -105,6 +105,34 @@ __device__ __forceinline__ unsigned code_exact(float x, float mn, float scale) {
     return clamp_code(__fdiv_rn(__fsub_rn(x, mn), scale));
 }
 
+// Two elements at a time with the packed fp32 instructions of sm_100 (add / mul / fma .f32x2: two
+// independent IEEE round-to-nearest operations per instruction, so the bits are those of
+// code_bits_fast). Returns the raw bits of both q + magic values.
+__device__ __forceinline__ unsigned long long f32x2(float lo, float hi) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ uint2 code_bits_fast2(float x0, float x1, unsigned long long neg_mn, unsigned long long neg_scale,
+                                                 unsigned long long rcp) {
+    unsigned long long a, q, r;
+    const unsigned long long x = f32x2(x0, x1);
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(a) : "l"(x), "l"(neg_mn));
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(q) : "l"(a), "l"(rcp));
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(neg_scale), "l"(q), "l"(a));
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(q) : "l"(r), "l"(rcp), "l"(q));
+    float q0, q1;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(q0), "=f"(q1) : "l"(q));
+    q0 = fmaxf(q0, 0.0f);   // NaN -> 0
+    q1 = fmaxf(q1, 0.0f);
+    const unsigned long long magic = f32x2(12582912.0f, 12582912.0f);
+    unsigned long long m;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(m) : "l"(f32x2(q0, q1)), "l"(magic));
+    uint2 bits;
+    asm("mov.b64 {%0, %1}, %2;" : "=r"(bits.x), "=r"(bits.y) : "l"(m));
+    return bits;
+}
+
 template <class Shape>
 __device__ __forceinline__ void stage_tile(const Shape& g, const WriteParams& p, const SeqWrite& s,
                                            const __half* scratch, const __half* fresh, int h, int pos0, __half* tile) {
@@ -134,7 +162,11 @@ __device__ __forceinline__ unsigned pack_word(const uint4& v, const float* mn, c
     if (!exact) {
         // Horner over the nibbles: every term is 0x4B400000 + code
 #pragma unroll
-        for (int e = 7; e >= 0; --e) word = word * 16u + code_bits_fast(x[e], mn[e], sc[e], rc[e]);
+        for (int e = 6; e >= 0; e -= 2) {
+            const uint2 b = code_bits_fast2(x[e], x[e + 1], f32x2(-mn[e], -mn[e + 1]), f32x2(-sc[e], -sc[e + 1]),
+                                            f32x2(rc[e], rc[e + 1]));
+            word = (word * 16u + b.y) * 16u + b.x;
+        }
         word -= 0x4B400000u * 0x11111111u;
     } else {
 #pragma unroll

@@ -7,8 +7,7 @@
 // The partials were written by other SMs, so every read is an L2 round trip of the order of a
 // microsecond; the kernel is organised so that each thread has all of its loads in flight at once
 // (thread (lane of chunks, run of four channels) owns every LANES-th chunk), pays that latency once
-// and finishes through shared memory. It is launched with programmatic stream serialisation: its
-// CTAs are resident and waiting when the decode kernel retires.
+// and finishes through shared memory.
 #include "decode_merge.cuh"
 
 namespace kivi {
@@ -93,17 +92,7 @@ cudaError_t launch_decode_merge(const DecodeParams& p, cudaStream_t stream) {
     if (p.geom.d % 4 || p.geom.d / 4 > kMergeThreads) return cudaErrorInvalidValue;
     const size_t smem = (((size_t)p.max_chunks * sizeof(float2) + 15) / 16) * 16 + (size_t)kMergeThreads * sizeof(float4);
     if (smem > 48 * 1024) return cudaErrorInvalidValue;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(p.geom.qpk, p.geom.nkv, p.n);
-    cfg.blockDim = dim3(kMergeThreads, 1, 1);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, decode_merge_kernel, p);
+    return launch_pdl(decode_merge_kernel, dim3(p.geom.qpk, p.geom.nkv, p.n), dim3(kMergeThreads), smem, stream, p);
 }
 
 }  // namespace kivi

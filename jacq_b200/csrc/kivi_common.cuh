@@ -241,10 +241,12 @@ __device__ __forceinline__ void ldmatrix_x4_32(uint32_t (&r)[4], uint32_t a) {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-// The small kernels of the attention chain (RoPE, writer, decode) can be launched this way too
-// (KIVI_PDL_CHAIN=1 in the environment), but measured slower than ordinary launches inside a CUDA graph
-// (7.58 vs 7.46 ms per decode step): early launch pays only where there is something to do before the
-// wait, as in the GEMVs, which prefetch their weights. The kernels are correct either way.
+// The small kernels of the attention chain (RoPE + write, decode, merge) can be launched this way too
+// (KIVI_PDL_CHAIN=1 in the environment), but that measured slower than ordinary launches inside a CUDA
+// graph: 7.02 vs 6.01 ms per decode step with the merge kernel alone launched early. Early launch pays
+// where there is something to do before the wait, as in the GEMVs, which prefetch their weights; a
+// small kernel parked behind the decode kernel only takes resources from it. The kernels are correct
+// either way.
 inline bool pdl_chain_enabled() {
     static const bool on = [] { const char* e = getenv("KIVI_PDL_CHAIN"); return e && atoi(e) != 0; }();
     return on;

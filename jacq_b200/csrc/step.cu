@@ -217,10 +217,10 @@ size_t argmax_payload_bytes(int batch, int vocab) {
 // (the copy kernel covers shapes neither can).
 int project(const __half* w, const __half* x, __half* y, int out_dim, int in_dim, int batch, cudaStream_t stream,
             const P2pPush* push = nullptr) {
-    if (batch <= 4 && push) {
+    if (batch <= 4) {
         GemvPrologue pro = {};
         pro.x = x;
-        pro.push = *push;
+        if (push) pro.push = *push;
         return ok(launch_gemv_fused(w, kGemvPlain, pro, y, nullptr, out_dim, in_dim, batch, stream));
     }
     if (skinny_gemm_supports(in_dim, batch) && (!push || out_dim % 4 == 0))   // delivers from its own epilogue too
