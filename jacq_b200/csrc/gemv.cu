@@ -293,7 +293,7 @@ __global__ void __launch_bounds__(kSgThreads, kSgCtasPerSm) skinny_gemm_kernel(
     // each thread always copies the same (row, 16-byte column) positions of a tile
     const int cp_row = threadIdx.x >> 3, cp_chunk = threadIdx.x & 7;   // rows cp_row + 16 k
     const uint32_t cp_dst = sg_offset(cp_row, cp_chunk);               // row parity is that of cp_row
-    auto issue = [&](int c) {
+    auto issue_w = [&](int c) {
         const uint32_t st = s32 + (uint32_t)(c % kSgStages) * STAGE;
         const size_t k0 = (size_t)(c0 + c) * kSgK;
 #pragma unroll
@@ -301,6 +301,10 @@ __global__ void __launch_bounds__(kSgThreads, kSgCtasPerSm) skinny_gemm_kernel(
             const int row = min(row0 + cp_row + 16 * k, out_dim - 1);
             cp_async16_32(st + cp_dst + (uint32_t)(16 * k) * kSgRowBytes, w + (size_t)row * in_dim + k0 + cp_chunk * 8);
         }
+    };
+    auto issue_x = [&](int c) {
+        const uint32_t st = s32 + (uint32_t)(c % kSgStages) * STAGE;
+        const size_t k0 = (size_t)(c0 + c) * kSgK;
 #pragma unroll
         for (int k = 0; k < (XROWS + 15) / 16; ++k) {
             const int row = cp_row + 16 * k;
@@ -309,9 +313,16 @@ __global__ void __launch_bounds__(kSgThreads, kSgCtasPerSm) skinny_gemm_kernel(
                               x + (size_t)row * in_dim + k0 + cp_chunk * 8);
         }
     };
+    auto issue = [&](int c) { issue_w(c); issue_x(c); };
+    // The weights do not depend on the kernel before this one: the W tiles of the first stages are requested
+    // before waiting for it (the kernel may have been launched early), the x chunks after.
+    pdl_trigger();
+    for (int c = 0; c < kSgStages - 1; ++c)
+        if (c < nchunks) issue_w(c);
+    pdl_wait();
     for (int c = 0; c < kSgStages - 1; ++c) {
-        if (c < nchunks) issue(c);
-        asm volatile("cp.async.commit_group;" ::: "memory");
+        if (c < nchunks) issue_x(c);
+        asm volatile("cp.async.commit_group;" ::: "memory");   // group c: x chunk c (and, in group 0, every early W tile)
     }
 
     float acc[2][NT][4];
@@ -445,6 +456,12 @@ SkinnyPlan plan_skinny(int out_dim, int in_dim, int batch) {
     return p;
 }
 
+// KIVI_SKINNY_EARLY=0 in the environment launches the skinny GEMM the ordinary way (tuning switch).
+inline bool skinny_early_launch() {
+    static const bool on = [] { const char* e = getenv("KIVI_SKINNY_EARLY"); return !e || atoi(e) != 0; }();
+    return on;
+}
+
 template <int NT>
 cudaError_t launch_skinny_nt(const __half* w, const __half* x, __half* y16, float* y32, int out_dim, int in_dim, int batch,
                              const SkinnyPlan& p, const P2pPush& push, cudaStream_t stream) {
@@ -456,13 +473,15 @@ cudaError_t launch_skinny_nt(const __half* w, const __half* x, __half* y16, floa
     cfg.blockDim = dim3(kSgThreads, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = p.splits;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = skinny_early_launch() ? 2 : 1;
     return cudaLaunchKernelEx(&cfg, skinny_gemm_kernel<NT>, w, x, y16, y32, out_dim, in_dim, batch, p.chunks_per_split, push);
 }
 

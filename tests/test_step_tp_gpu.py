@@ -17,13 +17,15 @@ pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
 
 
+@pytest.mark.parametrize("batch", [3, 6])
 @pytest.mark.parametrize("comm", ["nccl", "p2p"])
-def test_two_rank_step(native_lib, comm):
+def test_two_rank_step(native_lib, comm, batch):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
-           "127.0.0.1", "--master-port", "29611" if comm == "nccl" else "29612", str(ROOT / "tests" / "tp_worker.py"), comm]
+           "127.0.0.1", "--master-port", str(29611 + (comm == "p2p") + 2 * (batch > 4)), str(ROOT / "tests" / "tp_worker.py"), comm,
+           str(batch)]
     proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
     out = proc.stdout + proc.stderr
     assert proc.returncode == 0, out[-4000:]

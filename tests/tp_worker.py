@@ -23,6 +23,7 @@ TINY = so.StepShape(layers=2, hidden=256, nh=4, nkv=2, hd=64, ffn=512, vocab=102
 
 def main():
     comm = sys.argv[1] if len(sys.argv) > 1 else "nccl"
+    batch = int(sys.argv[2]) if len(sys.argv) > 2 else 3   # <= 4: GEMV with fused prologues; above: skinny GEMM path
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     device = torch.device(f"cuda:{int(os.environ['LOCAL_RANK'])}")
     torch.cuda.set_device(device)
@@ -32,7 +33,7 @@ def main():
                             norm_eps=s.norm_eps, attn_bias=s.attn_bias, block_size=s.block, group_size=s.group,
                             residual=s.residual)
     w = so.random_weights(s, 21)
-    batch, per_seq, steps = 3, 8, 80
+    per_seq, steps = 8, 80
     bt = np.random.default_rng(9).permutation(batch * per_seq).reshape(batch, per_seq).astype(np.int32)
     oracle = so.StepOracle(s, w, bt, batch * per_seq, world=world)
     vl = s.vocab // world
@@ -43,7 +44,7 @@ def main():
     rt = DecodeRuntime(cfg, shard, batch=batch, max_seq_len=per_seq * s.block + s.residual, device=device, rank=rank,
                        world=world, group=dist.group.WORLD, block_tables=torch.from_numpy(bt), comm=comm)
     dist.all_reduce(torch.zeros(8, device=device, dtype=torch.float16))   # communicator up before any capture
-    tok = np.array([4, 99, 512], np.int32)
+    tok = (np.arange(batch, dtype=np.int32) * 101 + 4) % s.vocab
     worst = 0.0
     for i in range(steps):
         if i == steps // 2:
@@ -64,7 +65,7 @@ def main():
     rt.close()
     dist.barrier()
     torch.cuda.synchronize()
-    print(f"TP_WORKER_OK comm={comm} rank={rank} worst_abs_err={worst:.3e}", flush=True)
+    print(f"TP_WORKER_OK comm={comm} batch={batch} rank={rank} worst_abs_err={worst:.3e}", flush=True)
     # leave without tearing the communicator down: destroying a process group whose collectives sit in a
     # captured CUDA graph has been seen to block for minutes
     sys.stdout.flush()
