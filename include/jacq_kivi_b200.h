@@ -135,6 +135,21 @@ int kivi_b200_decode(const kivi_geometry* geom, const kivi_cache* cache, const k
                      const int32_t* slot_ids, int batch, int max_seq_len, float* out,
                      void* workspace, size_t workspace_bytes, cudaStream_t stream);
 
+/* Sparse-retained decode for `batch` sequences (the reference's jac_launch_sparse_retained applied per
+ * sequence: crates/jac-codegen-cuda/src/variants.rs:2620-2691, :2737-2742; tables built by the page-aware
+ * allocator, integrations/vllm_kivi/source_patch.py:1839-1900). Row i of retained_block_tables is sequence
+ * i's COMPACT table: its first retained_pages[i] entries are the old pages still kept, in their original
+ * order; a sequence scans min(retained_pages[i], its dense old pages, max_blocks_per_seq) of them and then
+ * its fp16 residual, whose bounds still follow the dense seq_lens[i]. retained_pages is a device array, so a
+ * batch can mix sequences that dropped pages with dense ones (give those their dense table and a count at
+ * least as large as their dense page count). The tensor-core kernel covers group_size == block_size; other
+ * geometries run the generic kernel. Everything else as kivi_b200_decode. */
+int kivi_b200_decode_sparse(const kivi_geometry* geom, const kivi_cache* cache, const kivi_f16* q,
+                            const int32_t* retained_block_tables, int max_blocks_per_seq,
+                            const int32_t* seq_lens, const int32_t* retained_pages, const int32_t* slot_ids,
+                            int batch, int max_seq_len, float* out, void* workspace, size_t workspace_bytes,
+                            cudaStream_t stream);
+
 /* Decode for callers that cannot allocate device memory. Some hosts of this library hand it
  * buffers but have no allocator of their own to ask for a workspace: a serving runtime whose memory
  * pool was sized and frozen at start-up, a plugin running inside someone else's captured step, a

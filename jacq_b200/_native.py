@@ -87,6 +87,8 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "kivi_b200_decode_workspace_init": (c_int, [_P, c_size_t, _P]),
     "kivi_b200_decode": (c_int, [ctypes.POINTER(KiviGeometry), ctypes.POINTER(KiviCacheStruct), _P, _P, c_int, _P, _P,
                                  c_int, c_int, _P, _P, c_size_t, _P]),
+    "kivi_b200_decode_sparse": (c_int, [ctypes.POINTER(KiviGeometry), ctypes.POINTER(KiviCacheStruct), _P, _P, c_int, _P, _P,
+                                        _P, c_int, c_int, _P, _P, c_size_t, _P]),
     "kivi_b200_decode_noalloc": (c_int, [ctypes.POINTER(KiviGeometry), ctypes.POINTER(KiviCacheStruct), _P, _P, c_int, _P,
                                          _P, c_int, c_int, _P, _P]),
     "kivi_b200_gemv_f16": (c_int, [_P, _P, _P, _P, c_int, c_int, c_int, _P]),

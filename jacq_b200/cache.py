@@ -93,6 +93,9 @@ class KiviCache:
             t.K_RESIDUAL_SCRATCH.data_ptr(), t.V_RESIDUAL_SCRATCH.data_ptr(), num_blocks, num_slots)
         self._workspace: torch.Tensor | None = None
         self._workspace_key: tuple[int, int] | None = None
+        # sparse-retained state: keep_mask[slot, logical page] is False for old pages that were dropped
+        self.keep_mask = torch.ones((num_slots, max_blocks_per_seq), dtype=torch.bool, device=self.device)
+        self._sparse = False
 
     # ---- page bookkeeping (host) ---------------------------------------------------------------
     def set_block_tables(self, tables: torch.Tensor) -> None:
@@ -100,6 +103,32 @@ class KiviCache:
         tables = tables.to(device=self.device, dtype=torch.int32)
         self.block_tables.zero_()
         self.block_tables[: tables.shape[0], : tables.shape[1]] = tables
+
+    def drop_pages(self, slot: int, logical_pages) -> list[int]:
+        """Evict whole old pages of one sequence (the page-aware allocator's move,
+        ``integrations/vllm_kivi/source_patch.py:1839-1900`` of the reference): later decodes skip them
+        through a compact table; the writer keeps its dense table, whose entries for dropped pages are
+        never read again. Returns the physical page ids that are now free for other sequences."""
+        pages = torch.as_tensor(sorted({int(p) for p in logical_pages}), dtype=torch.long, device=self.device)
+        if pages.numel() == 0:
+            return []
+        if int(pages.min()) < 0 or int(pages.max()) >= self.max_blocks_per_seq:
+            raise ValueError("logical page outside the block table")
+        self.keep_mask[slot, pages] = False
+        self._sparse = True
+        return [int(p) for p in self.block_tables[slot, pages].tolist()]
+
+    def retained_tables(self, lens: torch.Tensor, tables: torch.Tensor, mask: torch.Tensor):
+        """Compact tables and retained-page counts for the current lengths, built on the device:
+        kept pages first (stable order), count = kept pages among each sequence's dense old pages."""
+        lay = self.layout
+        old = torch.clamp(lens.to(torch.int64) - lay.residual_tokens, min=0) // lay.group_size * lay.group_size
+        dense_pages = (old // lay.block_size).to(torch.int64)
+        idx = torch.arange(tables.shape[1], device=self.device)
+        live = mask & (idx[None, :] < dense_pages[:, None])
+        order = torch.argsort((~live).to(torch.int8), dim=1, stable=True)
+        compact = torch.gather(tables, 1, order).contiguous()
+        return compact, live.sum(dim=1).to(torch.int32).contiguous()
 
     def bytes_allocated(self) -> int:
         return sum(getattr(self.tensors, n).numel() * getattr(self.tensors, n).element_size()
@@ -174,6 +203,15 @@ class KiviCache:
         if lens.dtype != torch.int32:
             raise TypeError("SEQ_LENS must be torch.int32")
         ws, ws_bytes = self.workspace(batch, max_seq_len)
+        if self._sparse:
+            mask = self.keep_mask if slot_ids is None else self.keep_mask.index_select(0, slot_ids.long())
+            compact, counts = self.retained_tables(lens[:batch], tables[:batch], mask[:batch])
+            rc = _native.lib().kivi_b200_decode_sparse(
+                ctypes.byref(self._geom), ctypes.byref(self._struct), _ptr(q), _ptr(compact), self.max_blocks_per_seq,
+                _ptr(lens), _ptr(counts), _ptr(slot_ids), batch, max_seq_len, _ptr(out), _ptr(ws), ws_bytes,
+                _stream_ptr(self.device))
+            _native.check(rc, "kivi_b200_decode_sparse")
+            return out
         rc = _native.lib().kivi_b200_decode(
             ctypes.byref(self._geom), ctypes.byref(self._struct), _ptr(q), _ptr(tables), self.max_blocks_per_seq,
             _ptr(lens), _ptr(slot_ids), batch, max_seq_len, _ptr(out), _ptr(ws), ws_bytes, _stream_ptr(self.device))

@@ -96,10 +96,10 @@ size_t decode_workspace_total(const Geom& g, int n, int max_old_tokens) {
 
 int run_decode(const Geom& g, const CachePtrs& cache, const SeqAddressing& seq, const __half* q, float* out,
                __half* out_h, int n, int max_seq_cap, int max_old_tokens, int retained_pages, void* ws,
-               size_t ws_bytes, cudaStream_t stream) {
+               size_t ws_bytes, cudaStream_t stream, const int* retained_dev) {
     DecodeParams p;
     p.geom = g; p.cache = cache; p.seq = seq; p.q = q; p.out = out; p.out_h = out_h; p.n = n;
-    p.max_seq = max_seq_cap; p.retained_pages = retained_pages; p.status = nullptr;
+    p.max_seq = max_seq_cap; p.retained_pages = retained_pages; p.retained_dev = retained_dev; p.status = nullptr;
     const SplitPlan sp = plan_split(g, n, max_old_tokens);
     const WsLayout wl = ws_layout(g, n, sp);
     p.chunk_tokens = sp.chunk_tokens;
@@ -111,7 +111,7 @@ int run_decode(const Geom& g, const CachePtrs& cache, const SeqAddressing& seq, 
     unsigned char* base = static_cast<unsigned char*>(ws);
     p.ws_ml = base ? reinterpret_cast<float*>(base + wl.ml_off) : nullptr;
     p.ws_o = base ? reinterpret_cast<float*>(base + wl.o_off) : nullptr;
-    cudaError_t e = decode_mma_supports(g, retained_pages) ? launch_decode_mma(p, stream)
+    cudaError_t e = decode_mma_supports(g, retained_dev ? 0 : retained_pages) ? launch_decode_mma(p, stream)
                                                            : launch_decode_generic(p, stream);
     if (e == cudaSuccess) e = launch_decode_merge(p, stream);   // nothing to do unless the plan splits the context
     return e == cudaSuccess ? KIVI_OK : KIVI_ERR_CUDA;
@@ -281,6 +281,33 @@ extern "C" size_t kivi_b200_decode_workspace_bytes(const kivi_geometry* geom, in
 extern "C" int kivi_b200_decode_workspace_init(void* workspace, size_t workspace_bytes, cudaStream_t stream) {
     if (!workspace) return workspace_bytes ? KIVI_ERR_NULL_POINTER : KIVI_OK;
     return cudaMemsetAsync(workspace, 0, workspace_bytes, stream) == cudaSuccess ? KIVI_OK : KIVI_ERR_CUDA;
+}
+
+extern "C" int kivi_b200_decode_sparse(const kivi_geometry* geom, const kivi_cache* cache, const kivi_f16* q,
+                                       const int32_t* retained_block_tables, int max_blocks_per_seq,
+                                       const int32_t* seq_lens, const int32_t* retained_pages, const int32_t* slot_ids,
+                                       int batch, int max_seq_len, float* out, void* workspace, size_t workspace_bytes,
+                                       cudaStream_t stream) {
+    int rc = check_geometry(geom);
+    if (rc != KIVI_OK) return rc;
+    rc = check_cache(cache);
+    if (rc != KIVI_OK) return rc;
+    if (!q || !retained_block_tables || !seq_lens || !retained_pages || !out) return KIVI_ERR_NULL_POINTER;
+    if (!aligned16(q) || !aligned16(out)) return KIVI_ERR_ALIGNMENT;
+    if (batch < 0 || max_seq_len < 0 || max_seq_len > 0x3fffffff || max_blocks_per_seq < 0) return KIVI_ERR_RANGE;
+    if (batch == 0) return KIVI_OK;
+    if (!slot_ids && batch > cache->num_slots) return KIVI_ERR_RANGE;
+    const Geom g = make_geom(*geom);
+    SeqAddressing a;
+    a.seq_lens = seq_lens; a.seq_len_scalar = 0;
+    a.block_tables = retained_block_tables; a.bt_stride = max_blocks_per_seq; a.bt_width = max_blocks_per_seq;
+    a.slot_ids = slot_ids; a.slot_shared = 0;
+    // the launch is planned for the longest dense context; a sequence scans min(its count, its dense pages,
+    // the table width) pages of its compact table
+    long long max_old = split_old(max_seq_len, g.r, g.g);
+    if (max_old > (long long)max_blocks_per_seq * g.b) max_old = (long long)max_blocks_per_seq * g.b;
+    return run_decode(g, cache_ptrs(*cache), a, reinterpret_cast<const __half*>(q), out, nullptr, batch, max_seq_len,
+                      (int)max_old, -1, workspace, workspace_bytes, stream, retained_pages);
 }
 
 extern "C" int kivi_b200_decode(const kivi_geometry* geom, const kivi_cache* cache, const kivi_f16* q,

@@ -22,7 +22,7 @@ __global__ void __launch_bounds__(256) decode_generic_kernel(const DecodeParams 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
 
     const int seq_len = seq_len_of(p.seq, i);
-    const DecodeBounds bnd = effective_bounds(p, seq_len);
+    const DecodeBounds bnd = effective_bounds(p, seq_len, i);
     const int old_valid = bnd.old_valid;
     const ChunkWork work = chunk_work(p, bnd, chunk);
     const int nchunks = work.nchunks;

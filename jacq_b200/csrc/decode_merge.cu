@@ -22,7 +22,7 @@ __global__ void __launch_bounds__(kMergeThreads) decode_merge_kernel(const Decod
     const int hq = blockIdx.x, kv = blockIdx.y, i = blockIdx.z;
     pdl_trigger();
     const int seq_len = seq_len_of(p.seq, i);
-    const DecodeBounds bnd = effective_bounds(p, seq_len);
+    const DecodeBounds bnd = effective_bounds(p, seq_len, i);
     const int nchunks = chunk_work(p, bnd, 0).nchunks;
     // Every CTA waits, also the ones with nothing to merge: a kernel launched behind this one only waits
     // for THIS grid, so a CTA that left early would let it overtake the decode kernel.

@@ -9,13 +9,14 @@ namespace kivi {
 
 // Effective scan bounds of one query: quantised tokens to walk (already reduced to the retained
 // pages in sparse mode) and residual rows.
-__device__ __forceinline__ DecodeBounds effective_bounds(const DecodeParams& p, int seq_len) {
+__device__ __forceinline__ DecodeBounds effective_bounds(const DecodeParams& p, int seq_len, int i) {
     const Geom& g = p.geom;
-    const bool sparse = p.retained_pages >= 0;
+    const bool sparse = p.retained_pages >= 0 || p.retained_dev != nullptr;
     DecodeBounds b = decode_bounds(seq_len, g.r, g.g, p.max_seq, sparse ? 0x3fffffff / g.b : p.seq.bt_width, g.b);
     if (sparse) {
         int dense_pages = b.old_valid / g.b;
-        int rp = p.retained_pages < dense_pages ? p.retained_pages : dense_pages;
+        const int retained = p.retained_dev ? p.retained_dev[i] : p.retained_pages;
+        int rp = retained < dense_pages ? retained : dense_pages;
         if (rp > p.seq.bt_width) rp = p.seq.bt_width;
         b.old_valid = (rp < 0 ? 0 : rp) * g.b;
     }

@@ -167,7 +167,7 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
     const int r = lane >> 2, t = lane & 3;
 
     const int seq_len = seq_len_of(p.seq, i);
-    const DecodeBounds bnd = effective_bounds(p, seq_len);
+    const DecodeBounds bnd = effective_bounds(p, seq_len, i);
     const ChunkWork work = chunk_work(p, bnd, chunk);
     const int nchunks = work.nchunks;
     if (chunk >= nchunks) return;

@@ -101,6 +101,7 @@ struct DecodeParams {
     int n;                // queries (sequences) in this launch
     int max_seq;          // longest sequence the launch is planned for (reference: LQ + RESIDUAL), or -1
     int retained_pages;   // sparse-retained: pages to scan from the compact table, else -1
+    const int* retained_dev;  // sparse-retained with one count per sequence (device [n]); overrides retained_pages
     // split over the context: each CTA takes `chunk_tokens` quantised tokens; the residual rides
     // with the last chunk. Partials go to the workspace, the last CTA to arrive merges.
     int chunk_tokens;
@@ -313,7 +314,7 @@ cudaError_t launch_rope_write(const RopeParams& rp, const WriteParams& p, cudaSt
 // kivi_status. `out_h` (fp16) replaces `out` (fp32) when non-null.
 int run_decode(const Geom& g, const CachePtrs& cache, const SeqAddressing& seq, const __half* q, float* out,
                __half* out_h, int n, int max_seq_cap, int max_old_tokens, int retained_pages, void* ws,
-               size_t ws_bytes, cudaStream_t stream);
+               size_t ws_bytes, cudaStream_t stream, const int* retained_dev = nullptr);
 size_t decode_workspace_total(const Geom& g, int n, int max_old_tokens);
 cudaError_t launch_decode_generic(const DecodeParams& p, cudaStream_t stream);
 cudaError_t launch_decode_mma(const DecodeParams& p, cudaStream_t stream);

@@ -211,3 +211,46 @@ def test_decode_after_write_round_trip(native_lib):
         if t % 9 == 0 or t >= steps - 3 or (t + 1 - case.r) % case.g in (0, 1):
             want = ko.decode_batch(oc, q, tables, np.full(n, t + 1, np.int32), mode=1)
             _check(out.cpu().numpy(), want, f"step {t}")
+
+
+@pytest.mark.parametrize("name", ["reflane", "qwen05b", "mistral7b"])
+def test_v2_sparse_retained_per_sequence(native_lib, name):
+    """Page-aware eviction, many sequences: each sequence drops its own set of old pages (one drops
+    none, one drops all but the newest), the decode walks per-sequence compact tables. The oracle is the
+    reference's sparse-retained recurrence (compact table + retained-page count) per sequence. With
+    group_size > block_size a dropped page breaks a key group, so such geometries take the generic
+    kernel; the reference lane (group = block) runs the tensor-core kernel."""
+    from tests.gpu_utils import DEV, f16_tensor, upload
+    case = helpers.CONFIGS[name]
+    ctx = min(case.context, 2048)
+    seq_lens = np.array([ctx, ctx - 37, ctx // 2 + 5, case.r + case.g + 3], np.int32)
+    geom, oc, tables, slots = _build_oracle_cache(case, seq_lens)
+    q = helpers.make_q(case, len(seq_lens))
+    cache = upload(oc, case, tables.shape[1])
+    cache.set_block_tables(torch.from_numpy(tables))
+    cache.seq_lens.copy_(torch.from_numpy(seq_lens))
+    rng = np.random.default_rng(5)
+    ppg = case.g // case.b                                  # pages per key group: groups are dropped whole
+    drops = []
+    for i, t in enumerate(seq_lens):
+        groups = geom.split_old(int(t)) // case.g
+        if i == 0:
+            gone = np.array([], np.int64)                    # dense sequence in a sparse batch
+        elif i == 1:
+            gone = np.arange(max(0, groups - 1))            # keeps only the newest group
+        else:
+            gone = np.sort(rng.choice(groups, size=groups // 2, replace=False)) if groups > 1 else np.array([], np.int64)
+        pages = (gone[:, None] * ppg + np.arange(ppg)[None, :]).reshape(-1)
+        drops.append(pages)
+        freed = cache.drop_pages(i, pages.tolist())
+        assert freed == [int(tables[i, p]) for p in pages]
+    out = cache.decode(f16_tensor(q), max_seq_len=int(seq_lens.max()))
+    torch.cuda.synchronize()
+    got = out.cpu().numpy()
+    for i, t in enumerate(seq_lens):
+        dense_pages = geom.split_old(int(t)) // case.b
+        keep = np.array([p for p in range(dense_pages) if p not in set(drops[i].tolist())], np.int64)
+        compact = np.zeros(tables.shape[1], np.int32)
+        compact[: len(keep)] = tables[i, keep]
+        want = ko.decode(oc, q[i], compact, int(t), slot=i, mode=0, num_retained_pages=len(keep))
+        _check(got[i], want, f"{name} sequence {i} ({len(keep)} of {dense_pages} pages kept)")

@@ -152,3 +152,24 @@ def test_sharding_helpers():
     assert sharding.shard_imbalance(costs, b) < 1.05
     assert sharding.shard_imbalance(costs, [list(r) for r in sharding.contiguous_shards(8, 2)]) > 1.1
     assert sharding.balanced_shards([], 3) == [[], [], []]
+
+
+def test_retained_tables_compaction_on_cpu():
+    """Compact tables and counts of the sparse-retained decode: kept pages first in their original
+    order, the count is the kept pages among the dense old pages of the current length."""
+    import torch
+    from jacq_b200.cache import KiviCache, model_layout
+    cache = KiviCache.__new__(KiviCache)          # the arithmetic needs no device
+    cache.layout = model_layout("reference-lane")  # block = group = 32, residual 128
+    cache.device = torch.device("cpu")
+    tables = torch.arange(100, 110, dtype=torch.int32).repeat(3, 1) + torch.tensor([[0], [1000], [2000]], dtype=torch.int32)
+    mask = torch.ones((3, 10), dtype=torch.bool)
+    mask[0, [1, 3]] = False                         # sequence 0 dropped pages 1 and 3
+    mask[2, :4] = False                             # sequence 2 dropped its first four pages
+    lens = torch.tensor([128 + 6 * 32 + 5, 128 + 2 * 32, 128 + 5 * 32 + 31], dtype=torch.int32)   # 6, 2, 5 dense old pages
+    compact, counts = cache.retained_tables(lens, tables, mask)
+    assert counts.tolist() == [4, 2, 1]
+    assert compact[0, :4].tolist() == [100, 102, 104, 105]
+    assert compact[1, :2].tolist() == [1100, 1101]
+    assert compact[2, :1].tolist() == [2104]
+    assert sorted(compact[0].tolist()) == sorted(tables[0].tolist())   # a permutation: nothing lost
