@@ -1,6 +1,7 @@
 """Host-side logic of the v1 adapter and the sharding helpers, on CPU tensors: every check the
 reference's backend stub makes (integrations/vllm_kivi/source_patch.py:179-553) fires with the
 same exception type before any library call."""
+from pathlib import Path
 import pytest
 import torch
 
@@ -173,3 +174,26 @@ def test_retained_tables_compaction_on_cpu():
     assert compact[1, :2].tolist() == [1100, 1101]
     assert compact[2, :1].tolist() == [2104]
     assert sorted(compact[0].tolist()) == sorted(tables[0].tolist())   # a permutation: nothing lost
+
+
+def test_library_artifact_places_forwarding_units(tmp_path, native_lib):
+    """The vLLM-lane artefact for the prebuilt library: every kernel file of the reference's flow
+    gets a unit that defines nothing, the header and a CMake fragment ride along."""
+    from jacq_b200 import abi, dsl_decode
+    root = Path(__file__).resolve().parent.parent
+    art = dsl_decode.B200KernelLibraryArtifact(str(root), str(tmp_path))
+    rep = art.report()
+    assert rep["library_exists"] and rep["header_exists"] and rep["abi_version"] == abi.JACQ_KIVI_ABI_VERSION
+    assert set(rep["symbols"]) <= set(abi.V1_SYMBOLS) | {"kivi_cache_write_launch", "kivi_cache_write_batched_launch"}
+    assert not any(rep["kernel_files"].values())
+    written = art.emit()
+    assert all(p.exists() for p in written)
+    unit = (tmp_path / "csrc/kivi/decode_attention_kivi_batched_dsl.cu").read_text()
+    assert "Library artifact for embedding in a runtime extension" in unit and "jac_launch_batched" in unit
+    assert "__global__" not in unit and "int main(" not in unit and 'extern "C" void' not in unit
+    assert (tmp_path / "csrc/kivi/jacq_kivi_b200.h").read_text() == (root / "include/jacq_kivi_b200.h").read_text()
+    cmake = (tmp_path / "csrc/kivi/jacq_kivi_b200.cmake").read_text()
+    assert "IMPORTED_LOCATION" in cmake and "libjacq_kivi_b200.so" in cmake
+    rep = art.report()
+    assert all(rep["kernel_files"].values())
+    assert rep["serving_env"]["JAC_VLLM_KIVI_DECODE_KERNEL_SOURCE"] == "b200-kivi-library"
