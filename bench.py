@@ -54,6 +54,9 @@ SECONDARY = {
     # one step = the four projections (qkv, o, gate_up, down) of 8 layers of the Qwen2.5-14B shape at
     # batch 1, every GEMV on its own weights: 4.4 GB of fp16 weights streamed once per step
     "gemv_qwen25_14b_8layers_b1": "gemv",
+    # the same 32 projections for 8 and 64 sequences: the tensor-core skinny GEMM
+    "gemv_qwen25_14b_8layers_b8": "gemv",
+    "gemv_qwen25_14b_8layers_b64": "gemv",
     # one step = one 512-token chunk appended to each of 128 sequences (Mistral-7B shape): every
     # sequence ages out four key groups
     "writer_mistral7b_b128_chunk512": "writer",
@@ -400,14 +403,15 @@ def run_secondary(args):
     peak, peak_kind = _peaks()
     kind = SECONDARY[args.workload]
     if kind == "gemv":
+        gbatch = int(args.workload.rsplit("_b", 1)[1])
         hidden, ffn, qkv = 5120, 13824, 7168
         shapes = [(qkv, hidden), (hidden, hidden), (2 * ffn, hidden), (hidden, ffn)]
         layers = 8
         gen = torch.Generator(device=device).manual_seed(11)
         weights = [[(torch.randn((o, i), device=device, dtype=torch.float16, generator=gen) * 0.02) for o, i in shapes]
                    for _ in range(layers)]
-        xs = {i: torch.randn((i,), device=device, dtype=torch.float16, generator=gen) for i in (hidden, ffn)}
-        ys = [[torch.empty((o,), device=device, dtype=torch.float16) for o, _ in shapes] for _ in range(layers)]
+        xs = {i: torch.randn((gbatch, i), device=device, dtype=torch.float16, generator=gen) for i in (hidden, ffn)}
+        ys = [[torch.empty((gbatch, o), device=device, dtype=torch.float16) for o, _ in shapes] for _ in range(layers)]
         lib = _native.lib()
         import ctypes
         stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
@@ -416,13 +420,13 @@ def run_secondary(args):
             for lw, ly in zip(weights, ys):
                 for w, y in zip(lw, ly):
                     rc = lib.kivi_b200_gemv_f16(w.data_ptr(), xs[w.shape[1]].data_ptr(), y.data_ptr(), None,
-                                                w.shape[0], w.shape[1], 1, stream)
+                                                w.shape[0], w.shape[1], gbatch, stream)
                     assert rc == 0
-        step_bytes = layers * sum(o * i * 2 + (o + i) * 2 for o, i in shapes)
+        step_bytes = layers * sum(o * i * 2 + gbatch * (o + i) * 2 for o, i in shapes)
         launches = layers * len(shapes)
-        metric, kernel = "fp16 GEMV achieved HBM GB/s", "gemv_kernel<1>"
+        metric, kernel = "fp16 GEMV achieved HBM GB/s", ("gemv_kernel" if gbatch <= 4 else "skinny_gemm_kernel")
         ms = _timed_steps(step, args.steps, args.warmup, device)
-        extra = {"shapes_out_in": shapes, "layers": layers, "batch": 1}
+        extra = {"shapes_out_in": shapes, "layers": layers, "batch": gbatch}
     else:
         case = helpers.CONFIGS["mistral7b"]
         lay = helpers.layout_of(case)
