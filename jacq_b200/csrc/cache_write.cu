@@ -213,6 +213,7 @@ __device__ __forceinline__ void pack_group(const WriteParams& p, const Shape& g,
             const int rows = (g.g + parts - 1) / parts;
             const int r0 = part * rows, r1 = min(g.g, r0 + rows);
             float mn0 = NAN, mx0 = NAN, mn1 = NAN, mx1 = NAN;   // NaN is the neutral element of fmin/fmax
+#pragma unroll 8
             for (int t = r0; t < r1; ++t) {
                 const float2 x = __half22float2(reinterpret_cast<const __half2*>(tile + (size_t)t * g.d)[cp]);
                 mn0 = fminf(mn0, x.x); mx0 = fmaxf(mx0, x.x);
@@ -251,6 +252,7 @@ __device__ __forceinline__ void pack_group(const WriteParams& p, const Shape& g,
             *reinterpret_cast<float4*>(rc + e) = *reinterpret_cast<const float4*>(p_rcp + w * 8 + e);
         }
         const bool exact = s_exact != 0;
+#pragma unroll 4
         for (int idx = threadIdx.x; idx < g.g * words_per_row; idx += kThreads) {
             const int t = idx / words_per_row;
             const uint4 v = reinterpret_cast<const uint4*>(tile)[idx];
@@ -260,6 +262,7 @@ __device__ __forceinline__ void pack_group(const WriteParams& p, const Shape& g,
         }
         return;
     }
+#pragma unroll 4
     for (int idx = threadIdx.x; idx < g.g * words_per_row; idx += kThreads) {
         const int t = idx / words_per_row, w = idx - t * words_per_row;
         const uint4 v = reinterpret_cast<const uint4*>(tile)[idx];
@@ -289,6 +292,7 @@ __device__ __forceinline__ void pack_group(const WriteParams& p, const Shape& g,
             if (item < items) {
                 const int t = item / g.hg, cg = item - t * g.hg;
                 const __half2* seg = reinterpret_cast<const __half2*>(tile + (size_t)t * g.d + cg * g.vg) + side * half_words;
+#pragma unroll 8
                 for (int k = 0; k < half_words; ++k) {
                     const float2 x = __half22float2(seg[(k + t) % half_words]);
                     mn = fminf(mn, fminf(x.x, x.y));
@@ -313,6 +317,7 @@ __device__ __forceinline__ void pack_group(const WriteParams& p, const Shape& g,
         }
     }
     __syncthreads();
+#pragma unroll 4
     for (int idx = threadIdx.x; idx < g.g * words_per_row; idx += kThreads) {
         const int t = idx / words_per_row, w = idx - t * words_per_row;
         const uint4 v = reinterpret_cast<const uint4*>(tile)[idx];
