@@ -35,11 +35,14 @@ struct StaticShape {
     __device__ __forceinline__ explicit StaticShape(const Geom&) {}
     static constexpr int d = D_, g = G_, b = B_;
     static constexpr int vg = G_ < D_ ? G_ : D_, hg = D_ / vg, pages_per_group = G_ / B_;
+    // The register-tile form of the pack (pack_group_regs below) covers every shape of this kind.
+    static constexpr bool in_registers = true;
 };
 struct DynamicShape {
     __device__ __forceinline__ explicit DynamicShape(const Geom& x)
         : d(x.d), g(x.g), b(x.b), vg(x.vg), hg(x.hg), pages_per_group(x.pages_per_group) {}
     const int d, g, b, vg, hg, pages_per_group;
+    static constexpr bool in_registers = false;
 };
 
 struct SeqWrite {
@@ -175,11 +178,259 @@ __device__ __forceinline__ unsigned pack_word(const uint4& v, const float* mn, c
     return word;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Register-tile pack (compile-time shapes). The G x D tile never touches shared memory: thread
+// (w, r) = (tid % WPR, tid / WPR), WPR = D / 8 words per row, loads the 16-byte word w of rows
+// r, r + RPP, r + 2 RPP, ... (RPP = 256 / WPR rows per pass) straight into registers -- sixteen (or
+// eight) neighbouring lanes cover one row, so the loads are whole 128/256-byte rows -- and keeps them
+// for both passes over the data. Minima and maxima are taken on the fp16 values themselves, two per
+// instruction (min/max return one of their inputs, so nothing is rounded and the result equals the
+// reference's fp32 scan; NaN is dropped and -0 orders below +0 exactly as fminf/fmaxf do). A third
+// half2 instruction per pair, acc = x * 0 + acc, turns any NaN or Inf element into a NaN flag: tiles
+// that hold one are packed with the plain IEEE division, all others with the reciprocal form,
+// which then needs no NaN handling per element.
+
+struct PackPairs {   // parameters of eight channels as f32x2 operands
+    unsigned long long neg_mn[4], neg_sc[4], rcp[4];
+};
+
+__device__ __forceinline__ unsigned pack_word_pairs(const uint4& v, const PackPairs& pp) {
+    const __half2* h = reinterpret_cast<const __half2*>(&v);
+    const unsigned long long magic = f32x2(12582912.0f, 12582912.0f);
+    unsigned word = 0;
+    // Horner over the nibbles: every term is 0x4B400000 + code
+#pragma unroll
+    for (int e = 3; e >= 0; --e) {
+        const float2 f = __half22float2(h[e]);
+        unsigned long long a, q, r, m;
+        const unsigned long long x = f32x2(f.x, f.y);
+        asm("add.rn.f32x2 %0, %1, %2;" : "=l"(a) : "l"(x), "l"(pp.neg_mn[e]));
+        asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(q) : "l"(a), "l"(pp.rcp[e]));
+        asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(pp.neg_sc[e]), "l"(q), "l"(a));
+        asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(q) : "l"(r), "l"(pp.rcp[e]), "l"(q));
+        asm("add.rn.f32x2 %0, %1, %2;" : "=l"(m) : "l"(q), "l"(magic));
+        uint2 b;
+        asm("mov.b64 {%0, %1}, %2;" : "=r"(b.x), "=r"(b.y) : "l"(m));
+        word = (word * 16u + b.y) * 16u + b.x;
+    }
+    return word - 0x4B400000u * 0x11111111u;
+}
+
+__device__ __forceinline__ unsigned h2_bits(__half2 v) { return *reinterpret_cast<unsigned*>(&v); }
+__device__ __forceinline__ __half2 bits_h2(unsigned v) { return *reinterpret_cast<__half2*>(&v); }
+
+// scale, zero-point and reciprocal of one group from its extremes (reference arithmetic)
+__device__ __forceinline__ float4 group_params(float mn, float mx) {
+    float scale = __fdiv_rn(__fsub_rn(mx, mn), 15.0f);
+    if (!(scale > 0.0f)) scale = 1.0f;
+    return make_float4(mn, scale, __frcp_rn(scale), 0.0f);
+}
+
+template <class Shape>
+__device__ __forceinline__ void pack_group_regs(const WriteParams& p, const SeqWrite& s, int h, int j, bool values,
+                                                unsigned char* smem_raw) {
+    constexpr int D = Shape::d, G = Shape::g, B = Shape::b;
+    constexpr int WPR = D / 8, RPP = kThreads / WPR, NK = G / RPP;
+    static_assert(kThreads % WPR == 0 && G % RPP == 0 && NK >= 1 && NK <= 8, "shape not covered by the register tile");
+    const int nkv = p.geom.nkv;
+    const int pos0 = s.prev_old + j * G;
+    const int lp0 = pos0 / B;
+    if (lp0 + Shape::pages_per_group > p.seq.bt_width) return;  // table too narrow: host validation failed
+    const int tid = threadIdx.x, w = tid % WPR, r = tid / WPR, lane = tid & 31, warp = tid >> 5;
+
+    // ---- the tile: word w of rows r + RPP k, from the old scratch rows or the new rows
+    uint4 x[NK];
+    {
+        const __half* scratch = values ? p.cache.v_scratch : p.cache.k_scratch;
+        const __half* fresh = values ? p.new_v : p.new_k;
+        const int pos = pos0 + r;
+        const uint4* from_scratch = reinterpret_cast<const uint4*>(
+            scratch + (((size_t)s.slot * nkv + h) * p.geom.scratch_rows + (pos - s.prev_old)) * D) + w;
+        const uint4* from_fresh = reinterpret_cast<const uint4*>(
+            fresh + ((long long)(s.new_row0 + pos - s.start) * nkv + h) * D) + w;
+        const size_t fresh_step = (size_t)RPP * nkv * WPR;
+#pragma unroll
+        for (int k = 0; k < NK; ++k) {
+            x[k] = __ldcg(pos + RPP * k < s.start ? from_scratch + k * RPP * WPR : from_fresh);
+            from_fresh += fresh_step;
+        }
+    }
+    // Row r + RPP k of the group: which of the group's pages it lies in and which row of that page it is.
+    // Either a pass covers whole pages (the row within the page is the same for every k) or a page
+    // takes several passes (r < RPP <= B); both are compile-time functions of k on top of r.
+    constexpr bool kWholePages = RPP % B == 0;
+    static_assert(kWholePages || B % RPP == 0, "rows per pass and page size must divide one another");
+    const int row0 = kWholePages ? r % B : r;
+    const int* pages = s.bt + lp0 + (kWholePages ? r / B : 0);
+    int page_of[NK];
+#pragma unroll
+    for (int k = 0; k < NK; ++k) page_of[k] = pages[kWholePages ? (RPP / B) * k : (RPP * k) / B];
+    // the thread's code word in row r + RPP k: one multiply-add on the page index
+    const size_t page_words = (size_t)nkv * B * (D / 8);
+    uint32_t* const codes = reinterpret_cast<uint32_t*>(values ? p.cache.v_code : p.cache.k_code) +
+                            ((size_t)h * B + row0) * (D / 8) + w;
+    auto code_word = [&](int k) -> uint32_t* {
+        return codes + (size_t)page_of[k] * page_words + (kWholePages ? 0 : ((RPP * k) % B) * (D / 8));
+    };
+
+    const __half2 zero2 = __float2half2_rn(0.0f);
+    if (!values) {
+        // ---------------- keys: per channel over the G tokens ----------------
+        uint4* part = reinterpret_cast<uint4*>(smem_raw);                       // [8 warps][WPR][min, max]
+        float* p_neg_min = reinterpret_cast<float*>(part + (kThreads / 32) * WPR * 2);   // [D] each: -zero, -scale, 1/scale
+        float* p_neg_scale = p_neg_min + D;
+        float* p_rcp = p_neg_scale + D;
+        __half2 mn[4], mx[4], bad = zero2;
+        {
+            const __half2* h0 = reinterpret_cast<const __half2*>(&x[0]);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { mn[e] = h0[e]; mx[e] = h0[e]; bad = __hfma2(h0[e], zero2, bad); }
+        }
+#pragma unroll
+        for (int k = 1; k < NK; ++k) {
+            const __half2* hk = reinterpret_cast<const __half2*>(&x[k]);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                mn[e] = __hmin2(mn[e], hk[e]);
+                mx[e] = __hmax2(mx[e], hk[e]);
+                bad = __hfma2(hk[e], zero2, bad);
+            }
+        }
+        // rows of the same warp: lanes that differ in the bits above the word index
+#pragma unroll
+        for (int off = WPR; off < 32; off <<= 1)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                mn[e] = __hmin2(mn[e], bits_h2(__shfl_xor_sync(0xffffffffu, h2_bits(mn[e]), off)));
+                mx[e] = __hmax2(mx[e], bits_h2(__shfl_xor_sync(0xffffffffu, h2_bits(mx[e]), off)));
+            }
+        if (lane < WPR) {
+            part[(warp * WPR + w) * 2] = make_uint4(h2_bits(mn[0]), h2_bits(mn[1]), h2_bits(mn[2]), h2_bits(mn[3]));
+            part[(warp * WPR + w) * 2 + 1] = make_uint4(h2_bits(mx[0]), h2_bits(mx[1]), h2_bits(mx[2]), h2_bits(mx[3]));
+        }
+        const bool exact = __syncthreads_or(__hisnan(__low2half(bad)) || __hisnan(__high2half(bad)));
+        if (tid < D) {
+            const int c = tid;
+            const __half* col = reinterpret_cast<const __half*>(part) + (c / 8) * 16 + (c % 8);
+            __half lo = col[0], hi = col[8];
+#pragma unroll
+            for (int q = 1; q < kThreads / 32; ++q) {
+                lo = __hmin(lo, col[q * WPR * 16]);
+                hi = __hmax(hi, col[q * WPR * 16 + 8]);
+            }
+            const float4 gp = group_params(__half2float(lo), __half2float(hi));
+            p_neg_min[c] = -gp.x;
+            p_neg_scale[c] = -gp.y;
+            p_rcp[c] = gp.z;
+            const __half hs = __float2half_rn(gp.y), hz = __float2half_rn(gp.x);
+#pragma unroll
+            for (int pi = 0; pi < Shape::pages_per_group; ++pi) {
+                const size_t page = (size_t)s.bt[lp0 + pi];
+                p.cache.k_scale[(page * nkv + h) * D + c] = hs;
+                p.cache.k_zero[(page * nkv + h) * D + c] = hz;
+            }
+        }
+        __syncthreads();
+        // a thread packs the same eight channels of all its rows: their parameters stay in registers, already
+        // negated and paired the way the packed arithmetic takes them
+        if (!exact) {
+            PackPairs pp;
+#pragma unroll
+            for (int e = 0; e < 4; e += 2) {
+                const ulonglong2 a = *reinterpret_cast<const ulonglong2*>(p_neg_min + w * 8 + 2 * e);
+                const ulonglong2 b = *reinterpret_cast<const ulonglong2*>(p_neg_scale + w * 8 + 2 * e);
+                const ulonglong2 c = *reinterpret_cast<const ulonglong2*>(p_rcp + w * 8 + 2 * e);
+                pp.neg_mn[e] = a.x; pp.neg_mn[e + 1] = a.y;
+                pp.neg_sc[e] = b.x; pp.neg_sc[e + 1] = b.y;
+                pp.rcp[e] = c.x; pp.rcp[e + 1] = c.y;
+            }
+#pragma unroll
+            for (int k = 0; k < NK; ++k) *code_word(k) = pack_word_pairs(x[k], pp);
+        } else {
+            float pmn[8], psc[8], prc[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) { pmn[e] = -p_neg_min[w * 8 + e]; psc[e] = -p_neg_scale[w * 8 + e]; prc[e] = p_rcp[w * 8 + e]; }
+#pragma unroll
+            for (int k = 0; k < NK; ++k) *code_word(k) = pack_word(x[k], pmn, psc, prc, true);
+        }
+        return;
+    }
+
+    // ---------------- values: per token over each channel group ----------------
+    // LPI neighbouring lanes hold one (token, channel group). Each lane folds its word into the half2
+    // (min, -max); the warp's folded words go through shared memory so that lane i can finish group i of
+    // the warp: the parameter arithmetic is then issued once per warp, not once per row.
+    constexpr int VG = Shape::vg, HG = Shape::hg, LPI = VG / 8, GPP = 32 / LPI, IPW = GPP * NK;   // groups per pass / per warp
+    static_assert(LPI >= 4 && LPI <= 32 && (LPI & (LPI - 1)) == 0 && IPW <= 32, "value groups not covered");
+    unsigned* folded = reinterpret_cast<unsigned*>(smem_raw) + warp * (NK * 32);                  // [NK][32 lanes]
+    float4* params = reinterpret_cast<float4*>(smem_raw + (kThreads / 32) * NK * 32 * 4) + warp * IPW * 2;   // [IPW][2]:
+    // (-zero, -zero, -scale, -scale), (1/scale, 1/scale, zero, scale): operand pairs of the packed arithmetic
+    __half2 bad = zero2;
+#pragma unroll
+    for (int k = 0; k < NK; ++k) {
+        const __half2* hk = reinterpret_cast<const __half2*>(&x[k]);
+        const __half2 lo = __hmin2(__hmin2(hk[0], hk[1]), __hmin2(hk[2], hk[3]));
+        const __half2 hi = __hmax2(__hmax2(hk[0], hk[1]), __hmax2(hk[2], hk[3]));
+        bad = __hfma2(hk[0], zero2, bad); bad = __hfma2(hk[1], zero2, bad);
+        bad = __hfma2(hk[2], zero2, bad); bad = __hfma2(hk[3], zero2, bad);
+        const unsigned nhi = h2_bits(hi) ^ 0x80008000u;   // -max: the maximum becomes a minimum
+        const __half2 a = bits_h2(__byte_perm(h2_bits(lo), nhi, 0x5410));   // (lo.x, -hi.x)
+        const __half2 b = bits_h2(__byte_perm(h2_bits(lo), nhi, 0x7632));   // (lo.y, -hi.y)
+        folded[k * 32 + lane] = h2_bits(__hmin2(a, b));
+    }
+    const bool exact = __any_sync(0xffffffffu, __hisnan(__low2half(bad)) || __hisnan(__high2half(bad)));
+    __syncwarp();
+    if (lane < IPW) {
+        const uint4* src = reinterpret_cast<const uint4*>(folded + lane * LPI);
+        uint4 v = src[0];
+#pragma unroll
+        for (int q = 1; q < LPI / 4; ++q) {
+            const uint4 u = src[q];
+            v.x = h2_bits(__hmin2(bits_h2(v.x), bits_h2(u.x))); v.y = h2_bits(__hmin2(bits_h2(v.y), bits_h2(u.y)));
+            v.z = h2_bits(__hmin2(bits_h2(v.z), bits_h2(u.z))); v.w = h2_bits(__hmin2(bits_h2(v.w), bits_h2(u.w)));
+        }
+        const __half2 m = __hmin2(__hmin2(bits_h2(v.x), bits_h2(v.y)), __hmin2(bits_h2(v.z), bits_h2(v.w)));
+        const __half lo = __low2half(m), hi = __hneg(__high2half(m));
+        const float4 gp = group_params(__half2float(lo), __half2float(hi));
+        params[lane * 2] = make_float4(-gp.x, -gp.x, -gp.y, -gp.y);
+        params[lane * 2 + 1] = make_float4(gp.z, gp.z, gp.x, gp.y);
+        // group `lane` of the warp: pass k, lanes [first, first + LPI) of that pass
+        const int k = lane / GPP, first = (lane % GPP) * LPI;
+        const int t = (warp * 32 + first) / WPR + RPP * k, cg = ((first % WPR) * 8) / VG;
+        const size_t page = (size_t)s.bt[lp0 + t / B];
+        const size_t param = ((page * nkv + h) * B + (t % B)) * HG + cg;
+        p.cache.v_scale[param] = __float2half_rn(gp.y);
+        p.cache.v_zero[param] = __float2half_rn(gp.x);
+    }
+    __syncwarp();
+    if (!exact) {
+#pragma unroll
+        for (int k = 0; k < NK; ++k) {
+            const float4* gp = params + (k * GPP + lane / LPI) * 2;
+            const ulonglong2 a = *reinterpret_cast<const ulonglong2*>(gp);
+            const unsigned long long c = *reinterpret_cast<const unsigned long long*>(gp + 1);
+            PackPairs pp;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { pp.neg_mn[e] = a.x; pp.neg_sc[e] = a.y; pp.rcp[e] = c; }
+            *code_word(k) = pack_word_pairs(x[k], pp);
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < NK; ++k) {
+            const float4 gp = params[(k * GPP + lane / LPI) * 2 + 1];
+            const float pmn[8] = {gp.z, gp.z, gp.z, gp.z, gp.z, gp.z, gp.z, gp.z};
+            const float psc[8] = {gp.w, gp.w, gp.w, gp.w, gp.w, gp.w, gp.w, gp.w};
+            const float prc[8] = {gp.x, gp.x, gp.x, gp.x, gp.x, gp.x, gp.x, gp.x};
+            *code_word(k) = pack_word(x[k], pmn, psc, prc, true);
+        }
+    }
+}
+
 // Quantises the keys (values == false) or the values of aged-out group j of (sequence s, kv head h) into
 // its pages. Called by every thread of a CTA of kThreads threads; smem_raw holds pack_smem_bytes().
 template <class Shape>
-__device__ __forceinline__ void pack_group(const WriteParams& p, const Shape& g, const SeqWrite& s, int h, int j,
-                                           bool values, unsigned char* smem_raw) {
+__device__ __forceinline__ void pack_group_staged(const WriteParams& p, const Shape& g, const SeqWrite& s, int h, int j,
+                                                  bool values, unsigned char* smem_raw) {
     const int nkv = p.geom.nkv;
 
     const int nparam = g.d > g.g * g.hg ? g.d : g.g * g.hg;
@@ -332,10 +583,17 @@ __device__ __forceinline__ void pack_group(const WriteParams& p, const Shape& g,
     }
 }
 
+template <class Shape>
+__device__ __forceinline__ void pack_group(const WriteParams& p, const Shape& g, const SeqWrite& s, int h, int j,
+                                           bool values, unsigned char* smem_raw) {
+    if constexpr (Shape::in_registers) pack_group_regs<Shape>(p, s, h, j, values, smem_raw);
+    else pack_group_staged(p, g, s, h, j, values, smem_raw);
+}
+
 // keys and values of a group are quantised independently (per channel / per token): one CTA each, so a
 // tile's worth of shared memory per CTA and twice the loads in flight per SM
 template <class Shape>
-__global__ void __launch_bounds__(kThreads) pack_groups_kernel(const WriteParams p) {
+__global__ void __launch_bounds__(kThreads, Shape::in_registers ? 3 : 1) pack_groups_kernel(const WriteParams p) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const Shape g(p.geom);
     const int i = blockIdx.z, h = blockIdx.y, j = blockIdx.x >> 1;
@@ -434,13 +692,25 @@ __global__ void __launch_bounds__(kThreads) rope_write_kernel(const RopeParams r
     if (s.num_new > 0) scratch_update(p, s, h);
 }
 
+// Dynamic shared memory of the pack: the staged form holds the tile and its parameters, the register-tile
+// form only what crosses lanes (keys: per-warp extremes and the channel parameters; values: the folded
+// words of every warp and the group parameters).
+template <class Shape>
 size_t pack_smem_bytes(const Geom& g) {
-    size_t params = (size_t)(g.d > g.g * g.hg ? g.d : g.g * g.hg);
-    return (size_t)g.g * g.d * sizeof(__half) + (3 * params + 4 * kThreads) * sizeof(float);
+    if constexpr (Shape::in_registers) {
+        constexpr int WPR = Shape::d / 8, RPP = kThreads / WPR, NK = Shape::g / RPP, LPI = Shape::vg / 8;
+        constexpr size_t keys = (size_t)(kThreads / 32) * WPR * 32 + 3 * Shape::d * sizeof(float);
+        constexpr size_t vals = (size_t)(kThreads / 32) * NK * 32 * 4 + (size_t)(kThreads / 32) * (32 / LPI) * NK * 32;
+        return keys > vals ? keys : vals;
+    } else {
+        size_t params = (size_t)(g.d > g.g * g.hg ? g.d : g.g * g.hg);
+        return (size_t)g.g * g.d * sizeof(__half) + (3 * params + 4 * kThreads) * sizeof(float);
+    }
 }
 
 template <class Shape>
-cudaError_t launch_pack(const WriteParams& p, dim3 grid, size_t smem, cudaStream_t stream) {
+cudaError_t launch_pack(const WriteParams& p, dim3 grid, cudaStream_t stream) {
+    const size_t smem = pack_smem_bytes<Shape>(p.geom);
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(pack_groups_kernel<Shape>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
@@ -449,16 +719,17 @@ cudaError_t launch_pack(const WriteParams& p, dim3 grid, size_t smem, cudaStream
 }
 
 template <int D, int G>
-cudaError_t launch_pack_for_block(const WriteParams& p, dim3 grid, size_t smem, cudaStream_t stream, bool* done) {
+cudaError_t launch_pack_for_block(const WriteParams& p, dim3 grid, cudaStream_t stream, bool* done) {
     *done = true;
-    if (p.geom.b == 16) return launch_pack<StaticShape<D, G, 16>>(p, grid, smem, stream);
-    if (p.geom.b == 32) return launch_pack<StaticShape<D, G, 32>>(p, grid, smem, stream);
+    if (p.geom.b == 16) return launch_pack<StaticShape<D, G, 16>>(p, grid, stream);
+    if (p.geom.b == 32) return launch_pack<StaticShape<D, G, 32>>(p, grid, stream);
     *done = false;
     return cudaSuccess;
 }
 
 template <class Shape>
-cudaError_t launch_rope_write_shape(const RopeParams& rp, const WriteParams& p, size_t smem, cudaStream_t stream) {
+cudaError_t launch_rope_write_shape(const RopeParams& rp, const WriteParams& p, cudaStream_t stream) {
+    const size_t smem = pack_smem_bytes<Shape>(p.geom);
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(rope_write_kernel<Shape>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
@@ -468,11 +739,10 @@ cudaError_t launch_rope_write_shape(const RopeParams& rp, const WriteParams& p, 
 }
 
 template <int D, int G>
-cudaError_t launch_rope_write_for_block(const RopeParams& rp, const WriteParams& p, size_t smem, cudaStream_t stream,
-                                        bool* done) {
+cudaError_t launch_rope_write_for_block(const RopeParams& rp, const WriteParams& p, cudaStream_t stream, bool* done) {
     *done = true;
-    if (p.geom.b == 16) return launch_rope_write_shape<StaticShape<D, G, 16>>(rp, p, smem, stream);
-    if (p.geom.b == 32) return launch_rope_write_shape<StaticShape<D, G, 32>>(rp, p, smem, stream);
+    if (p.geom.b == 16) return launch_rope_write_shape<StaticShape<D, G, 16>>(rp, p, stream);
+    if (p.geom.b == 32) return launch_rope_write_shape<StaticShape<D, G, 32>>(rp, p, stream);
     *done = false;
     return cudaSuccess;
 }
@@ -485,37 +755,35 @@ cudaError_t launch_rope_write(const RopeParams& rp, const WriteParams& p, cudaSt
     const Geom& g = p.geom;
     if (p.n <= 0) return cudaSuccess;
     if (p.new_k != rp.k || p.new_v != rp.v || p.new_offsets || p.num_new_scalar != 1) return cudaErrorInvalidValue;
-    const size_t smem = pack_smem_bytes(g);
     bool done = false;
     cudaError_t e = cudaSuccess;
-    if (g.d == 128 && g.g == 128) e = launch_rope_write_for_block<128, 128>(rp, p, smem, stream, &done);
-    else if (g.d == 128 && g.g == 64) e = launch_rope_write_for_block<128, 64>(rp, p, smem, stream, &done);
-    else if (g.d == 128 && g.g == 32) e = launch_rope_write_for_block<128, 32>(rp, p, smem, stream, &done);
-    else if (g.d == 64 && g.g == 128) e = launch_rope_write_for_block<64, 128>(rp, p, smem, stream, &done);
-    else if (g.d == 64 && g.g == 64) e = launch_rope_write_for_block<64, 64>(rp, p, smem, stream, &done);
-    else if (g.d == 64 && g.g == 32) e = launch_rope_write_for_block<64, 32>(rp, p, smem, stream, &done);
+    if (g.d == 128 && g.g == 128) e = launch_rope_write_for_block<128, 128>(rp, p, stream, &done);
+    else if (g.d == 128 && g.g == 64) e = launch_rope_write_for_block<128, 64>(rp, p, stream, &done);
+    else if (g.d == 128 && g.g == 32) e = launch_rope_write_for_block<128, 32>(rp, p, stream, &done);
+    else if (g.d == 64 && g.g == 128) e = launch_rope_write_for_block<64, 128>(rp, p, stream, &done);
+    else if (g.d == 64 && g.g == 64) e = launch_rope_write_for_block<64, 64>(rp, p, stream, &done);
+    else if (g.d == 64 && g.g == 32) e = launch_rope_write_for_block<64, 32>(rp, p, stream, &done);
     if (e != cudaSuccess) return e;
-    if (!done) e = launch_rope_write_shape<DynamicShape>(rp, p, smem, stream);
+    if (!done) e = launch_rope_write_shape<DynamicShape>(rp, p, stream);
     return e;
 }
 
 cudaError_t launch_cache_write(const WriteParams& p, int max_new_per_seq, cudaStream_t stream) {
     const Geom& g = p.geom;
     if (p.n <= 0 || max_new_per_seq <= 0) return cudaSuccess;
-    const size_t smem = pack_smem_bytes(g);
     const int max_groups = max_new_per_seq / g.g + 1;
     const dim3 grid(2 * max_groups, g.nkv, p.n);   // (group, keys | values)
     bool done = false;
     cudaError_t e = cudaSuccess;
-    if (g.d == 128 && g.g == 128) e = launch_pack_for_block<128, 128>(p, grid, smem, stream, &done);
-    else if (g.d == 128 && g.g == 64) e = launch_pack_for_block<128, 64>(p, grid, smem, stream, &done);
-    else if (g.d == 128 && g.g == 32) e = launch_pack_for_block<128, 32>(p, grid, smem, stream, &done);
-    else if (g.d == 64 && g.g == 128) e = launch_pack_for_block<64, 128>(p, grid, smem, stream, &done);
-    else if (g.d == 64 && g.g == 64) e = launch_pack_for_block<64, 64>(p, grid, smem, stream, &done);
-    else if (g.d == 64 && g.g == 32) e = launch_pack_for_block<64, 32>(p, grid, smem, stream, &done);
+    if (g.d == 128 && g.g == 128) e = launch_pack_for_block<128, 128>(p, grid, stream, &done);
+    else if (g.d == 128 && g.g == 64) e = launch_pack_for_block<128, 64>(p, grid, stream, &done);
+    else if (g.d == 128 && g.g == 32) e = launch_pack_for_block<128, 32>(p, grid, stream, &done);
+    else if (g.d == 64 && g.g == 128) e = launch_pack_for_block<64, 128>(p, grid, stream, &done);
+    else if (g.d == 64 && g.g == 64) e = launch_pack_for_block<64, 64>(p, grid, stream, &done);
+    else if (g.d == 64 && g.g == 32) e = launch_pack_for_block<64, 32>(p, grid, stream, &done);
     if (e != cudaSuccess) return e;
     if (!done) {
-        e = launch_pack<DynamicShape>(p, grid, smem, stream);
+        e = launch_pack<DynamicShape>(p, grid, stream);
         if (e != cudaSuccess) return e;
     }
     return launch_pdl(scratch_update_kernel, dim3(g.nkv, p.n), dim3(kThreads), 0, stream, p);

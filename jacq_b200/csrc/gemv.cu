@@ -351,24 +351,40 @@ __global__ void __launch_bounds__(kSgThreads, kSgCtasPerSm) skinny_gemm_kernel(
                 a[m][0] = lds128(wa + (uint32_t)(16 * m) * kSgRowBytes);
                 a[m][1] = lds128(wa + (uint32_t)(16 * m + 8) * kSgRowBytes);
             }
-            uint4 b[NT];
+            // The MMA wants its four A registers as one aligned group: (row, k pair 0), (row + 8, pair 0), (row, pair 1),
+            // (row + 8, pair 1). They come from two different 16-byte loads, so each group is put together once
+            // here and then serves every column tile; the x fragments are fetched four tiles at a time to leave
+            // the registers for that.
+            uint32_t aq[2][2][4];
 #pragma unroll
-            for (int j = 0; j < NT; ++j) b[j] = lds128(xa + (uint32_t)(8 * j) * kSgRowBytes);
-            // the two MMAs that update one accumulator are issued a whole sweep apart, so neither waits on the other
+            for (int m = 0; m < 2; ++m) {
+                aq[m][0][0] = a[m][0].x; aq[m][0][1] = a[m][1].x; aq[m][0][2] = a[m][0].y; aq[m][0][3] = a[m][1].y;
+                aq[m][1][0] = a[m][0].z; aq[m][1][1] = a[m][1].z; aq[m][1][2] = a[m][0].w; aq[m][1][3] = a[m][1].w;
+            }
+            constexpr int JB = NT < 4 ? NT : 4;
 #pragma unroll
-            for (int j = 0; j < NT; ++j)
+            for (int j0 = 0; j0 < NT; j0 += JB) {
+                uint4 b[JB];
 #pragma unroll
-                for (int m = 0; m < 2; ++m)
-                    mma16816(acc[m][j], a[m][0].x, a[m][1].x, a[m][0].y, a[m][1].y, b[j].x, b[j].y);
+                for (int j = 0; j < JB; ++j)
+                    if (j0 + j < NT) b[j] = lds128(xa + (uint32_t)(8 * (j0 + j)) * kSgRowBytes);
+                // the two MMAs that update one accumulator are issued a sweep apart, so neither waits on the other
 #pragma unroll
-            for (int j = 0; j < NT; ++j)
+                for (int j = 0; j < JB; ++j)
 #pragma unroll
-                for (int m = 0; m < 2; ++m)
-                    mma16816(acc[m][j], a[m][0].z, a[m][1].z, a[m][0].w, a[m][1].w, b[j].z, b[j].w);
+                    for (int m = 0; m < 2; ++m)
+                        if (j0 + j < NT)
+                            mma16816(acc[m][j0 + j], aq[m][0][0], aq[m][0][1], aq[m][0][2], aq[m][0][3], b[j].x, b[j].y);
+#pragma unroll
+                for (int j = 0; j < JB; ++j)
+#pragma unroll
+                    for (int m = 0; m < 2; ++m)
+                        if (j0 + j < NT)
+                            mma16816(acc[m][j0 + j], aq[m][1][0], aq[m][1][1], aq[m][1][2], aq[m][1][3], b[j].z, b[j].w);
+            }
         }
     }
 
-    // acc[m][j] = rows (row0 + 32 warp + 16 m + r, +8) x batch columns (8j + 2t, +1)
     // tensor parallel (push.tp > 0, out_dim a multiple of 4): the result also goes straight into every
     // rank's exchange slot, two fp16 rows per 8-byte word
     const int splits = gridDim.y;
