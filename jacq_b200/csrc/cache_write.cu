@@ -11,10 +11,11 @@
 // How it is laid out differs: the reference launches 1-thread blocks with strided 2-byte loads and
 // a serial row-by-row shift, one sequence and at most one age-out per call. Here one launch covers
 // every sequence of the batch and every group a chunk ages out:
-//   pack kernel    one CTA per (sequence, kv head, aged-out group): the G x D tile is staged in
-//                  shared memory with 16-byte loads, min/max are reduced in parallel (min/max
-//                  are order-independent, so the result is bit-identical to the serial scan) and
-//                  codes leave as 32-bit words, 8 channels each, fully coalesced;
+//   pack kernel    one CTA per (sequence, kv head, aged-out group, keys | values): the G x D tile is
+//                  loaded 16 bytes per lane straight into registers (shared-memory staging for run-time
+//                  geometries), min/max are reduced in parallel (min/max are order-independent, so the
+//                  result is bit-identical to the serial scan) and codes leave as 32-bit words, 8
+//                  channels each, fully coalesced;
 //   scratch kernel one CTA per (sequence, kv head): overlapping move-to-front through registers
 //                  with a barrier per step, then the append of the rows that stay unquantised.
 // A token at absolute position p comes from scratch row p - old_tokens when it predates the call,
