@@ -268,6 +268,45 @@ __device__ __forceinline__ uint32_t sg_offset(int row, int chunk) {
     return (uint32_t)row * kSgRowBytes + (uint32_t)((chunk ^ ((row & 1) << 2)) << 4);
 }
 
+constexpr int kSgTileStride = kSgRows + 4;   // floats per batch column of a partial tile: 16-byte aligned, conflict-free stores
+
+// Every CTA of the cluster has left its partial tile, [batch column][row] with stride kSgTileStride, at the same
+// place of its shared memory. After a cluster barrier each CTA adds up one share of the tile across its peers
+// through distributed shared memory, in rank order, and stores it (and delivers it to the tensor-parallel
+// peers when push.tp > 0). Called by all kSgThreads threads of every CTA of the cluster.
+__device__ __forceinline__ void sg_reduce_store(float* tile, int row0, int out_dim, int batch, int splits, __half* y16,
+                                                float* y32, const P2pPush& push, const P2pTarget& target) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    constexpr int TS = kSgTileStride;
+    cluster.sync();
+    const unsigned rank = cluster.block_rank();
+    const int quads = batch * (kSgRows / 4);              // 4 consecutive rows of one column
+    const int per = (quads + splits - 1) / splits;
+    const int lo = (int)rank * per, hi = min(quads, lo + per);
+    for (int u = lo + (int)threadIdx.x; u < hi; u += kSgThreads) {
+        const int col = u / (kSgRows / 4), rr = (u - col * (kSgRows / 4)) * 4;
+        float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (int peer = 0; peer < splits; ++peer) {
+            const float4 v = *reinterpret_cast<const float4*>(cluster.map_shared_rank(tile, peer) + col * TS + rr);
+            sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+        }
+        const float vals[4] = {sum.x, sum.y, sum.z, sum.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int row = row0 + rr + k;
+            if (row < out_dim) {
+                if (y32) y32[(size_t)col * out_dim + row] = vals[k];
+                if (y16) y16[(size_t)col * out_dim + row] = __float2half_rn(vals[k]);
+            }
+        }
+        if (push.tp > 0 && row0 + rr + 3 < out_dim)
+            p2p_write2(push, target, ((size_t)col * out_dim + row0 + rr) >> 2, pack_half2(vals[0], vals[1]),
+                       pack_half2(vals[2], vals[3]));
+    }
+    cluster.sync();   // nobody leaves while a peer may still read its tile
+}
+
 template <int NT>   // batch columns padded to 8 * NT
 __global__ void __launch_bounds__(kSgThreads, kSgCtasPerSm) skinny_gemm_kernel(
     const __half* __restrict__ w, const __half* __restrict__ x, __half* __restrict__ y16, float* __restrict__ y32,
@@ -412,11 +451,9 @@ __global__ void __launch_bounds__(kSgThreads, kSgCtasPerSm) skinny_gemm_kernel(
     }
     // Partial tile of this split, [batch column][row] with a padded column stride, in the (now idle)
     // pipeline buffers; the cluster then shares the reduction out by flat 4-float slices.
-    namespace cg = cooperative_groups;
-    cg::cluster_group cluster = cg::this_cluster();
     asm volatile("cp.async.wait_all;" ::: "memory");
     __syncthreads();
-    constexpr int TS = kSgRows + 4;                       // floats per column: 16-byte aligned, conflict-free stores
+    constexpr int TS = kSgTileStride;
     float* tile = reinterpret_cast<float*>(smem);
 #pragma unroll
     for (int m = 0; m < 2; ++m)
@@ -425,32 +462,199 @@ __global__ void __launch_bounds__(kSgThreads, kSgCtasPerSm) skinny_gemm_kernel(
 #pragma unroll
             for (int e = 0; e < 4; ++e)
                 tile[(8 * j + 2 * t + (e & 1)) * TS + warp * 32 + 16 * m + r + ((e & 2) ? 8 : 0)] = acc[m][j][e];
-    cluster.sync();
-    const unsigned rank = cluster.block_rank();
-    const int quads = batch * (kSgRows / 4);              // 4 consecutive rows of one column
-    const int per = (quads + splits - 1) / splits;
-    const int lo = (int)rank * per, hi = min(quads, lo + per);
-    for (int u = lo + (int)threadIdx.x; u < hi; u += kSgThreads) {
-        const int col = u / (kSgRows / 4), rr = (u - col * (kSgRows / 4)) * 4;
-        float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        for (int peer = 0; peer < splits; ++peer) {
-            const float4 v = *reinterpret_cast<const float4*>(cluster.map_shared_rank(tile, peer) + col * TS + rr);
-            sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
-        }
-        const float vals[4] = {sum.x, sum.y, sum.z, sum.w};
+    sg_reduce_store(tile, row0, out_dim, batch, splits, y16, y32, push, target);
+}
+
+// ------------------------------------------------------------------------------------------------
+// The same product on the 5th-generation tensor cores (tcgen05): the legacy mma.sync path above is half
+// busy at half the weight bandwidth once the batch reaches 64 columns, this one leaves the SM's issue slots
+// to the copies. Per CTA: 128 output rows x N batch columns (N = 16, 32 or 64), accumulated in tensor
+// memory (N fp32 columns of the 128 lanes). A [128 x 64] W tile is the A operand and the [N x 64] x chunk
+// the B operand, both K-major in shared memory in the canonical 128-byte-swizzled form (row pitch 128
+// bytes, 16-byte chunk c of row r stored at chunk c ^ (r % 8), eight-row groups 1024 bytes apart), which
+// is what the matrix descriptors below describe. All 128 threads stream the tiles with 16-byte cp.async
+// through a 3-stage ring; thread 0 issues four tcgen05.mma (K = 16 each) per chunk and commits them to the
+// stage's mbarrier, which is what a later refill of that stage waits for. The epilogue reads the
+// accumulators with tcgen05.ld (warp w owns lanes 32 w .. 32 w + 31, one output row per thread) into the
+// partial tile and shares the split-K reduction with the mma.sync kernel.
+// Every mbarrier wait is bounded; a wait that gives up is counted in g_umma_wait_failures and the kernel
+// runs to its end (tensor memory freed, cluster barriers met) with a meaningless result.
+__device__ unsigned g_umma_wait_failures = 0;
+
+constexpr int kUmControlBytes = 1024;   // mbarriers and the tensor-memory address, ahead of the 1024-byte aligned stages
+
+__device__ __forceinline__ uint32_t um_offset(int row, int chunk) {
+    return (uint32_t)row * kSgRowBytes + (uint32_t)((chunk ^ (row & 7)) << 4);
+}
+// Shared-memory matrix descriptor of a K-major, 128-byte-swizzled tile whose rows are 128 bytes: start
+// address, leading-dimension offset 16 bytes (unused by this layout), stride between 8-row groups 1024
+// bytes, descriptor version 1, layout type 2 (128-byte swizzle). All offsets in units of 16 bytes.
+__device__ __forceinline__ uint64_t um_desc(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor, kind::f16: fp32 accumulate (bit 4), fp16 A and B (formats 0), both K-major, N >> 3
+// at bit 17, M >> 4 at bit 24.
+__host__ __device__ constexpr uint32_t um_idesc(int n) {
+    return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kSgRows >> 4) << 24);
+}
+__device__ __forceinline__ void um_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void um_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void um_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void um_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// 16 consecutive fp32 columns of the thread's lane
+__device__ __forceinline__ void um_ld16(uint32_t taddr, float* v) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const int row = row0 + rr + k;
-            if (row < out_dim) {
-                if (y32) y32[(size_t)col * out_dim + row] = vals[k];
-                if (y16) y16[(size_t)col * out_dim + row] = __float2half_rn(vals[k]);
-            }
-        }
-        if (push.tp > 0 && row0 + rr + 3 < out_dim)
-            p2p_write2(push, target, ((size_t)col * out_dim + row0 + rr) >> 2, pack_half2(vals[0], vals[1]),
-                       pack_half2(vals[2], vals[3]));
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+template <int N>   // batch columns padded to N
+__global__ void __launch_bounds__(kSgThreads, kSgCtasPerSm) umma_gemm_kernel(
+    const __half* __restrict__ w, const __half* __restrict__ x, __half* __restrict__ y16, float* __restrict__ y32,
+    int out_dim, int in_dim, int batch, int chunks_per_split, const P2pPush push) {
+    extern __shared__ __align__(128) unsigned char smem_unaligned[];
+    constexpr int W_BYTES = kSgRows * kSgRowBytes, X_BYTES = N * kSgRowBytes, STAGE = W_BYTES + X_BYTES;
+    constexpr int TMEM_COLS = N < 32 ? 32 : N;
+    static_assert(N == 16 || N == 32 || N == 64, "batch columns per tile");
+    static_assert(STAGE % 1024 == 0 && W_BYTES % 1024 == 0, "swizzled tiles start on 1024-byte boundaries");
+    // the swizzle is a function of the address bits, so the stages start on a 1024-byte boundary of the window
+    const uint32_t base = (smem_u32(smem_unaligned) + 1023u) & ~1023u;
+    unsigned char* smem = smem_unaligned + (base - smem_u32(smem_unaligned));
+    const uint32_t bar0 = base;                            // mma_done[stage] at +8 stage, all_done at +8 kSgStages
+    const uint32_t all_done = bar0 + 8u * kSgStages;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + 8 * (kSgStages + 1));
+    const uint32_t stages = base + kUmControlBytes;
+    unsigned char* stage_ptr = smem + kUmControlBytes;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row0 = blockIdx.x * kSgRows;
+    const int total_chunks = in_dim / kSgK;
+    const int c0 = blockIdx.y * chunks_per_split;
+    const int c1 = min(total_chunks, c0 + chunks_per_split);
+    const int nchunks = max(c1 - c0, 0);
+
+    if (threadIdx.x == 0) {
+        for (int st = 0; st <= kSgStages; ++st) mbar_init(reinterpret_cast<uint64_t*>(smem) + st, 1);
+        fence_barrier_init();
     }
-    cluster.sync();   // nobody leaves while a peer may still read its tile
+    // rows of x beyond the batch are zero in every stage (they are never overwritten)
+    for (int idx = threadIdx.x; idx < kSgStages * (N - batch) * (kSgRowBytes / 4); idx += kSgThreads) {
+        const int st = idx / ((N - batch) * (kSgRowBytes / 4));
+        const int rem = idx - st * ((N - batch) * (kSgRowBytes / 4));
+        reinterpret_cast<uint32_t*>(stage_ptr + st * STAGE + W_BYTES + batch * kSgRowBytes)[rem] = 0u;
+    }
+    if (warp == 0) {   // tensor memory for the accumulators: allocated by one warp, the address lands in shared memory
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "n"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    um_fence_before();
+    __syncthreads();
+    um_fence_after();
+    const uint32_t tmem_d = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+    // each thread always copies the same (row, 16-byte column) positions of a tile
+    const int cp_row = threadIdx.x >> 3, cp_chunk = threadIdx.x & 7;   // rows cp_row + 16 k: the same row % 8
+    const uint32_t cp_dst = um_offset(cp_row, cp_chunk);
+    auto issue_w = [&](int c) {
+        const uint32_t st = stages + (uint32_t)(c % kSgStages) * STAGE;
+        const size_t k0 = (size_t)(c0 + c) * kSgK;
+#pragma unroll
+        for (int k = 0; k < kSgRows / 16; ++k) {
+            const int row = min(row0 + cp_row + 16 * k, out_dim - 1);
+            cp_async16_32(st + cp_dst + (uint32_t)(16 * k) * kSgRowBytes, w + (size_t)row * in_dim + k0 + cp_chunk * 8);
+        }
+    };
+    auto issue_x = [&](int c) {
+        const uint32_t st = stages + (uint32_t)(c % kSgStages) * STAGE;
+        const size_t k0 = (size_t)(c0 + c) * kSgK;
+#pragma unroll
+        for (int k = 0; k < N / 16; ++k) {
+            const int row = cp_row + 16 * k;
+            if (row < batch)
+                cp_async16_32(st + W_BYTES + cp_dst + (uint32_t)(16 * k) * kSgRowBytes,
+                              x + (size_t)row * in_dim + k0 + cp_chunk * 8);
+        }
+    };
+    // The weights do not depend on the kernel before this one: the W tiles of the first stages are requested
+    // before waiting for it (the kernel may have been launched early), the x chunks after.
+    pdl_trigger();
+    for (int c = 0; c < kSgStages - 1; ++c)
+        if (c < nchunks) issue_w(c);
+    pdl_wait();
+    for (int c = 0; c < kSgStages - 1; ++c) {
+        if (c < nchunks) issue_x(c);
+        asm volatile("cp.async.commit_group;" ::: "memory");   // group c: x chunk c (and, in group 0, every early W tile)
+    }
+
+    bool failed = false;
+    constexpr uint32_t idesc = um_idesc(N);
+    for (int c = 0; c < nchunks; ++c) {
+        asm volatile("cp.async.wait_group %0;" ::"n"(kSgStages - 2) : "memory");
+        fence_proxy_async();   // this thread's part of chunk c, written by cp.async, becomes visible to the tensor core's reads
+        __syncthreads();       // ... and so has everybody else's
+        const int st = c % kSgStages;
+        if (threadIdx.x == 0) {
+            um_fence_after();
+            const uint64_t adesc = um_desc(stages + (uint32_t)st * STAGE), bdesc = um_desc(stages + (uint32_t)st * STAGE + W_BYTES);
+#pragma unroll
+            for (int k = 0; k < kSgK / 16; ++k)   // 16 contraction elements = 32 bytes further along the swizzled row
+                um_mma(tmem_d, adesc + 2u * k, bdesc + 2u * k, idesc, (c > 0 || k > 0) ? 1u : 0u);
+            um_commit(bar0 + 8u * st);            // arrives when these (and all earlier) MMAs have read their operands
+        }
+        // chunk c + stages - 1 goes where chunk c - 1 was: wait until the tensor core has finished with it
+        if (c + kSgStages - 1 < nchunks) {
+            if (c > 0) {
+                const int prev = (c - 1) % kSgStages;
+                if (!mbar_wait32(bar0 + 8u * prev, (uint32_t)((c - 1) / kSgStages) & 1u)) failed = true;
+            }
+            issue_w(c + kSgStages - 1);
+            issue_x(c + kSgStages - 1);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    if (nchunks > 0) {
+        if (threadIdx.x == 0) um_commit(all_done);   // every MMA of this CTA has completed when this arrives
+        if (!mbar_wait32(all_done, 0u)) failed = true;
+    }
+    um_fence_after();
+    asm volatile("cp.async.wait_all;" ::: "memory");
+
+    // accumulators: lane (= output row) 32 warp + lane, N columns
+    float acc[N];
+    if (nchunks > 0) {
+#pragma unroll
+        for (int j = 0; j < N; j += 16) um_ld16(tmem_d + ((uint32_t)(warp * 32) << 16) + (uint32_t)j, acc + j);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    } else {
+#pragma unroll
+        for (int j = 0; j < N; ++j) acc[j] = 0.0f;
+    }
+    um_fence_before();
+    __syncthreads();   // all warps have their accumulators; the stages are idle
+    if (warp == 0)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "n"(TMEM_COLS) : "memory");
+    if (failed && lane == 0) atomicAdd(&g_umma_wait_failures, 1u);
+
+    constexpr int TS = kSgTileStride;
+    float* tile = reinterpret_cast<float*>(stage_ptr);
+#pragma unroll
+    for (int j = 0; j < N; ++j) tile[j * TS + warp * 32 + lane] = acc[j];
+    P2pTarget target = {};
+    if (push.tp > 0) target = p2p_target(push);
+    sg_reduce_store(tile, row0, out_dim, batch, (int)gridDim.y, y16, y32, push, target);
 }
 
 struct SkinnyPlan { int row_blocks, splits, chunks_per_split, nt; };
@@ -501,6 +705,36 @@ cudaError_t launch_skinny_nt(const __half* w, const __half* x, __half* y16, floa
     return cudaLaunchKernelEx(&cfg, skinny_gemm_kernel<NT>, w, x, y16, y32, out_dim, in_dim, batch, p.chunks_per_split, push);
 }
 
+// KIVI_SKINNY_UMMA in the environment: the smallest batch that takes the tcgen05 kernel (tuning switch; above 64: never).
+inline int umma_min_batch() {
+    static const int v = [] { const char* e = getenv("KIVI_SKINNY_UMMA"); return e ? atoi(e) : 33; }();
+    return v;
+}
+
+template <int N>
+cudaError_t launch_umma_n(const __half* w, const __half* x, __half* y16, float* y32, int out_dim, int in_dim, int batch,
+                          const SkinnyPlan& p, const P2pPush& push, cudaStream_t stream) {
+    // 1024 bytes of slack to align the stages, the control block, the ring
+    const int smem = 1024 + kUmControlBytes + kSgStages * (kSgRows + N) * kSgRowBytes;
+    cudaError_t e = cudaFuncSetAttribute(umma_gemm_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return e;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.row_blocks, p.splits, 1);
+    cfg.blockDim = dim3(kSgThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = p.splits;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = skinny_early_launch() ? 2 : 1;
+    return cudaLaunchKernelEx(&cfg, umma_gemm_kernel<N>, w, x, y16, y32, out_dim, in_dim, batch, p.chunks_per_split, push);
+}
+
 }  // namespace
 
 bool skinny_gemm_supports(int in_dim, int batch) { return batch > 4 && batch <= 64 && in_dim % kSgK == 0; }
@@ -511,6 +745,11 @@ cudaError_t launch_skinny_gemm(const __half* w, const __half* x, __half* y16, fl
     if (push_or_null && out_dim % 4) return cudaErrorInvalidValue;
     const P2pPush push = push_or_null ? *push_or_null : P2pPush{};
     const SkinnyPlan p = plan_skinny(out_dim, in_dim, batch);
+    if (batch >= umma_min_batch()) {
+        if (batch <= 16) return launch_umma_n<16>(w, x, y16, y32, out_dim, in_dim, batch, p, push, stream);
+        if (batch <= 32) return launch_umma_n<32>(w, x, y16, y32, out_dim, in_dim, batch, p, push, stream);
+        return launch_umma_n<64>(w, x, y16, y32, out_dim, in_dim, batch, p, push, stream);
+    }
     switch (p.nt) {
         case 1: return launch_skinny_nt<1>(w, x, y16, y32, out_dim, in_dim, batch, p, push, stream);
         case 2: return launch_skinny_nt<2>(w, x, y16, y32, out_dim, in_dim, batch, p, push, stream);
