@@ -7,6 +7,7 @@
 // four k-steps are in flight per row, x sits in shared memory as fp16, products accumulate in fp32
 // and a shuffle tree finishes each row. Up to four batch columns share one pass over W.
 #include <cooperative_groups.h>
+#include <cuda.h>
 
 #include "kivi_common.cuh"
 #include "step_math.cuh"
@@ -243,7 +244,9 @@ cudaError_t launch_gemv(const __half* w, const __half* x, __half* y16, float* y3
 }  // namespace kivi
 
 // ------------------------------------------------------------------------------------------------
-// Skinny GEMM for 5..64 batch columns: y[b, o] = sum_i W[o, i] x[b, i] on the tensor cores.
+// Skinny GEMM for 5..64 batch columns: y[b, o] = sum_i W[o, i] x[b, i] on the tensor cores. Two kernels: the
+// tcgen05 + TMA kernel further down is the one that runs; the mma.sync kernel described here is what it
+// replaced, kept behind KIVI_SKINNY_UMMA as the comparison (both share the split-K reduction).
 //
 // The product is still weight-bandwidth bound (every W byte is used once per batch column), so the
 // kernel is a W streamer whose arithmetic happens to be MMAs. A CTA of four warps owns 128 output
@@ -263,6 +266,7 @@ namespace {
 
 constexpr int kSgRows = 128, kSgK = 64, kSgStages = 3, kSgThreads = 128, kSgCtasPerSm = 3;
 constexpr int kSgRowBytes = kSgK * 2;
+constexpr int kSgMaxSplits = 8;   // portable cluster size
 
 __device__ __forceinline__ uint32_t sg_offset(int row, int chunk) {
     return (uint32_t)row * kSgRowBytes + (uint32_t)((chunk ^ ((row & 1) << 2)) << 4);
@@ -286,11 +290,15 @@ __device__ __forceinline__ void sg_reduce_store(float* tile, int row0, int out_d
     const int lo = (int)rank * per, hi = min(quads, lo + per);
     for (int u = lo + (int)threadIdx.x; u < hi; u += kSgThreads) {
         const int col = u / (kSgRows / 4), rr = (u - col * (kSgRows / 4)) * 4;
+        // all remote loads are issued before the first one is used: their latencies overlap
+        float4 part[kSgMaxSplits];
+#pragma unroll
+        for (int peer = 0; peer < kSgMaxSplits; ++peer)
+            if (peer < splits) part[peer] = *reinterpret_cast<const float4*>(cluster.map_shared_rank(tile, peer) + col * TS + rr);
         float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        for (int peer = 0; peer < splits; ++peer) {
-            const float4 v = *reinterpret_cast<const float4*>(cluster.map_shared_rank(tile, peer) + col * TS + rr);
-            sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
-        }
+#pragma unroll
+        for (int peer = 0; peer < kSgMaxSplits; ++peer)
+            if (peer < splits) { sum.x += part[peer].x; sum.y += part[peer].y; sum.z += part[peer].z; sum.w += part[peer].w; }
         const float vals[4] = {sum.x, sum.y, sum.z, sum.w};
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
@@ -466,26 +474,27 @@ __global__ void __launch_bounds__(kSgThreads, kSgCtasPerSm) skinny_gemm_kernel(
 }
 
 // ------------------------------------------------------------------------------------------------
-// The same product on the 5th-generation tensor cores (tcgen05): the legacy mma.sync path above is half
-// busy at half the weight bandwidth once the batch reaches 64 columns, this one leaves the SM's issue slots
-// to the copies. Per CTA: 128 output rows x N batch columns (N = 16, 32 or 64), accumulated in tensor
-// memory (N fp32 columns of the 128 lanes). A [128 x 64] W tile is the A operand and the [N x 64] x chunk
-// the B operand, both K-major in shared memory in the canonical 128-byte-swizzled form (row pitch 128
-// bytes, 16-byte chunk c of row r stored at chunk c ^ (r % 8), eight-row groups 1024 bytes apart), which
-// is what the matrix descriptors below describe. All 128 threads stream the tiles with 16-byte cp.async
-// through a 3-stage ring; thread 0 issues four tcgen05.mma (K = 16 each) per chunk and commits them to the
-// stage's mbarrier, which is what a later refill of that stage waits for. The epilogue reads the
-// accumulators with tcgen05.ld (warp w owns lanes 32 w .. 32 w + 31, one output row per thread) into the
-// partial tile and shares the split-K reduction with the mma.sync kernel.
+// The same product on the 5th-generation tensor cores (tcgen05 + TMA), the form taken by default: the legacy
+// mma.sync path above is half busy at half the weight bandwidth once the batch reaches 64 columns, and its
+// copies compete with the MMAs for issue slots. Per CTA: 128 output rows x N batch columns (N = 16, 32 or
+// 64), accumulated in tensor memory (N fp32 columns of the 128 lanes). A [128 x 64] W tile is the A operand
+// and the [N x 64] x chunk the B operand, both K-major in shared memory in the canonical 128-byte-swizzled
+// form (row pitch 128 bytes, 16-byte chunk c of row r stored at chunk c ^ (r % 8), eight-row groups 1024
+// bytes apart): that is what a tiled bulk copy with 128-byte swizzle writes and what the matrix
+// descriptors below describe. Nothing in the main loop is done by the CTA as a whole. One thread of warp 0
+// requests, per chunk, the W tile and the x chunk as two tiled bulk copies (cp.async.bulk.tensor; rows
+// beyond out_dim or the batch arrive as zeros) into a 4-stage ring and arms the stage's `full` barrier with
+// the byte count; one thread of warp 1 waits for `full`, issues the four tcgen05.mma (K = 16 each) of the
+// chunk and commits them to the stage's `empty` barrier, which the requesting thread waits for before it
+// reuses the stage. The other threads sleep on `all_done` until the last MMA has completed; then every warp
+// reads its accumulators with tcgen05.ld (warp w owns lanes 32 w .. 32 w + 31, one output row per thread)
+// into the partial tile and the split-K reduction is the one of the mma.sync kernel.
 // Every mbarrier wait is bounded; a wait that gives up is counted in g_umma_wait_failures and the kernel
 // runs to its end (tensor memory freed, cluster barriers met) with a meaningless result.
 __device__ unsigned g_umma_wait_failures = 0;
 
 constexpr int kUmControlBytes = 1024;   // mbarriers and the tensor-memory address, ahead of the 1024-byte aligned stages
 
-__device__ __forceinline__ uint32_t um_offset(int row, int chunk) {
-    return (uint32_t)row * kSgRowBytes + (uint32_t)((chunk ^ (row & 7)) << 4);
-}
 // Shared-memory matrix descriptor of a K-major, 128-byte-swizzled tile whose rows are 128 bytes: start
 // address, leading-dimension offset 16 bytes (unused by this layout), stride between 8-row groups 1024
 // bytes, descriptor version 1, layout type 2 (128-byte swizzle). All offsets in units of 16 bytes.
@@ -521,21 +530,35 @@ __device__ __forceinline__ void um_ld16(uint32_t taddr, float* v) {
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+constexpr int kUmTmaStages = 4, kUmTmaCtasPerSm = 2;
+// The cluster reduction moves splits x N x 128 partial sums through distributed shared memory, whose throughput is
+// far below the load path's: with N = 64, seven splits cost 10-15 us per launch, four cost a third of that and
+// still leave enough CTAs (each with four 24 KB stages in flight) to stream at full rate.
+constexpr int kUmTmaMaxSplits = 4;
+__host__ __device__ constexpr int um_tma_smem_bytes(int n) {   // 1024 bytes of slack to align the stages
+    return 1024 + kUmControlBytes + kUmTmaStages * (kSgRows + n) * kSgRowBytes;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+
 template <int N>   // batch columns padded to N
-__global__ void __launch_bounds__(kSgThreads, kSgCtasPerSm) umma_gemm_kernel(
-    const __half* __restrict__ w, const __half* __restrict__ x, __half* __restrict__ y16, float* __restrict__ y32,
-    int out_dim, int in_dim, int batch, int chunks_per_split, const P2pPush push) {
+__global__ void __launch_bounds__(kSgThreads, kUmTmaCtasPerSm) umma_tma_gemm_kernel(
+    const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap, __half* __restrict__ y16,
+    float* __restrict__ y32, int out_dim, int in_dim, int batch, int chunks_per_split, const P2pPush push) {
     extern __shared__ __align__(128) unsigned char smem_unaligned[];
+    constexpr int S = kUmTmaStages;
     constexpr int W_BYTES = kSgRows * kSgRowBytes, X_BYTES = N * kSgRowBytes, STAGE = W_BYTES + X_BYTES;
     constexpr int TMEM_COLS = N < 32 ? 32 : N;
     static_assert(N == 16 || N == 32 || N == 64, "batch columns per tile");
     static_assert(STAGE % 1024 == 0 && W_BYTES % 1024 == 0, "swizzled tiles start on 1024-byte boundaries");
-    // the swizzle is a function of the address bits, so the stages start on a 1024-byte boundary of the window
     const uint32_t base = (smem_u32(smem_unaligned) + 1023u) & ~1023u;
     unsigned char* smem = smem_unaligned + (base - smem_u32(smem_unaligned));
-    const uint32_t bar0 = base;                            // mma_done[stage] at +8 stage, all_done at +8 kSgStages
-    const uint32_t all_done = bar0 + 8u * kSgStages;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + 8 * (kSgStages + 1));
+    const uint32_t full0 = base, empty0 = base + 8u * S, all_done = base + 16u * S;   // mbarriers
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + 16 * S + 8);
     const uint32_t stages = base + kUmControlBytes;
     unsigned char* stage_ptr = smem + kUmControlBytes;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -546,16 +569,10 @@ __global__ void __launch_bounds__(kSgThreads, kSgCtasPerSm) umma_gemm_kernel(
     const int nchunks = max(c1 - c0, 0);
 
     if (threadIdx.x == 0) {
-        for (int st = 0; st <= kSgStages; ++st) mbar_init(reinterpret_cast<uint64_t*>(smem) + st, 1);
+        for (int i = 0; i < 2 * S + 1; ++i) mbar_init(reinterpret_cast<uint64_t*>(smem) + i, 1);
         fence_barrier_init();
     }
-    // rows of x beyond the batch are zero in every stage (they are never overwritten)
-    for (int idx = threadIdx.x; idx < kSgStages * (N - batch) * (kSgRowBytes / 4); idx += kSgThreads) {
-        const int st = idx / ((N - batch) * (kSgRowBytes / 4));
-        const int rem = idx - st * ((N - batch) * (kSgRowBytes / 4));
-        reinterpret_cast<uint32_t*>(stage_ptr + st * STAGE + W_BYTES + batch * kSgRowBytes)[rem] = 0u;
-    }
-    if (warp == 0) {   // tensor memory for the accumulators: allocated by one warp, the address lands in shared memory
+    if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                      ::"r"(smem_u32(tmem_slot)), "n"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -565,72 +582,47 @@ __global__ void __launch_bounds__(kSgThreads, kSgCtasPerSm) umma_gemm_kernel(
     um_fence_after();
     const uint32_t tmem_d = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
 
-    // each thread always copies the same (row, 16-byte column) positions of a tile
-    const int cp_row = threadIdx.x >> 3, cp_chunk = threadIdx.x & 7;   // rows cp_row + 16 k: the same row % 8
-    const uint32_t cp_dst = um_offset(cp_row, cp_chunk);
-    auto issue_w = [&](int c) {
-        const uint32_t st = stages + (uint32_t)(c % kSgStages) * STAGE;
-        const size_t k0 = (size_t)(c0 + c) * kSgK;
-#pragma unroll
-        for (int k = 0; k < kSgRows / 16; ++k) {
-            const int row = min(row0 + cp_row + 16 * k, out_dim - 1);
-            cp_async16_32(st + cp_dst + (uint32_t)(16 * k) * kSgRowBytes, w + (size_t)row * in_dim + k0 + cp_chunk * 8);
-        }
-    };
-    auto issue_x = [&](int c) {
-        const uint32_t st = stages + (uint32_t)(c % kSgStages) * STAGE;
-        const size_t k0 = (size_t)(c0 + c) * kSgK;
-#pragma unroll
-        for (int k = 0; k < N / 16; ++k) {
-            const int row = cp_row + 16 * k;
-            if (row < batch)
-                cp_async16_32(st + W_BYTES + cp_dst + (uint32_t)(16 * k) * kSgRowBytes,
-                              x + (size_t)row * in_dim + k0 + cp_chunk * 8);
-        }
-    };
-    // The weights do not depend on the kernel before this one: the W tiles of the first stages are requested
-    // before waiting for it (the kernel may have been launched early), the x chunks after.
-    pdl_trigger();
-    for (int c = 0; c < kSgStages - 1; ++c)
-        if (c < nchunks) issue_w(c);
-    pdl_wait();
-    for (int c = 0; c < kSgStages - 1; ++c) {
-        if (c < nchunks) issue_x(c);
-        asm volatile("cp.async.commit_group;" ::: "memory");   // group c: x chunk c (and, in group 0, every early W tile)
-    }
-
     bool failed = false;
-    constexpr uint32_t idesc = um_idesc(N);
-    for (int c = 0; c < nchunks; ++c) {
-        asm volatile("cp.async.wait_group %0;" ::"n"(kSgStages - 2) : "memory");
-        fence_proxy_async();   // this thread's part of chunk c, written by cp.async, becomes visible to the tensor core's reads
-        __syncthreads();       // ... and so has everybody else's
-        const int st = c % kSgStages;
-        if (threadIdx.x == 0) {
-            um_fence_after();
-            const uint64_t adesc = um_desc(stages + (uint32_t)st * STAGE), bdesc = um_desc(stages + (uint32_t)st * STAGE + W_BYTES);
+    pdl_trigger();
+    if (threadIdx.x == 0) {
+        // The weights do not depend on the kernel before this one: the W tiles of the first stages are requested
+        // before waiting for it (the kernel may have been launched early), the x chunks after.
+        const int pre = min(S, nchunks);
+        for (int c = 0; c < pre; ++c) {
+            mbar_expect_tx32(full0 + 8u * c, STAGE);
+            tma_load_2d(stages + (uint32_t)c * STAGE, &wmap, (c0 + c) * kSgK, row0, full0 + 8u * c);
+        }
+        pdl_wait();
+        for (int c = 0; c < pre; ++c)
+            tma_load_2d(stages + (uint32_t)c * STAGE + W_BYTES, &xmap, (c0 + c) * kSgK, 0, full0 + 8u * c);
+        for (int c = pre; c < nchunks; ++c) {
+            const int st = c % S;
+            // the MMAs of chunk c - S, the stage's previous tenant, have read their operands
+            if (!mbar_wait32(empty0 + 8u * st, (uint32_t)(c / S - 1) & 1u)) failed = true;
+            mbar_expect_tx32(full0 + 8u * st, STAGE);
+            tma_load_2d(stages + (uint32_t)st * STAGE, &wmap, (c0 + c) * kSgK, row0, full0 + 8u * st);
+            tma_load_2d(stages + (uint32_t)st * STAGE + W_BYTES, &xmap, (c0 + c) * kSgK, 0, full0 + 8u * st);
+        }
+    } else {
+        pdl_wait();
+        if (threadIdx.x == 32) {
+            constexpr uint32_t idesc = um_idesc(N);
+            for (int c = 0; c < nchunks; ++c) {
+                const int st = c % S;
+                if (!mbar_wait32(full0 + 8u * st, (uint32_t)(c / S) & 1u)) failed = true;
+                um_fence_after();
+                const uint64_t adesc = um_desc(stages + (uint32_t)st * STAGE), bdesc = um_desc(stages + (uint32_t)st * STAGE + W_BYTES);
 #pragma unroll
-            for (int k = 0; k < kSgK / 16; ++k)   // 16 contraction elements = 32 bytes further along the swizzled row
-                um_mma(tmem_d, adesc + 2u * k, bdesc + 2u * k, idesc, (c > 0 || k > 0) ? 1u : 0u);
-            um_commit(bar0 + 8u * st);            // arrives when these (and all earlier) MMAs have read their operands
-        }
-        // chunk c + stages - 1 goes where chunk c - 1 was: wait until the tensor core has finished with it
-        if (c + kSgStages - 1 < nchunks) {
-            if (c > 0) {
-                const int prev = (c - 1) % kSgStages;
-                if (!mbar_wait32(bar0 + 8u * prev, (uint32_t)((c - 1) / kSgStages) & 1u)) failed = true;
+                for (int k = 0; k < kSgK / 16; ++k)   // 16 contraction elements = 32 bytes further along the swizzled row
+                    um_mma(tmem_d, adesc + 2u * k, bdesc + 2u * k, idesc, (c > 0 || k > 0) ? 1u : 0u);
+                um_commit(empty0 + 8u * st);
             }
-            issue_w(c + kSgStages - 1);
-            issue_x(c + kSgStages - 1);
+            if (nchunks > 0) um_commit(all_done);   // every MMA of this CTA has completed when this arrives
         }
-        asm volatile("cp.async.commit_group;" ::: "memory");
     }
-    if (nchunks > 0) {
-        if (threadIdx.x == 0) um_commit(all_done);   // every MMA of this CTA has completed when this arrives
-        if (!mbar_wait32(all_done, 0u)) failed = true;
-    }
+    __syncwarp();
+    if (nchunks > 0 && !mbar_wait32(all_done, 0u)) failed = true;
     um_fence_after();
-    asm volatile("cp.async.wait_all;" ::: "memory");
 
     // accumulators: lane (= output row) 32 warp + lane, N columns
     float acc[N];
@@ -643,13 +635,13 @@ __global__ void __launch_bounds__(kSgThreads, kSgCtasPerSm) umma_gemm_kernel(
         for (int j = 0; j < N; ++j) acc[j] = 0.0f;
     }
     um_fence_before();
-    __syncthreads();   // all warps have their accumulators; the stages are idle
+    __syncthreads();   // all warps have their accumulators
     if (warp == 0)
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "n"(TMEM_COLS) : "memory");
-    if (failed && lane == 0) atomicAdd(&g_umma_wait_failures, 1u);
+    if (failed) atomicAdd(&g_umma_wait_failures, 1u);
 
     constexpr int TS = kSgTileStride;
-    float* tile = reinterpret_cast<float*>(stage_ptr);
+    float* tile = reinterpret_cast<float*>(stage_ptr);   // the stages are idle
 #pragma unroll
     for (int j = 0; j < N; ++j) tile[j * TS + warp * 32 + lane] = acc[j];
     P2pTarget target = {};
@@ -659,17 +651,15 @@ __global__ void __launch_bounds__(kSgThreads, kSgCtasPerSm) umma_gemm_kernel(
 
 struct SkinnyPlan { int row_blocks, splits, chunks_per_split, nt; };
 
-constexpr int kSgMaxSplits = 8;   // portable cluster size
-
-SkinnyPlan plan_skinny(int out_dim, int in_dim, int batch) {
+SkinnyPlan plan_skinny(int out_dim, int in_dim, int batch, int ctas_per_sm = kSgCtasPerSm, int split_cap = kSgMaxSplits) {
     SkinnyPlan p;
     p.nt = (batch + 7) / 8;
     p.row_blocks = (out_dim + kSgRows - 1) / kSgRows;
     const int chunks = in_dim / kSgK;
-    int splits = kSgCtasPerSm * 148 / p.row_blocks;              // at most one wave of resident CTAs
+    int splits = ctas_per_sm * 148 / p.row_blocks;               // at most one wave of resident CTAs
     const int max_splits = chunks / 8 > 0 ? chunks / 8 : 1;      // at least 8 chunks (512 elements) per CTA
     if (splits > max_splits) splits = max_splits;
-    if (splits > kSgMaxSplits) splits = kSgMaxSplits;
+    if (splits > split_cap) splits = split_cap;
     if (splits < 1) splits = 1;
     p.chunks_per_split = (chunks + splits - 1) / splits;
     p.splits = splits;   // a trailing split may get fewer chunks, or none: it still joins the reduction
@@ -705,18 +695,52 @@ cudaError_t launch_skinny_nt(const __half* w, const __half* x, __half* y16, floa
     return cudaLaunchKernelEx(&cfg, skinny_gemm_kernel<NT>, w, x, y16, y32, out_dim, in_dim, batch, p.chunks_per_split, push);
 }
 
-// KIVI_SKINNY_UMMA in the environment: the smallest batch that takes the tcgen05 kernel (tuning switch; above 64: never).
+// KIVI_SKINNY_UMMA in the environment: the smallest batch that takes the tcgen05 kernel (tuning switch; above 64:
+// never, every batch then runs on the mma.sync kernel).
 inline int umma_min_batch() {
-    static const int v = [] { const char* e = getenv("KIVI_SKINNY_UMMA"); return e ? atoi(e) : 33; }();
+    static const int v = [] { const char* e = getenv("KIVI_SKINNY_UMMA"); return e ? atoi(e) : 5; }();
     return v;
 }
 
+// cuTensorMapEncodeTiled through the runtime's driver entry point lookup: the library does not link libcuda.
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+inline EncodeTiledFn encode_tiled() {
+    static const EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// Tensor map of a row-major fp16 matrix [rows, cols] read in boxes of box_rows x 64 columns, 128-byte swizzle,
+// out-of-range elements as zeros. base 16-byte aligned, cols a multiple of 8.
+inline bool make_tile_map(CUtensorMap* map, const __half* base, int rows, int cols, int box_rows) {
+    const EncodeTiledFn fn = encode_tiled();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)cols * sizeof(__half)};
+    const cuuint32_t box[2] = {(cuuint32_t)kSgK, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(base), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int N>
-cudaError_t launch_umma_n(const __half* w, const __half* x, __half* y16, float* y32, int out_dim, int in_dim, int batch,
-                          const SkinnyPlan& p, const P2pPush& push, cudaStream_t stream) {
-    // 1024 bytes of slack to align the stages, the control block, the ring
-    const int smem = 1024 + kUmControlBytes + kSgStages * (kSgRows + N) * kSgRowBytes;
-    cudaError_t e = cudaFuncSetAttribute(umma_gemm_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+cudaError_t launch_umma_tma_n(const __half* w, const __half* x, __half* y16, float* y32, int out_dim, int in_dim, int batch,
+                              const P2pPush& push, cudaStream_t stream) {
+    const SkinnyPlan p = plan_skinny(out_dim, in_dim, batch, kUmTmaCtasPerSm, kUmTmaMaxSplits);
+    CUtensorMap wmap, xmap;
+    if (!make_tile_map(&wmap, w, out_dim, in_dim, kSgRows) || !make_tile_map(&xmap, x, batch, in_dim, N))
+        return cudaErrorInvalidValue;
+    const int smem = um_tma_smem_bytes(N);
+    cudaError_t e = cudaFuncSetAttribute(umma_tma_gemm_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(p.row_blocks, p.splits, 1);
@@ -732,7 +756,7 @@ cudaError_t launch_umma_n(const __half* w, const __half* x, __half* y16, float* 
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = skinny_early_launch() ? 2 : 1;
-    return cudaLaunchKernelEx(&cfg, umma_gemm_kernel<N>, w, x, y16, y32, out_dim, in_dim, batch, p.chunks_per_split, push);
+    return cudaLaunchKernelEx(&cfg, umma_tma_gemm_kernel<N>, wmap, xmap, y16, y32, out_dim, in_dim, batch, p.chunks_per_split, push);
 }
 
 }  // namespace
@@ -746,9 +770,9 @@ cudaError_t launch_skinny_gemm(const __half* w, const __half* x, __half* y16, fl
     const P2pPush push = push_or_null ? *push_or_null : P2pPush{};
     const SkinnyPlan p = plan_skinny(out_dim, in_dim, batch);
     if (batch >= umma_min_batch()) {
-        if (batch <= 16) return launch_umma_n<16>(w, x, y16, y32, out_dim, in_dim, batch, p, push, stream);
-        if (batch <= 32) return launch_umma_n<32>(w, x, y16, y32, out_dim, in_dim, batch, p, push, stream);
-        return launch_umma_n<64>(w, x, y16, y32, out_dim, in_dim, batch, p, push, stream);
+        if (batch <= 16) return launch_umma_tma_n<16>(w, x, y16, y32, out_dim, in_dim, batch, push, stream);
+        if (batch <= 32) return launch_umma_tma_n<32>(w, x, y16, y32, out_dim, in_dim, batch, push, stream);
+        return launch_umma_tma_n<64>(w, x, y16, y32, out_dim, in_dim, batch, push, stream);
     }
     switch (p.nt) {
         case 1: return launch_skinny_nt<1>(w, x, y16, y32, out_dim, in_dim, batch, p, push, stream);
