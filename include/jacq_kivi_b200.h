@@ -178,10 +178,17 @@ int kivi_b200_decode_noalloc(const kivi_geometry* geom, const kivi_cache* cache,
  * crates/jac-codegen-cuda/src/templates/runtime.cu:15-26, a cublasGemmEx call). 1 <= batch <= 64.
  * in_dim % 8 == 0. Exactly one of y_f16 / y_f32 may be NULL; y_f32 is the kernel-DSL form
  * (crates/jac-codegen-cuda/src/variants.rs:318-329). Batches of 5..64 columns with in_dim % 64 == 0
- * run as a tensor-core skinny GEMM that splits the contraction over a thread-block cluster and
- * reduces through distributed shared memory; no call of this entry point allocates. */
+ * run as a tensor-core skinny GEMM (tcgen05, tiles moved by TMA, accumulators in tensor memory) that
+ * splits the contraction over a thread-block cluster and reduces through distributed shared memory;
+ * w and x must then be 16-byte aligned. No call of this entry point allocates. */
 int kivi_b200_gemv_f16(const kivi_f16* w, const kivi_f16* x, kivi_f16* y_f16, float* y_f32,
                        int out_dim, int in_dim, int batch, cudaStream_t stream);
+
+/* The skinny GEMM waits on shared-memory barriers for its copies and tensor-core operations; every such
+ * wait is bounded, and a CTA whose wait gave up runs to its end (result undefined) and counts itself
+ * here. Writes the number of such CTAs since the library was loaded on the current device (0 in any
+ * healthy run) to *failures_out; synchronises the device. */
+int kivi_b200_gemm_wait_failures(uint32_t* failures_out);
 
 /* ------------------------------------------------------------------ ABI v1 (reference lane) -- */
 

@@ -92,6 +92,7 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "kivi_b200_decode_noalloc": (c_int, [ctypes.POINTER(KiviGeometry), ctypes.POINTER(KiviCacheStruct), _P, _P, c_int, _P,
                                          _P, c_int, c_int, _P, _P]),
     "kivi_b200_gemv_f16": (c_int, [_P, _P, _P, _P, c_int, c_int, c_int, _P]),
+    "kivi_b200_gemm_wait_failures": (c_int, [ctypes.POINTER(c_uint32)]),
     "kivi_b200_decode_step_workspace_bytes": (c_size_t, [ctypes.POINTER(KiviStepConfig), c_int, c_int]),
     "kivi_b200_decode_step": (c_int, [ctypes.POINTER(KiviStepConfig), ctypes.POINTER(KiviStepWeights),
                                       ctypes.POINTER(KiviStepState), _P, c_int, c_int, _P, _P,

@@ -635,10 +635,10 @@ __global__ void __launch_bounds__(kSgThreads, kUmTmaCtasPerSm) umma_tma_gemm_ker
         for (int j = 0; j < N; ++j) acc[j] = 0.0f;
     }
     um_fence_before();
-    __syncthreads();   // all warps have their accumulators
+    const bool cta_failed = __syncthreads_or(failed);   // all warps have their accumulators
     if (warp == 0)
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "n"(TMEM_COLS) : "memory");
-    if (failed) atomicAdd(&g_umma_wait_failures, 1u);
+    if (cta_failed && threadIdx.x == 0) atomicAdd(&g_umma_wait_failures, 1u);
 
     constexpr int TS = kSgTileStride;
     float* tile = reinterpret_cast<float*>(stage_ptr);   // the stages are idle
@@ -787,3 +787,11 @@ cudaError_t launch_skinny_gemm(const __half* w, const __half* x, __half* y16, fl
 }
 
 }  // namespace kivi
+
+extern "C" int kivi_b200_gemm_wait_failures(uint32_t* failures_out) {
+    if (!failures_out) return KIVI_ERR_NULL_POINTER;
+    unsigned v = 0;
+    if (cudaMemcpyFromSymbol(&v, kivi::g_umma_wait_failures, sizeof(v)) != cudaSuccess) return KIVI_ERR_CUDA;
+    *failures_out = v;
+    return KIVI_OK;
+}

@@ -60,3 +60,45 @@ def test_gemv_rejects_bad_arguments(native_lib):
         gemv(w, x)
     with pytest.raises(TypeError):
         gemv(w.float(), x)
+
+
+def test_skinny_gemm_waits_did_not_fail(native_lib):
+    """Every barrier wait of the tcgen05 kernel is bounded and counted when it gives up: after a
+    batch that takes that kernel the counter is still zero."""
+    from jacq_b200.cache import gemv
+    from tests.gpu_utils import f16_tensor
+    w, x = _wx(512, 1024, 24, 5)
+    gemv(f16_tensor(w), f16_tensor(x))
+    failures = ctypes.c_uint32(123)
+    assert native_lib.kivi_b200_gemm_wait_failures(ctypes.byref(failures)) == 0
+    assert failures.value == 0
+
+
+_MMA_SYNC_CHECK = """
+import numpy as np, torch
+from jacq_b200.cache import gemv
+from oracle import kivi_oracle as ko
+from tests.gpu_utils import f16_tensor
+rng = np.random.default_rng(11)
+for out_dim, in_dim, batch in [(777, 1024, 13), (1024, 5120, 64), (4096, 128, 8)]:
+    w = (rng.standard_normal((out_dim, in_dim), dtype=np.float32) * 0.02).astype(np.float16)
+    x = rng.standard_normal((batch, in_dim), dtype=np.float32).astype(np.float16)
+    want16, want32 = ko.gemv(w, x, nthreads=8)
+    got32 = gemv(f16_tensor(w), f16_tensor(x), out_dtype=torch.float32).cpu().numpy()
+    assert np.abs(got32 - want32).max() < 2e-3, (out_dim, in_dim, batch)
+print("mma.sync skinny GEMM ok")
+"""
+
+
+def test_mma_sync_skinny_gemm_still_matches(native_lib):
+    """The mma.sync kernel that the tcgen05 kernel replaced stays selectable (KIVI_SKINNY_UMMA above 64);
+    the switch is read once per process, so the check runs in a child."""
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+    env = dict(os.environ, KIVI_SKINNY_UMMA="99")
+    root = Path(__file__).resolve().parent.parent
+    done = subprocess.run([sys.executable, "-c", _MMA_SYNC_CHECK], cwd=root, env=env, capture_output=True, text=True,
+                          timeout=300)
+    assert done.returncode == 0 and "mma.sync skinny GEMM ok" in done.stdout, done.stderr[-2000:]
