@@ -61,7 +61,9 @@ struct SplitPlan { int chunk_tokens; int max_chunks; };
 SplitPlan plan_split(const Geom& g, int n, int max_old_tokens) {
     SplitPlan sp;
     const long long units = (long long)n * g.nkv;
-    long long want = (2LL * kSmCount + units - 1) / units;
+    // as many chunks as fill the resident CTA slots (three per SM) without exceeding them: a second, partial
+    // wave costs more than the idle slots (the residual CTAs a split adds are tiny and do not count)
+    long long want = (3LL * kSmCount) / units;
     if (want < 1) want = 1;
     long long chunk = (max_old_tokens + want - 1) / want;
     if (chunk < kMinChunkTokens) chunk = kMinChunkTokens;
