@@ -164,7 +164,7 @@ __device__ __forceinline__ void fence_barrier_init() {
 __device__ __forceinline__ void fence_proxy_async() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
-// 1-D bulk asynchronous copy global -> shared (the TMA engine, no tensor map, no multicast).
+// 1-D bulk asynchronous copy global -> shared (the TMA engine, no tensor map; the plain single-CTA form).
 // dst, src 16-byte aligned; bytes a multiple of 16.
 __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {
     asm volatile(
