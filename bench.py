@@ -13,7 +13,9 @@ metric / value  achieved HBM GB/s = algorithmic bytes of the step / device time,
                 in HBM; tokens/s rides along as `tokens_per_s`
 e2e             the same bytes over the time of a full serving step through the public API with
                 HOST buffers: pinned q and the step's new K/V rows copied host->device, cache write,
-                decode, output copied device->host
+                decode, output copied device->host; the step is captured once as a CUDA graph and
+                launched once per step (--no-e2e-graph: separate calls), and its last output is
+                checked against a separate decode of the same cache state
 roofline        achieved = algorithmic bytes per launch / mean CUDA-event time of the decode launch,
                 against the measured HBM copy bandwidth in MEASURED_PEAKS.json
 cpu_baseline    the scalar CPU oracle (test infrastructure, a port of the reference's kernel math)
@@ -303,17 +305,42 @@ def run_b200(args):
     offs = torch.arange(batch + 1, device=device, dtype=torch.int32)
     cur = context
 
-    def serving_step(cur_len):
+    # One serving step as the serving engine replays it: copies in, append, attention, copy out, captured once as a
+    # CUDA graph (the bounds the launch plan needs are those of the last step of the run) and launched once per
+    # step. --no-e2e-graph, or a failed capture, issues the same calls one by one.
+    bound = context + e2e_steps + max(3, args.warmup) + 4
+
+    def enqueue_step():
         q_dev.copy_(q_host, non_blocking=True)
         nk_dev.copy_(nk_host, non_blocking=True)
         nv_dev.copy_(nv_host, non_blocking=True)
-        cache.write(nk_dev, nv_dev, offs, max_new_per_seq=1, max_start_seq_len=cur_len)
-        cache.decode(q_dev, out, max_seq_len=cur_len + 1)
+        cache.write(nk_dev, nv_dev, offs, max_new_per_seq=1, max_start_seq_len=bound)
+        cache.decode(q_dev, out, max_seq_len=bound + 1)
         out_host.copy_(out, non_blocking=True)
+
+    enqueue_step()   # once eagerly: every buffer the calls allocate lazily exists before a capture
+    torch.cuda.synchronize(device)
+    cur += 1
+    graph = None
+    if args.e2e_graph:
+        try:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                enqueue_step()
+            graph = g
+        except Exception as exc:   # noqa: BLE001 - the eager path below measures the same step
+            print(f"bench: graph capture of the serving step failed ({exc}); timing the eager calls", file=sys.stderr)
+            torch.cuda.synchronize(device)
+
+    def serving_step():
+        if graph is not None:
+            graph.replay()
+        else:
+            enqueue_step()
         torch.cuda.synchronize(device)
 
     for _ in range(max(3, args.warmup)):
-        serving_step(cur)
+        serving_step()
         cur += 1
     if world > 1:
         dist.barrier()
@@ -321,10 +348,15 @@ def run_b200(args):
     e2e_bytes = 0
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
-        serving_step(cur)
+        serving_step()
         cur += 1
         e2e_bytes += lay.decode_algorithmic_bytes(cur) * batch
     e2e_s = time.perf_counter() - t0
+    # what the last replay copied out is what a separate decode call computes from the same cache state
+    check = cache.decode(q_dev, max_seq_len=bound + 1)
+    torch.cuda.synchronize(device)
+    if not torch.equal(check.cpu(), out_host):
+        raise RuntimeError("bench: the end-to-end step's output differs from a decode of the same cache state")
     if world > 1:
         t = torch.tensor([e2e_s], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -360,7 +392,8 @@ def run_b200(args):
         "pct_of_8TBs_nominal": 100.0 * value / world / 8000.0,
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_s / e2e_steps * 1e3, "tokens_per_s": batch * world / (e2e_s / e2e_steps),
-                "what": "pinned q + new K/V rows H2D, cache write (1 token/sequence), decode, O D2H"},
+                "what": "pinned q + new K/V rows H2D, cache write (1 token/sequence), decode, O D2H"
+                        + ("; one CUDA graph launch per step" if graph is not None else "; eager calls")},
         "gpu_launches": args.steps,
         "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
@@ -821,6 +854,8 @@ def main():
     ap.add_argument("--comm", default="p2p", choices=["p2p", "nccl"],
                     help="decode-step workloads on several GPUs: the library's peer-memory exchange or NCCL hooks")
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
+    ap.add_argument("--no-e2e-graph", dest="e2e_graph", action="store_false",
+                    help="attention workloads: issue the end-to-end serving step as separate calls instead of one CUDA graph")
     ap.add_argument("--profile-only", action="store_true",
                     help="build the cache, run warmup+steps decode launches and exit (for ncu)")
     args = ap.parse_args()
