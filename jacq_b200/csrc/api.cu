@@ -11,6 +11,7 @@ namespace kivi {
 namespace {
 
 constexpr int kSmCount = 148;       // B200
+constexpr int kLongChunkTokens = 6144;
 constexpr int kMinChunkTokens = 256;
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -65,6 +66,19 @@ SplitPlan plan_split(const Geom& g, int n, int max_old_tokens) {
     // wave costs more than the idle slots (the residual CTAs a split adds are tiny and do not count)
     long long want = (3LL * kSmCount) / units;
     if (want < 1) want = 1;
+    // Long contexts: finer chunks are worth their partial results when they round the number of waves better
+    // (256 units x 5 chunks = 2.9 waves of 444 slots instead of 256 CTAs on 444 slots), as long as a chunk stays
+    // long enough to amortise a CTA's start and end (kLongChunkTokens; below it splitting measured slower).
+    {
+        const long long slots = 3LL * kSmCount;
+        auto efficiency = [&](long long w) {
+            const long long ctas = units * w, waves = (ctas + slots - 1) / slots;
+            return (double)ctas / (double)(waves * slots);
+        };
+        double best = efficiency(want);
+        for (long long w = want + 1; w <= 64 && max_old_tokens / w >= kLongChunkTokens; ++w)
+            if (efficiency(w) > best + 0.02) { best = efficiency(w); want = w; }
+    }
     long long chunk = (max_old_tokens + want - 1) / want;
     if (chunk < kMinChunkTokens) chunk = kMinChunkTokens;
     const int gran = g.g > 64 ? g.g : ((64 + g.g - 1) / g.g) * g.g;  // multiple of the group, >= 64
