@@ -19,8 +19,8 @@ def _wx(out_dim, in_dim, batch, seed):
     return w, x
 
 
-@pytest.mark.parametrize("out_dim,in_dim", [(4096, 128), (1024, 5120), (777, 13824), (7168, 5120)])
-@pytest.mark.parametrize("batch", [1, 3, 8, 13, 33, 48, 64])
+@pytest.mark.parametrize("out_dim,in_dim", [(64, 256), (4096, 128), (1024, 5120), (777, 13824), (7168, 5120)])
+@pytest.mark.parametrize("batch", [1, 3, 5, 8, 13, 33, 48, 64])
 def test_gemv_matches_oracle(native_lib, out_dim, in_dim, batch):
     from jacq_b200.cache import gemv
     from tests.gpu_utils import f16_tensor
