@@ -325,7 +325,7 @@ def run_b200(args):
     if args.e2e_graph:
         try:
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
+            with torch.cuda.graph(g, capture_error_mode="thread_local"):   # other threads (NCCL's watchdog) may call CUDA
                 enqueue_step()
             graph = g
         except Exception as exc:   # noqa: BLE001 - the eager path below measures the same step
