@@ -126,22 +126,8 @@ def build_cache(case, batch, context, device, spare_tokens=0, seed=20261125):
 
 def sample_to_oracle(cache, case, seqs):
     """Host copy (OracleCache) of the chosen sequences, pages renumbered densely."""
-    import torch
-    from oracle import kivi_oracle as ko
-    from tests import helpers
-    geom = helpers.oracle_geometry(case)
-    pages = cache.max_blocks_per_seq
-    idx = cache.block_tables[seqs].reshape(-1).long()
-    oc = ko.OracleCache(geom, len(seqs) * pages, len(seqs))
-    t = cache.tensors
-    for name in ("K_CODE_PAGES", "K_SCALE_PAGES", "K_ZERO_PAGES", "V_CODE_PAGES", "V_SCALE_PAGES", "V_ZERO_PAGES"):
-        src = getattr(t, name).index_select(0, idx)
-        getattr(oc, helpers.ORACLE_FIELD[name])[...] = helpers.to_bits(src)
-    sel = torch.tensor(seqs, device=cache.device)
-    oc.k_scratch[...] = helpers.to_bits(t.K_RESIDUAL_SCRATCH.index_select(0, sel))
-    oc.v_scratch[...] = helpers.to_bits(t.V_RESIDUAL_SCRATCH.index_select(0, sel))
-    tables = np.arange(len(seqs) * pages, dtype=np.int32).reshape(len(seqs), pages)
-    return oc, tables
+    from tests.gpu_utils import oracle_copy
+    return oracle_copy(cache, case, seqs)
 
 
 def cpu_baseline(cache, q, case, context, nthreads, target_seconds=12.0):

@@ -89,6 +89,11 @@ def kernel_interface(seq_len: int = MAX_SEQ_LEN) -> dict[str, object]:
         ],
         "v1_symbols": list(V1_SYMBOLS),
         "v2_symbols": list(V2_SYMBOLS),
+        "integrity_boundary": (
+            "A description of the callable surface and nothing more: building it allocates no tensor and "
+            "launches no kernel (CUDA is NOT RUN by this call). Parity and throughput of the library are "
+            "established by its own GPU tests and benchmark, not by this report."
+        ),
     }
 
 

@@ -41,6 +41,26 @@ def bundle_from_oracle(oc: ko.OracleCache) -> dict:
     return b
 
 
+def oracle_copy(cache: KiviCache, case: helpers.Case, seqs):
+    """Host copy (OracleCache) of the chosen sequences of a device cache, their pages renumbered densely;
+    returns the copy and the matching block tables. Lets the CPU oracle decode what the library's writer built
+    on the device without re-quantising the whole context on the host."""
+    geom = helpers.oracle_geometry(case)
+    pages = cache.max_blocks_per_seq
+    seqs = list(seqs)
+    idx = cache.block_tables[seqs].reshape(-1).long()
+    oc = ko.OracleCache(geom, len(seqs) * pages, len(seqs))
+    t = cache.tensors
+    for name in helpers.PAGE_FIELDS:
+        src = getattr(t, name).index_select(0, idx)
+        getattr(oc, helpers.ORACLE_FIELD[name])[...] = helpers.to_bits(src)
+    sel = torch.tensor(seqs, device=cache.device)
+    oc.k_scratch[...] = helpers.to_bits(t.K_RESIDUAL_SCRATCH.index_select(0, sel))
+    oc.v_scratch[...] = helpers.to_bits(t.V_RESIDUAL_SCRATCH.index_select(0, sel))
+    tables = np.arange(len(seqs) * pages, dtype=np.int32).reshape(len(seqs), pages)
+    return oc, tables
+
+
 def ptr(t: torch.Tensor):
     return ctypes.c_void_p(t.data_ptr())
 

@@ -13,6 +13,18 @@ import numpy as np
 BASE_SEED = 20261125
 
 
+def reference_root():
+    """The reference checkout, when one is at hand: $JACQ_REFERENCE, else a directory named `reference`
+    beside this repository. None where neither exists (the GPU box), and the tests that read it skip."""
+    import os
+    from pathlib import Path
+    cands = [os.environ.get("JACQ_REFERENCE"), Path(__file__).resolve().parent.parent.parent / "reference"]
+    for c in cands:
+        if c and (Path(c) / "integrations" / "vllm_kivi" / "source_patch.py").is_file():
+            return Path(c)
+    return None
+
+
 @dataclass(frozen=True)
 class Case:
     name: str

@@ -55,10 +55,9 @@ def test_ragged_interleaved_writes_bit_exact_reduced(native_lib):
         cache.write(f16_tensor(nk), f16_tensor(nv), torch.from_numpy(offs).to(DEV),
                     max_new_per_seq=int(counts.max()), max_start_seq_len=int(lens.max()))
         lens = lens + counts
-        if step % 3 == 0 or step >= steps - 2:
-            torch.cuda.synchronize()
-            live = [int(t - geom.split_old(int(t))) for t in lens]
-            helpers.assert_cache_equal(cache.tensors, oc, live_rows=live, what=f"step {step}: ")
+        torch.cuda.synchronize()
+        live = [int(t - geom.split_old(int(t))) for t in lens]
+        helpers.assert_cache_equal(cache.tensors, oc, live_rows=live, what=f"step {step}: ")
     assert np.array_equal(lens, targets)
     q = helpers.make_q(case, n)
     got = cache.decode(f16_tensor(q), max_seq_len=int(lens.max())).cpu().numpy()
@@ -100,7 +99,7 @@ def _fill_full_size(cache, case, targets, chunk, const_v, seed):
 
 def test_ragged_full_size_properties(native_lib):
     from jacq_b200.cache import KiviCache
-    from tests.gpu_utils import DEV, f16_tensor
+    from tests.gpu_utils import DEV, f16_tensor, oracle_copy
     case = helpers.CONFIGS["mistral7b"]
     lay = helpers.layout_of(case)
     rng = np.random.default_rng(5)
@@ -132,10 +131,31 @@ def test_ragged_full_size_properties(native_lib):
     assert torch.isfinite(out).all()
     assert float((out - 0.75).abs().max()) < 2e-3
     # a sample of sequences against the oracle (pages copied to the host)
-    import bench
     sample = [0, 1, 2, 17, 200]
-    oc, tables = bench.sample_to_oracle(a, case, sample)
+    oc, tables = oracle_copy(a, case, sample)
     lens = targets[sample].astype(np.int32)
     want = ko.decode_batch(oc, helpers.to_bits(q[sample]), tables, lens, mode=1, nthreads=8)
     got = out[sample].cpu().numpy()
     assert (np.abs(got - want) <= 1e-2 + 1e-2 * np.abs(want)).all()
+    # the same sample, bit for bit: the CPU oracle's token-by-token writer over the sequences' own K/V rows
+    # (regenerated from their positions) must leave the pages and live scratch rows the device holds
+    gen = torch.Generator(device=DEV)
+    gen.manual_seed(3)
+    base = torch.randn((4096, case.nkv, case.d), device=DEV, dtype=torch.float16, generator=gen)
+    ks, vs = [], []
+    for i in sample:
+        pos = (torch.arange(int(targets[i])) + (i << 20)).to(DEV)
+        k = base[(pos * 2654435761 % 4096)] * (1.0 + (pos % 13).to(torch.float16)[:, None, None] * 0.1)
+        ks.append(helpers.to_bits(k))
+        vs.append(helpers.to_bits(torch.full_like(k, 0.75)))
+    ref = ko.OracleCache(oc.geom, oc.num_blocks, oc.num_slots)
+    offs = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    ko.write_batch(ref, np.concatenate(ks), np.concatenate(vs), tables, np.zeros(len(sample), np.int32), offs, nthreads=8)
+    for i, t in enumerate(lens):
+        used = oc.geom.split_old(int(t)) // case.b
+        for name in ko.OracleCache.PAGE_FIELDS:
+            a_, b_ = getattr(oc, name)[tables[i, :used]], getattr(ref, name)[tables[i, :used]]
+            assert np.array_equal(a_, b_), f"sequence {sample[i]}: {name} differs from the oracle writer"
+        rows_live = int(t) - oc.geom.split_old(int(t))
+        assert np.array_equal(oc.k_scratch[i][:, :rows_live], ref.k_scratch[i][:, :rows_live])
+        assert np.array_equal(oc.v_scratch[i][:, :rows_live], ref.v_scratch[i][:, :rows_live])

@@ -254,6 +254,70 @@ def test_step_matches_oracle_across_quantisation(native_lib, batch):
     assert worst < 2e-2
 
 
+Q14B_LAYER = so.StepShape(layers=2, hidden=5120, nh=40, nkv=8, hd=128, ffn=13824, vocab=4096, rope_base=1000000.0,
+                          norm_eps=1e-6, attn_bias=True, block=16, group=128, residual=128)
+
+
+@pytest.mark.parametrize("batch", [1, 8])
+def test_step_at_the_qwen25_14b_layer_shape_across_an_age_out(native_lib, batch):
+    """Two layers of the full-model configuration's shape (hidden 5120, 40 query / 8 kv heads of 128, FFN 13824,
+    block 16 / group 128 / residual 128; a 4096-row vocabulary keeps the CPU side short), 250 tokens of
+    synthetic context written into both sides' caches, then 9 steps: the 6th makes the scratch full and quantises
+    the first key group. Batch 1 runs the fused GEMV kernels, batch 8 the tensor-core skinny GEMM and the
+    stand-alone element-wise kernels. Logits against the CPU step oracle fed the same tokens."""
+    from jacq_b200.runtime import DecodeRuntime
+    from tests.gpu_utils import DEV, f16_tensor
+    shape = Q14B_LAYER
+    w = so.random_weights(shape, 77)
+    start, steps = 250, 9
+    max_len = 512
+    per_seq = (max_len - shape.residual) // shape.group * shape.group // shape.block   # the runtime's table width
+    bt = _tables(batch, per_seq, 100 + batch)
+    oracle = so.StepOracle(shape, w, bt, batch * per_seq, gemv_threads=16)
+    rt = DecodeRuntime(_config(shape), _torch_weights(w), batch=batch, max_seq_len=max_len,
+                       device=DEV, block_tables=torch.from_numpy(bt))
+    rng = np.random.default_rng(5)
+    offs = np.arange(batch + 1, dtype=np.int32) * start
+    for l in range(shape.layers):
+        k = rng.standard_normal((batch * start, shape.nkv, shape.hd), dtype=np.float32)
+        k[:, :, :3] *= 10.0
+        k = k.astype(np.float16)
+        v = rng.standard_normal((batch * start, shape.nkv, shape.hd), dtype=np.float32).astype(np.float16)
+        ko.write_batch(oracle.caches[0][l], k, v, bt, np.zeros(batch, np.int32), offs, nthreads=8)
+        c = rt.caches[l]
+        c.set_block_tables(torch.from_numpy(bt))
+        c.write(f16_tensor(k), f16_tensor(v), torch.from_numpy(offs).to(DEV), max_new_per_seq=start, max_start_seq_len=0)
+    oracle.seq_lens[:] = start
+    rt.set_seq_lens([start] * batch)
+    tok = (np.arange(batch, dtype=np.int32) * 311 + 5) % shape.vocab
+    worst = 0.0
+    for i in range(steps):
+        want_tok, want_logits = oracle.step(tok)
+        got_tok = rt.step(torch.from_numpy(tok)).cpu().numpy()
+        got = rt.logits.float().cpu().numpy()
+        want = want_logits.astype(np.float32)
+        worst = max(worst, float(np.abs(got - want).max()))
+        np.testing.assert_allclose(got, want, rtol=2e-2, atol=2e-2, err_msg=f"step {i}")
+        top2 = np.sort(want, axis=1)[:, -2:]
+        clear = (top2[:, 1] - top2[:, 0]) > 0.05
+        assert np.array_equal(got_tok[clear], want_tok[clear])
+        tok = want_tok.astype(np.int32)
+    assert np.array_equal(rt.seq_lens.cpu().numpy(), np.full(batch, start + steps, np.int32))
+    # the quantised group and the live scratch rows of every layer, bit for bit
+    torch.cuda.synchronize()
+    geom = oracle.geom
+    live = [start + steps - geom.split_old(start + steps)] * batch
+    assert geom.split_old(start + steps) == shape.group
+    from tests import helpers
+    for l in range(shape.layers):
+        oc = oracle.caches[0][l]
+        used = np.unique(bt[:, : shape.group // shape.block])
+        for name in helpers.PAGE_FIELDS:
+            got_pages = helpers.to_bits(getattr(rt.caches[l].tensors, name))[used]
+            want_pages = getattr(oc, helpers.ORACLE_FIELD[name])[used]
+            assert np.array_equal(got_pages, want_pages), f"layer {l} {name}"
+
+
 def test_step_graph_replay_equals_eager(native_lib):
     from jacq_b200.runtime import DecodeRuntime
     from tests.gpu_utils import DEV
