@@ -23,7 +23,7 @@ NVCC_FLAGS = [
 
 
 # compile-time tunables that may be overridden from the environment when experimenting
-TUNABLES = ("KIVI_DECODE_WARPS", "KIVI_DECODE_CTAS", "KIVI_STAGE_BULK", "KIVI_SUB", "KIVI_QK_SPLIT", "KIVI_DECODE_TRACE")
+TUNABLES = ("KIVI_DECODE_WARPS", "KIVI_DECODE_CTAS", "KIVI_SUB", "KIVI_QK_SPLIT", "KIVI_DECODE_TRACE")
 
 
 def sources() -> list[Path]:

@@ -56,10 +56,6 @@ constexpr int kSubMax = KIVI_SUB;        // tokens per ring slot (never more tha
 constexpr int kBarBytes = 512;           // room for 64 mbarriers
 constexpr int kMaxSlotsPerWarp = 4;
 constexpr int kBarArrivals = 33;         // lane 0's expect_tx arrive + one cp.async arrive per lane
-#ifndef KIVI_STAGE_BULK
-#define KIVI_STAGE_BULK 0
-#endif
-constexpr bool kStageBulk = KIVI_STAGE_BULK != 0;   // code pages by cp.async.bulk (1) or by 16-byte cp.async (0)
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleSlack = 8.0f;    // log2 units
 
@@ -72,9 +68,8 @@ struct Cfg {
     static constexpr int NMMA = D / 16;        // MMAs per 16-token tile, QK^T and PV each
     static constexpr int SUB = G < kSubMax ? G : kSubMax;   // tokens per ring slot
     static constexpr int SUBS = G / SUB;       // ring slots per key group
-    static constexpr bool HALF = (VG == 32);   // a lane uses half a value word per channel group
-    static constexpr int UNITS = HALF ? HG : WPR / 8;   // value words per lane per token
-    static constexpr int MPU = HALF ? 2 : 4;   // PV MMAs fed by one unit
+    static constexpr int VCOLS = D / 32;       // 16-byte chunks (32 channels) per token row of value codes
+    static constexpr int VSW_SHIFT = VCOLS == 4 ? 1 : 2;   // token bits that swizzle the chunk column (see below)
     // slot layout (bytes)
     static constexpr int KC = 0;
     static constexpr int VC = KC + SUB * D / 2;
@@ -95,8 +90,9 @@ struct Cfg {
     static constexpr int Q_BYTES = KW * 32 * 16;       // permuted query fragments of all lanes
     static constexpr int STATE_FLOATS = 8 * D + 16;    // per warp: O[8][D], m[8], l[8]
     static_assert(G % SUB == 0, "a key group must be whole slots");
-    static_assert(UNITS == 1 || UNITS == 2 || UNITS == 4, "unexpected value-word count");
-    static_assert(NMMA == UNITS * MPU, "value MMA bookkeeping");
+    static_assert(VCOLS == 2 || VCOLS == 4, "value rows of 32 or 64 bytes");
+    static_assert(NMMA == 2 * VCOLS, "two PV MMAs per 32-channel chunk column");
+    static_assert(VG % 32 == 0, "a chunk column lies inside one value channel group");
 };
 
 #ifdef KIVI_DECODE_TRACE
@@ -229,7 +225,12 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
     // per-lane constants of the 16-byte copies. Page strides fit 32 bits, so page * stride + base
     // is one wide multiply-add.
     constexpr uint32_t SLOT_PAGE_BYTES = (B >= kSub ? kSub : B) * (D / 2);   // a page's share of a slot's codes
-    static_assert(kStageBulk || SLOT_PAGE_BYTES % 512 == 0, "cp.async staging moves 512 bytes per warp instruction");
+    static_assert(SLOT_PAGE_BYTES % 512 == 0, "cp.async staging moves 512 bytes per warp instruction");
+    // Value codes land swizzled: the 16-byte chunk column c of token s sits at column c ^ ((s >> VSW_SHIFT) & (VCOLS - 1)),
+    // so that the eight token rows of an ldmatrix block fall into eight different bank groups. A warp
+    // instruction copies 512 contiguous bytes (8 or 16 token rows starting at a multiple of that), which makes
+    // the swizzle a lane constant: lane = token * VCOLS + column and the token bits in question are lane bits 3+.
+    const uint32_t v_stage_off = (uint32_t)((lane & ~(C::VCOLS - 1)) | ((lane & (C::VCOLS - 1)) ^ ((lane >> 3) & (C::VCOLS - 1)))) * 16u;
     const uint32_t page_stride32 = (uint32_t)page_stride;
     const uint8_t* kc_lane = kc_head + lane * 16;
     const uint8_t* vc_lane = vc_head + lane * 16;
@@ -264,20 +265,12 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
             uint32_t pg[PB];
 #pragma unroll
             for (int j = 0; j < PB; ++j) pg[j] = (uint32_t)__shfl_sync(0xffffffffu, my_page, j);
-            if (lane == 0) mbar_expect_tx32(bar, kStageBulk ? (uint32_t)C::CODE_BYTES : 0u);
-            if constexpr (kStageBulk) {
-                if (lane == 0) {
-#pragma unroll
-                    for (int j = 0; j < PB; ++j) {
-                        const size_t off = (size_t)pg[j] * page_stride + (B > kSub ? (size_t)(tokbase & bmask) * (D / 2) : 0);
-                        bulk_g2s32(st + C::KC + j * SLOT_PAGE_BYTES, kc_head + off, SLOT_PAGE_BYTES, bar);
-                        bulk_g2s32(st + C::VC + j * SLOT_PAGE_BYTES, vc_head + off, SLOT_PAGE_BYTES, bar);
-                    }
-                }
-            } else {
+            if (lane == 0) mbar_expect_tx32(bar, 0u);
+            {
                 // each page's share of the slot is contiguous in both memories: lane l moves the
                 // 16-byte chunks l, l+32, ... of it, one cp.async warp instruction per 512 bytes
                 const uint32_t dst = st + (uint32_t)lane * 16u;
+                const uint32_t dstv = st + v_stage_off;
 #pragma unroll
                 for (int j = 0; j < PB; ++j) {
                     const uint8_t* ks = kc_lane + (size_t)pg[j] * page_stride32 + (B > kSub ? (size_t)(tokbase & bmask) * (D / 2) : 0);
@@ -285,7 +278,7 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
 #pragma unroll
                     for (int h = 0; h < (int)SLOT_PAGE_BYTES / 512; ++h) {
                         cp_async16_32(dst + C::KC + j * SLOT_PAGE_BYTES + h * 512, ks + h * 512);
-                        cp_async16_32(dst + C::VC + j * SLOT_PAGE_BYTES + h * 512, vs + h * 512);
+                        cp_async16_32(dstv + C::VC + j * SLOT_PAGE_BYTES + h * 512, vs + h * 512);
                     }
                 }
             }
@@ -378,13 +371,23 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
 
     // lane-constant byte offsets inside a slot
     const uint32_t k_off = C::KC + row_token(r) * (D / 2) + (D / 8) * t;
-    const uint32_t v_lane = C::HALF ? 4u * (r & 3) : 4u * r;
-    const uint32_t vA_off = C::VC + (2 * t + (t & 1)) * (D / 2) + v_lane;          // k-slots 2t, 2t+1 of this lane are
-    const uint32_t vB_off = C::VC + (2 * t + ((t & 1) ^ 1)) * (D / 2) + v_lane;    // tokens tA, tB (and +8 for 2t+8, 2t+9)
+    // ldmatrix.x4.trans over the swizzled value codes: lanes 0-7 / 8-15 / 16-23 / 24-31 address the token rows of
+    // the blocks (chunk column c, tokens 0-7), (c, tokens 8-15), (c+1, tokens 0-7), (c+1, tokens 8-15); block row
+    // rho is token row_token(rho), the order the probability tile comes out of the QK^T MMA in. Transposed, a
+    // lane holds the 16-bit words (4 channels 4r..4r+3 of the column) of tokens (2t, 2t+1) of each block --
+    // the A fragment of O^T += V^T P with no byte permute.
+    uint32_t v_ldm[C::VCOLS / 2];
+    {
+        const int blk = lane >> 3;
+        const int tok = row_token(lane & 7) + 8 * (blk & 1);
+#pragma unroll
+        for (int h2 = 0; h2 < C::VCOLS / 2; ++h2) {
+            const int col = (blk >> 1) + 2 * h2;
+            v_ldm[h2] = C::VC + tok * (D / 2) + ((col ^ ((tok >> C::VSW_SHIFT) & (C::VCOLS - 1))) * 16);
+        }
+    }
     const uint32_t vs_off = C::VS + row_token(r) * C::HG * 2;
     const uint32_t ks_off = C::KS + (D / 2) * t;
-    const uint32_t sel_lo = C::HALF ? ((r >> 2) ? 0x7632u : 0x5410u) : 0x5410u;
-    constexpr uint32_t UNIT_STEP = C::HALF ? 16u : 32u;      // bytes between the value words of two units
     constexpr uint32_t TILE_STEP = 16u * (D / 2);            // bytes between 16-token tiles of codes
 
     // ================= key groups of int4 pages =================
@@ -476,27 +479,20 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
                 }
 
                 // ---- PV: O^T[channel, head] += V^T[channel, token] P'[token, head] ----
+                // MMA 2c (2c+1) takes nibbles 0,1 (2,3) of chunk column c: row r is channel 32c + 4r (+2), row r+8 the next one
 #pragma unroll
-                for (int u = 0; u < C::UNITS; ++u) {
-                    const int cg = C::HALF ? u : (64 * u) / C::VG;
-                    const uint32_t va = st + vA_off + tile * TILE_STEP + u * UNIT_STEP;
-                    const uint32_t vb = st + vB_off + tile * TILE_STEP + u * UNIT_STEP;
-                    const uint32_t wA = lds32(va), wB = lds32(vb);
-                    const uint32_t wA8 = lds32(va + 8 * (D / 2)), wB8 = lds32(vb + 8 * (D / 2));
-                    {
-                        const uint32_t xl = __byte_perm(wA, wB, sel_lo), xh = __byte_perm(wA8, wB8, sel_lo);
+                for (int h2 = 0; h2 < C::VCOLS / 2; ++h2) {
+                    uint32_t x[4];
+                    ldmatrix_x4_trans_32(x, st + v_ldm[h2] + tile * TILE_STEP);
+#pragma unroll
+                    for (int cc = 0; cc < 2; ++cc) {
+                        const int col = 2 * h2 + cc;
+                        const int cg = (32 * col) / C::VG;
+                        const uint32_t xl = x[2 * cc], xh = x[2 * cc + 1];
                         const uint32_t xl8 = shr8(xl), xh8 = shr8(xh);
-                        mma16816(o[u * C::MPU + 0], xl & 0x000f000fu, xl & 0x00f000f0u, xh & 0x000f000fu,
+                        mma16816(o[2 * col + 0], xl & 0x000f000fu, xl & 0x00f000f0u, xh & 0x000f000fu,
                                  xh & 0x00f000f0u, pb01[cg], pb23[cg]);
-                        mma16816(o[u * C::MPU + 1], xl8 & 0x000f000fu, xl8 & 0x00f000f0u, xh8 & 0x000f000fu,
-                                 xh8 & 0x00f000f0u, pb01[cg], pb23[cg]);
-                    }
-                    if constexpr (!C::HALF) {
-                        const uint32_t xl = __byte_perm(wA, wB, 0x7632), xh = __byte_perm(wA8, wB8, 0x7632);
-                        const uint32_t xl8 = shr8(xl), xh8 = shr8(xh);
-                        mma16816(o[u * C::MPU + 2], xl & 0x000f000fu, xl & 0x00f000f0u, xh & 0x000f000fu,
-                                 xh & 0x00f000f0u, pb01[cg], pb23[cg]);
-                        mma16816(o[u * C::MPU + 3], xl8 & 0x000f000fu, xl8 & 0x00f000f0u, xh8 & 0x000f000fu,
+                        mma16816(o[2 * col + 1], xl8 & 0x000f000fu, xl8 & 0x00f000f0u, xh8 & 0x000f000fu,
                                  xh8 & 0x00f000f0u, pb01[cg], pb23[cg]);
                     }
                 }
@@ -558,25 +554,19 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
             const uint32_t pb23 = movmatrix_trans(pack_half2(sc[2], sc[3]));
             const bool vA = tA < rows, vB = tB < rows, vA8 = tA + 8 < rows, vB8 = tB + 8 < rows;
 #pragma unroll
-            for (int u = 0; u < C::UNITS; ++u) {
-                // same channel-to-row assignment as the int4 path: rows (r, r+8) of MMA q are
+            for (int col = 0; col < C::VCOLS; ++col) {
+                // same channel-to-row assignment as the int4 path: rows (r, r+8) of MMA 2col + q are
                 // channels (c0 + 2q, c0 + 2q + 1)
-                const int c0 = C::HALF ? (C::VG * u + 8 * (r & 3) + 4 * (r >> 2)) : (64 * u + 8 * r);
-                uint32_t xa[C::MPU], xb[C::MPU], xa8[C::MPU], xb8[C::MPU];
-                auto load = [&](int tok, bool on, uint32_t (&x)[C::MPU]) {
-                    if constexpr (C::HALF) {
-                        const uint2 v = lds64(stv + tok * C::RES_STRIDE + c0 * 2);
-                        x[0] = on ? v.x : 0u; x[1] = on ? v.y : 0u;
-                    } else {
-                        const uint4 v = lds128(stv + tok * C::RES_STRIDE + c0 * 2);
-                        x[0] = on ? v.x : 0u; x[1] = on ? v.y : 0u; x[2] = on ? v.z : 0u; x[3] = on ? v.w : 0u;
-                    }
+                const int c0 = 32 * col + 4 * r;
+                auto load = [&](int tok, bool on) {
+                    const uint2 v = lds64(stv + tok * C::RES_STRIDE + c0 * 2);
+                    return on ? v : make_uint2(0u, 0u);
                 };
-                load(tA, vA, xa); load(tB, vB, xb); load(tA + 8, vA8, xa8); load(tB + 8, vB8, xb8);
-#pragma unroll
-                for (int q = 0; q < C::MPU; ++q)
-                    mma16816(o[u * C::MPU + q], __byte_perm(xa[q], xb[q], 0x5410), __byte_perm(xa[q], xb[q], 0x7632),
-                             __byte_perm(xa8[q], xb8[q], 0x5410), __byte_perm(xa8[q], xb8[q], 0x7632), pb01, pb23);
+                const uint2 xa = load(tA, vA), xb = load(tB, vB), xa8 = load(tA + 8, vA8), xb8 = load(tB + 8, vB8);
+                mma16816(o[2 * col + 0], __byte_perm(xa.x, xb.x, 0x5410), __byte_perm(xa.x, xb.x, 0x7632),
+                         __byte_perm(xa8.x, xb8.x, 0x5410), __byte_perm(xa8.x, xb8.x, 0x7632), pb01, pb23);
+                mma16816(o[2 * col + 1], __byte_perm(xa.y, xb.y, 0x5410), __byte_perm(xa.y, xb.y, 0x7632),
+                         __byte_perm(xa8.y, xb8.y, 0x5410), __byte_perm(xa8.y, xb8.y, 0x7632), pb01, pb23);
             }
             __syncwarp();
             issue_next();
@@ -602,16 +592,16 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
     __syncthreads();  // every slot has been consumed: the ring can hold the warp states
     float* state = reinterpret_cast<float*>(ring) + (size_t)warp * C::STATE_FLOATS;
 #pragma unroll
-    for (int u = 0; u < C::UNITS; ++u) {
-        const int c0 = C::HALF ? (C::VG * u + 8 * (r & 3) + 4 * (r >> 2)) : (64 * u + 8 * r);
-        const int cg = C::HALF ? u : (64 * u) / C::VG;
+    for (int col = 0; col < C::VCOLS; ++col) {
+        const int cg = (32 * col) / C::VG;
 #pragma unroll
-        for (int q = 0; q < C::MPU; ++q) {
-            const float* acc = o[u * C::MPU + q];
-            state[(2 * t) * D + c0 + 2 * q] = acc[0] + zacc[cg][0];
-            state[(2 * t + 1) * D + c0 + 2 * q] = acc[1] + zacc[cg][1];
-            state[(2 * t) * D + c0 + 2 * q + 1] = acc[2] + zacc[cg][0];
-            state[(2 * t + 1) * D + c0 + 2 * q + 1] = acc[3] + zacc[cg][1];
+        for (int q = 0; q < 2; ++q) {
+            const int ch = 32 * col + 4 * r + 2 * q;
+            const float* acc = o[2 * col + q];
+            state[(2 * t) * D + ch] = acc[0] + zacc[cg][0];
+            state[(2 * t + 1) * D + ch] = acc[1] + zacc[cg][1];
+            state[(2 * t) * D + ch + 1] = acc[2] + zacc[cg][0];
+            state[(2 * t + 1) * D + ch + 1] = acc[3] + zacc[cg][1];
         }
     }
     if (r == 0) {

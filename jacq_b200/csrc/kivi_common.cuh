@@ -234,6 +234,11 @@ __device__ __forceinline__ void ldmatrix_x4_32(uint32_t (&r)[4], uint32_t a) {
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
 }
 
+__device__ __forceinline__ void ldmatrix_x4_trans_32(uint32_t (&r)[4], uint32_t a) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+
 // Programmatic dependent launch: a kernel launched with the stream-serialisation attribute may start
 // while its predecessor drains; it must call pdl_wait() before touching anything the predecessor
 // wrote -- in EVERY CTA, also one that has nothing to do: the kernel after it waits only for this grid, and
