@@ -161,23 +161,73 @@ def cpu_baseline(cache, q, case, context, nthreads, target_seconds=12.0):
 # clocks
 
 class ClockSampler:
-    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap")
+    """SM clock, power and throttle reasons of one GPU, read through NVML from a thread about every
+    millisecond while a timed region runs (reading only; nothing is set). A timed region of a few
+    milliseconds still gets several samples, which `nvidia-smi -lms` (100 ms at best) would not give;
+    where NVML cannot be loaded the sampler falls back to nvidia-smi."""
+    SMI_FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+                  "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+                  "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index):
-        self.proc = None
         self.gpu_index = gpu_index
+        self.samples, self.thread, self.proc, self.stop_flag = [], None, None, None
+        self.nvml = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(gpu_index)
+            self.nvml = pynvml
+        except Exception:   # noqa: BLE001 - any failure means "no NVML here"
+            self.nvml = None
+
+    def _loop(self):
+        n = self.nvml
+        while not self.stop_flag.is_set():
+            try:
+                self.samples.append((n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM),
+                                     n.nvmlDeviceGetPowerUsage(self.handle) / 1000.0,
+                                     n.nvmlDeviceGetCurrentClocksEventReasons(self.handle)))
+            except Exception:   # noqa: BLE001
+                break
+            time.sleep(0.0005)
 
     def start(self):
+        if self.nvml is not None:
+            import threading
+            self.samples = []
+            self.stop_flag = threading.Event()
+            self.thread = threading.Thread(target=self._loop, daemon=True)
+            self.thread.start()
+            return
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(self.gpu_index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                ["nvidia-smi", "-i", str(self.gpu_index), f"--query-gpu={self.SMI_FIELDS}", "--format=csv,noheader,nounits",
                  "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
 
     def stop(self):
+        if self.nvml is not None:
+            n = self.nvml
+            self.stop_flag.set()
+            self.thread.join(timeout=2)
+            if not self.samples:
+                return {"sm_mhz": None, "sm_max_mhz": None, "samples": 0, "reasons": ["no NVML sample"]}
+            bits = 0
+            for _, _, r in self.samples:
+                bits |= r
+            names = (("hw_slowdown", n.nvmlClocksEventReasonHwSlowdown), ("hw_thermal_slowdown", n.nvmlClocksEventReasonHwThermalSlowdown),
+                     ("sw_thermal_slowdown", n.nvmlClocksEventReasonSwThermalSlowdown), ("sw_power_cap", n.nvmlClocksEventReasonSwPowerCap),
+                     ("hw_power_brake_slowdown", n.nvmlClocksEventReasonHwPowerBrakeSlowdown))
+            try:
+                mx = n.nvmlDeviceGetMaxClockInfo(self.handle, n.NVML_CLOCK_SM)
+            except Exception:   # noqa: BLE001
+                mx = None
+            return {"sm_mhz": statistics.median(s[0] for s in self.samples), "sm_min_mhz": min(s[0] for s in self.samples),
+                    "sm_max_mhz": mx, "power_w_max": max(s[1] for s in self.samples), "samples": len(self.samples),
+                    "source": "NVML, one sample per ~0.6 ms during the timed region",
+                    "reasons": [name for name, bit in names if bits & bit]}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -201,10 +251,66 @@ class ClockSampler:
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "source": "nvidia-smi -lms 100", "reasons": sorted(reasons)}
 
 
 # ------------------------------------------------------------------------------------------------
+
+def _max_over_ranks(value, device, world):
+    import torch
+    import torch.distributed as dist
+    if world == 1:
+        return float(value)
+    t = torch.tensor([float(value)], device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def time_decode(cache, q, out, context, steps, warmup, device, rank, world, local_rank, sample_clocks=True):
+    """W warm-up launches, then exactly K timed decode launches between a barrier + synchronize on both sides;
+    CUDA events on the launching stream (one pair around the K steps, one event after every step). Returns
+    (ms of the K steps on this rank, per-step ms, clocks sampled during the K steps on rank 0)."""
+    import torch
+    import torch.distributed as dist
+    for _ in range(max(3, warmup)):
+        cache.decode(q, out, max_seq_len=context)
+    torch.cuda.synchronize(device)
+    sampler = ClockSampler(local_rank) if (rank == 0 and sample_clocks) else None
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(device)
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    if sampler:
+        sampler.start()
+    marks[0].record()
+    for k in range(steps):
+        cache.decode(q, out, max_seq_len=context)
+        marks[k + 1].record()
+    torch.cuda.synchronize(device)
+    clocks = sampler.stop() if sampler else None
+    if world > 1:
+        dist.barrier()
+    per_step = [marks[k].elapsed_time(marks[k + 1]) for k in range(steps)]
+    return marks[0].elapsed_time(marks[steps]), per_step, clocks
+
+
+def sustained_decode(cache, q, out, context, device, local_rank, seconds=1.0):
+    """The same launch back to back for about a second: what the kernel sustains once the GPU sits at its power
+    limit (the SM clock drops), reported beside the K-step figure with the clocks seen."""
+    import torch
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    t0, ms = time.perf_counter(), []
+    while time.perf_counter() - t0 < seconds:
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(41)]
+        marks[0].record()
+        for k in range(40):
+            cache.decode(q, out, max_seq_len=context)
+            marks[k + 1].record()
+        torch.cuda.synchronize(device)
+        ms = [marks[k].elapsed_time(marks[k + 1]) for k in range(40)]
+    return statistics.mean(ms), sampler.stop()
+
 
 def run_b200(args):
     import torch
@@ -215,6 +321,8 @@ def run_b200(args):
 
     rank, local_rank, world = _dist_env()
     if world > 1:
+        # the tensor-parallel part below runs its own peer-memory kernels beside NCCL: keep NVLink multicast out of it
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
     device = torch.device(f"cuda:{local_rank}")
     torch.cuda.set_device(device)
@@ -223,7 +331,8 @@ def run_b200(args):
     case = helpers.CONFIGS[key]
     lay = helpers.layout_of(case)
     e2e_steps = args.steps
-    cache, q, writer = build_cache(case, batch, context, device, spare_tokens=e2e_steps + args.warmup + 8,
+    warm = max(3, args.warmup)
+    cache, q, writer = build_cache(case, batch, context, device, spare_tokens=e2e_steps + warm + 8,
                                    seed=20261125 + rank)
     out = torch.empty((batch, case.nh, case.d), dtype=torch.float32, device=device)
     step_bytes = lay.decode_algorithmic_bytes(context) * batch
@@ -238,39 +347,17 @@ def run_b200(args):
         return
 
     # ---- kernel-resident measurement: `value` and `roofline` --------------------------------
-    for _ in range(max(3, args.warmup)):
-        cache.decode(q, out, max_seq_len=context)
-    torch.cuda.synchronize(device)
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-        time.sleep(0.3)
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize(device)
-    events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    # keep the GPU busy long enough for clock samples: repeat the K timed steps in rounds
-    rounds = max(1, int(0.6 / max(1e-4, args.steps * 4e-4)))
-    per_step_ms = []
-    for rnd in range(rounds):
-        for e0, e1 in events:
-            e0.record()
-            cache.decode(q, out, max_seq_len=context)
-            e1.record()
-        torch.cuda.synchronize(device)
-        if rnd == rounds - 1:
-            per_step_ms = [e0.elapsed_time(e1) for e0, e1 in events]
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize(device)
-    clocks = sampler.stop() if rank == 0 else None
-    total_ms = float(sum(per_step_ms))
-    if world > 1:
-        t = torch.tensor([total_ms], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms = float(t.item())
+    total_ms, per_step_ms, clocks = time_decode(cache, q, out, context, args.steps, args.warmup, device, rank, world,
+                                                local_rank)
+    total_ms = _max_over_ranks(total_ms, device, world)
     ms_per_step = total_ms / args.steps
     value = step_bytes * world / (ms_per_step * 1e-3) / 1e9
+    plan = (ctypes_plan(cache, batch, context))
+    sustained = None
+    if rank == 0 and world == 1:
+        sus_ms, sus_clocks = sustained_decode(cache, q, out, context, device, local_rank)
+        sustained = {"value": step_bytes / (sus_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": sus_ms,
+                     "what": "the same launch back to back for 1 s (power-limited steady state)", "clocks": sus_clocks}
 
     # ---- CPU baseline on a bounded sample (rank 0, one GPU only); doubles as a parity check ------
     base, parity = None, None
@@ -280,33 +367,129 @@ def run_b200(args):
         got = out[:n].cpu().numpy()
         err = float(np.abs(got - want).max())
         parity = {"sequences": n, "max_abs_err": err, "within_1e-2": bool((np.abs(got - want) <= 1e-2 + 1e-2 * np.abs(want)).all())}
+        single = cpu_baseline(cache, q, case, context, 1, target_seconds=6.0)[0]
+        base["single_thread"] = {"value": single["value"], "unit": "GB/s", "sample": single["sample"]}
 
     # ---- end to end through the public API with host buffers ---------------------------------
+    e2e = measure_e2e(args, cache, q, case, lay, batch, context, device, rank, world, warm)
+
+    strong = tp = secondary = None
+    if world > 1:
+        strong = measure_strong_scaling(args, cache, q, out, case, lay, batch, context, device, rank, world, local_rank)
+    del cache, q, out
+    torch.cuda.empty_cache()
+    if world > 1 and args.extras:
+        tp = measure_tp_step(args, device, rank, local_rank, world)
+    if world == 1 and args.extras:
+        secondary = measure_secondary(args, device)
+
+    if rank == 0:
+        peak, peak_kind = _peaks()
+        kernel_ms = statistics.mean(per_step_ms)
+        achieved = step_bytes / (kernel_ms * 1e-3) / 1e9
+        # DRAM bytes per launch: one ncu capture of this kernel on 48 sequences of the same shape read 446.99 MB and
+        # wrote 3.93 MB against 447.58 MB of algorithmic bytes; traffic grows with the sequences, so that ratio is
+        # applied to this launch
+        traffic, traffic_source = None, None
+        if key == "mistral7b" and context == 8192:
+            traffic = step_bytes * TRAFFIC_RATIO_B48
+            traffic_source = "ncu dram__bytes_read+write of a 48-sequence launch, scaled by sequences"
+        line = {
+            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": warm, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "u4 codes, f16 params/residual, f32 accumulate", "data": "synthetic",
+            "config": {"workload": args.workload, "geometry": {"nh": case.nh, "nkv": case.nkv, "head_dim": case.d,
+                                                                "block": case.b, "group": case.g, "residual": case.r},
+                       "batch_per_gpu": batch, "context": context, "algorithmic_bytes_per_step_per_gpu": step_bytes,
+                       "l2": "inputs (1.49 GB of pages per GPU) exceed the 126 MB L2; no flush between iterations",
+                       "timing": "W warm-up launches, then K launches timed once with CUDA events between barriers; "
+                                 "`sustained` repeats the launch for a second",
+                       "launch_plan": plan,
+                       "parallelism": f"sequences sharded over {world} GPU(s), no collective"},
+            "tokens_per_s": batch * world / (ms_per_step * 1e-3),
+            "pct_of_8TBs_nominal": 100.0 * value / world / 8000.0,
+            "e2e": e2e,
+            "gpu_launches": args.steps * (2 if plan["cut_units"] else 1),
+            "clocks": clocks,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": traffic, "traffic_source": traffic_source, "peak_source": f"{peak_kind} HBM copy bandwidth",
+                         "kernel": "decode_mma_kernel", "ms_per_launch": kernel_ms},
+            "sustained": sustained,
+            "writer": writer,
+            "cpu_baseline": base,
+            "parity_vs_cpu_port": parity,
+        }
+        if strong is not None:
+            line["strong"] = strong
+        if tp is not None:
+            line["tp_step"] = tp
+        if secondary is not None:
+            line["secondary"] = secondary
+        print(json.dumps(line))
+        sys.stdout.flush()
+    if world > 1:
+        # no destroy_process_group(): with NCCL collectives inside a captured graph it can block for minutes
+        dist.barrier()
+        torch.cuda.synchronize(device)
+        sys.stdout.flush()
+        os._exit(0)
+
+
+# DRAM bytes over algorithmic bytes of decode_mma_kernel, from the ncu capture of the 48-sequence case
+TRAFFIC_RATIO_B48 = (446.99 + 3.93) / 447.58
+
+
+def ctypes_plan(cache, batch, context):
+    """The launch plan the library reports for this batch (kivi_b200_decode_plan)."""
+    import ctypes
+    from jacq_b200 import _native
+    out = (ctypes.c_int32 * 4)()
+    _native.check(_native.lib().kivi_b200_decode_plan(ctypes.byref(cache._geom), batch, context, out), "kivi_b200_decode_plan")
+    u1, k1, u2, k2 = (int(v) for v in out)
+    return {"whole_units": u1 if k1 == 1 else 0, "units_cut": [[u1, k1]] * (k1 > 1) + [[u2, k2]] * (k2 > 1),
+            "cut_units": (u1 if k1 > 1 else 0) + (u2 if k2 > 1 else 0), "jobs": u1 * k1 + u2 * k2}
+
+
+def measure_e2e(args, cache, q, case, lay, batch, context, device, rank, world, warm):
+    """One serving step through the public API (KiviCache.write / .decode) with HOST buffers, every step: pinned q,
+    the step's new K/V rows and the sequence lengths (host-side metadata, as a serving engine keeps them) copied
+    host->device, cache write of one token per sequence, decode with fp16 output, output copied device->host.
+    The step is captured once as a CUDA graph and launched once per step (--no-e2e-graph: separate calls); the
+    last output is checked against a separate decode of the same cache state."""
+    import torch
+    import torch.distributed as dist
+    e2e_steps = args.steps
+    out16 = torch.empty((batch, case.nh, case.d), dtype=torch.float16, device=device)
     q_host = q.cpu().pin_memory()
-    out_host = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+    out_host = torch.empty(out16.shape, dtype=out16.dtype).pin_memory()
     gen = torch.Generator().manual_seed(7 + rank)
     nk_host = torch.randn((batch, case.nkv, case.d), generator=gen).to(torch.float16).pin_memory()
     nv_host = torch.randn((batch, case.nkv, case.d), generator=gen).to(torch.float16).pin_memory()
+    lens_host = torch.empty((2, batch), dtype=torch.int32).pin_memory()      # row 0: before the write, row 1: after
     q_dev, nk_dev, nv_dev = torch.empty_like(q), torch.empty_like(nk_host, device=device), torch.empty_like(nv_host, device=device)
+    lens_dev = torch.empty((2, batch), dtype=torch.int32, device=device)
     offs = torch.arange(batch + 1, device=device, dtype=torch.int32)
-    cur = context
-
-    # One serving step as the serving engine replays it: copies in, append, attention, copy out, captured once as a
-    # CUDA graph (the bounds the launch plan needs are those of the last step of the run) and launched once per
-    # step. --no-e2e-graph, or a failed capture, issues the same calls one by one.
-    bound = context + e2e_steps + max(3, args.warmup) + 4
+    state = {"len": context}
+    # the bounds the launch plan needs are those of the last step of the run
+    bound = context + e2e_steps + warm + 4
 
     def enqueue_step():
         q_dev.copy_(q_host, non_blocking=True)
         nk_dev.copy_(nk_host, non_blocking=True)
         nv_dev.copy_(nv_host, non_blocking=True)
-        cache.write(nk_dev, nv_dev, offs, max_new_per_seq=1, max_start_seq_len=bound)
-        cache.decode(q_dev, out, max_seq_len=bound + 1)
-        out_host.copy_(out, non_blocking=True)
+        lens_dev.copy_(lens_host, non_blocking=True)
+        cache.write(nk_dev, nv_dev, offs, max_new_per_seq=1, max_start_seq_len=bound, start_seq_lens=lens_dev[0], advance=False)
+        cache.decode(q_dev, out16, max_seq_len=bound + 1, seq_lens=lens_dev[1])
+        out_host.copy_(out16, non_blocking=True)
 
+    def set_lens():
+        lens_host[0].fill_(state["len"])
+        lens_host[1].fill_(state["len"] + 1)
+
+    set_lens()
     enqueue_step()   # once eagerly: every buffer the calls allocate lazily exists before a capture
     torch.cuda.synchronize(device)
-    cur += 1
+    state["len"] += 1
     graph = None
     if args.e2e_graph:
         try:
@@ -319,15 +502,16 @@ def run_b200(args):
             torch.cuda.synchronize(device)
 
     def serving_step():
+        set_lens()
         if graph is not None:
             graph.replay()
         else:
             enqueue_step()
         torch.cuda.synchronize(device)
+        state["len"] += 1
 
-    for _ in range(max(3, args.warmup)):
+    for _ in range(warm):
         serving_step()
-        cur += 1
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize(device)
@@ -335,63 +519,38 @@ def run_b200(args):
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
         serving_step()
-        cur += 1
-        e2e_bytes += lay.decode_algorithmic_bytes(cur) * batch
+        e2e_bytes += lay.decode_algorithmic_bytes(state["len"]) * batch
     e2e_s = time.perf_counter() - t0
     # what the last replay copied out is what a separate decode call computes from the same cache state
-    check = cache.decode(q_dev, max_seq_len=bound + 1)
+    cache.seq_lens.fill_(state["len"])
+    check = torch.empty_like(out16)
+    cache.decode(q_dev, check, max_seq_len=bound + 1)
     torch.cuda.synchronize(device)
     if not torch.equal(check.cpu(), out_host):
         raise RuntimeError("bench: the end-to-end step's output differs from a decode of the same cache state")
-    if world > 1:
-        t = torch.tensor([e2e_s], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
-    e2e_value = e2e_bytes * world / e2e_s / 1e9
-    h2d = q_host.numel() * 2 + nk_host.numel() * 2 * 2
-    d2h = out_host.numel() * 4
+    e2e_s = _max_over_ranks(e2e_s, device, world)
+    h2d = q_host.numel() * 2 + nk_host.numel() * 2 * 2 + lens_host.numel() * 4
+    d2h = out_host.numel() * 2
+    return {"value": e2e_bytes * world / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+            "ms_per_step": e2e_s / e2e_steps * 1e3, "tokens_per_s": batch * world / (e2e_s / e2e_steps),
+            "what": "pinned q + new K/V rows + sequence lengths H2D, cache write (1 token/sequence), decode (fp16 out), O D2H"
+                    + ("; one CUDA graph launch per step" if graph is not None else "; eager calls")}
 
-    if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return
-    peak, peak_kind = _peaks()
-    kernel_ms = statistics.mean(per_step_ms)
-    achieved = step_bytes / (kernel_ms * 1e-3) / 1e9
-    # DRAM bytes per launch: one ncu capture of this kernel on 48 sequences of the same shape read 446.99 MB and
-    # wrote 3.93 MB against 447.58 MB of algorithmic bytes; traffic grows with the sequences, so that ratio is
-    # applied to this launch (profiles/decode_mma_kernel_mistral7b_b48_t8192.md)
-    traffic, traffic_source = None, None
-    if key == "mistral7b" and context == 8192:
-        traffic = step_bytes * (446.99 + 3.93) / 447.58
-        traffic_source = "ncu dram__bytes_read+write of a 48-sequence launch, scaled by sequences"
-    line = {
-        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
-        "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "u4 codes, f16 params/residual, f32 accumulate", "data": "synthetic",
-        "config": {"workload": args.workload, "geometry": {"nh": case.nh, "nkv": case.nkv, "head_dim": case.d,
-                                                            "block": case.b, "group": case.g, "residual": case.r},
-                   "batch_per_gpu": batch, "context": context, "algorithmic_bytes_per_step_per_gpu": step_bytes,
-                   "l2": "inputs (1.49 GB of pages per GPU) exceed the 126 MB L2; no flush between iterations",
-                   "parallelism": f"sequences sharded over {world} GPU(s), no collective"},
-        "tokens_per_s": batch * world / (ms_per_step * 1e-3),
-        "pct_of_8TBs_nominal": 100.0 * value / world / 8000.0,
-        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": e2e_s / e2e_steps * 1e3, "tokens_per_s": batch * world / (e2e_s / e2e_steps),
-                "what": "pinned q + new K/V rows H2D, cache write (1 token/sequence), decode, O D2H"
-                        + ("; one CUDA graph launch per step" if graph is not None else "; eager calls")},
-        "gpu_launches": args.steps,
-        "clocks": clocks,
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": traffic, "traffic_source": traffic_source, "peak_source": f"{peak_kind} HBM copy bandwidth",
-                     "kernel": "decode_mma_kernel", "ms_per_launch": kernel_ms},
-        "writer": writer,
-    }
-    line["cpu_baseline"] = base
-    line["parity_vs_cpu_port"] = parity
-    if world > 1:
-        dist.destroy_process_group()
-    print(json.dumps(line))
+
+def measure_strong_scaling(args, cache, q, out, case, lay, batch, context, device, rank, world, local_rank):
+    """Strong scaling of the same workload: the `batch` sequences of ONE GPU's workload split over the ranks
+    (contiguous shares of equal size; jacq_b200.sharding does the byte-balanced split for ragged batches), each
+    rank decoding its share of its own cache. value = bytes of the whole batch / slowest rank's time."""
+    from jacq_b200 import sharding
+    n = len(sharding.contiguous_shards(batch, world)[rank])
+    total_ms, per_step, _ = time_decode(cache, q[:n], out[:n], context, args.steps, args.warmup, device, rank, world,
+                                        local_rank, sample_clocks=False)
+    total_ms = _max_over_ranks(total_ms, device, world)
+    ms = total_ms / args.steps
+    value = lay.decode_algorithmic_bytes(context) * batch / (ms * 1e-3) / 1e9
+    return {"value": value, "unit": "GB/s", "ms_per_step": ms, "sequences_total": batch, "sequences_per_gpu": n,
+            "tokens_per_s": batch / (ms * 1e-3), "launch_plan": ctypes_plan(cache, n, context),
+            "what": f"{batch} sequences x {context} tokens in total, split over {world} GPUs; no collective"}
 
 
 def _timed_steps(fn, steps, warmup, device):
@@ -410,86 +569,178 @@ def _timed_steps(fn, steps, warmup, device):
     return ms
 
 
-def run_secondary(args):
-    """GEMV and cache-writer workloads: one GPU, value = algorithmic bytes / CUDA-event time."""
+def measure_gemv(gbatch, steps, warmup, device):
+    """One step = the four projections (qkv, o, gate_up, down) of 8 layers of the Qwen2.5-14B shape for `gbatch`
+    sequences, every GEMV on its own weights: 4.4 GB of fp16 weights streamed once per step."""
+    import ctypes
+    import torch
+    from jacq_b200 import _native
+    peak, peak_kind = _peaks()
+    hidden, ffn, qkv = 5120, 13824, 7168
+    shapes = [(qkv, hidden), (hidden, hidden), (2 * ffn, hidden), (hidden, ffn)]
+    layers = 8
+    gen = torch.Generator(device=device).manual_seed(11)
+    weights = [[(torch.randn((o, i), device=device, dtype=torch.float16, generator=gen) * 0.02) for o, i in shapes]
+               for _ in range(layers)]
+    xs = {i: torch.randn((gbatch, i), device=device, dtype=torch.float16, generator=gen) for i in (hidden, ffn)}
+    ys = [[torch.empty((gbatch, o), device=device, dtype=torch.float16) for o, _ in shapes] for _ in range(layers)]
+    lib = _native.lib()
+    stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+    def step():
+        for lw, ly in zip(weights, ys):
+            for w, y in zip(lw, ly):
+                rc = lib.kivi_b200_gemv_f16(w.data_ptr(), xs[w.shape[1]].data_ptr(), y.data_ptr(), None,
+                                            w.shape[0], w.shape[1], gbatch, stream)
+                assert rc == 0
+    step_bytes = layers * sum(o * i * 2 + gbatch * (o + i) * 2 for o, i in shapes)
+    ms = statistics.mean(_timed_steps(step, steps, warmup, device))
+    value = step_bytes / (ms * 1e-3) / 1e9
+    kernel = "gemv_kernel" if gbatch <= 4 else "umma_tma_gemm_kernel (tcgen05)"
+    return {"metric": "fp16 GEMV achieved HBM GB/s", "value": value, "unit": "GB/s", "ms_per_step": ms,
+            "config": {"workload": f"gemv_qwen25_14b_8layers_b{gbatch}", "algorithmic_bytes_per_step": step_bytes,
+                       "shapes_out_in": shapes, "layers": layers, "batch": gbatch, "l2": "working set exceeds the 126 MB L2"},
+            "gpu_launches": layers * len(shapes) * steps,
+            "roofline": {"bound": "hbm", "achieved": value, "peak": peak, "unit": "GB/s", "frac": value / peak,
+                         "traffic": None, "peak_source": f"{peak_kind} HBM copy bandwidth", "kernel": kernel}}
+
+
+def measure_writer(steps, warmup, device):
+    """One step = one 512-token chunk appended to each of 128 sequences (Mistral-7B shape): every sequence ages
+    out four key groups."""
     import torch
     from tests import helpers
+    from jacq_b200.cache import KiviCache
+    peak, peak_kind = _peaks()
+    case = helpers.CONFIGS["mistral7b"]
+    lay = helpers.layout_of(case)
+    batch, chunk, start = 128, 512, 512
+    pages = lay.old_pages(start + chunk * (steps + max(3, warmup) + 1)) + 1
+    cache = KiviCache(lay, batch * pages, batch, pages, device)
+    gen = torch.Generator(device=device).manual_seed(5)
+    cache.set_block_tables(torch.randperm(batch * pages, device=device, generator=gen).to(torch.int32)
+                           .reshape(batch, pages))
+    k = torch.randn((batch * chunk, case.nkv, case.d), device=device, dtype=torch.float16, generator=gen)
+    v = torch.randn((batch * chunk, case.nkv, case.d), device=device, dtype=torch.float16, generator=gen)
+    offs = torch.arange(batch + 1, device=device, dtype=torch.int32) * chunk
+    state = {"len": 0}
+
+    def step():
+        cache.write(k, v, offs, max_new_per_seq=chunk, max_start_seq_len=state["len"])
+        state["len"] += chunk
+    step()   # from empty: afterwards every step ages out exactly chunk / group groups per sequence
+    g, d, nkv, r, hg = case.g, case.d, case.nkv, case.r, lay.hd_groups
+    groups = chunk // g
+    per_head = (2 * chunk * d * 2                      # new K and V rows read (by the pack or the append)
+                + groups * (g * d + (g // case.b) * d * 4 + g * hg * 4)   # codes, key params per page, value params
+                + 2 * 2 * r * d * 2)                   # rows that stay fp16: read once, written once, K and V
+    step_bytes = batch * nkv * per_head
+    ms = statistics.mean(_timed_steps(step, steps, warmup, device))
+    value = step_bytes / (ms * 1e-3) / 1e9
+    return {"metric": "KIVI cache-writer achieved HBM GB/s", "value": value, "unit": "GB/s", "ms_per_step": ms,
+            "config": {"workload": "writer_mistral7b_b128_chunk512", "algorithmic_bytes_per_step": step_bytes, "batch": batch,
+                       "chunk_tokens": chunk, "tokens_per_s": batch * chunk / (ms * 1e-3),
+                       "l2": "working set exceeds the 126 MB L2"},
+            "gpu_launches": 2 * steps,
+            "roofline": {"bound": "hbm", "achieved": value, "peak": peak, "unit": "GB/s", "frac": value / peak,
+                         "traffic": None, "peak_source": f"{peak_kind} HBM copy bandwidth",
+                         "kernel": "pack_groups_kernel + scratch_update_kernel"}}
+
+
+def measure_decode_config(name, steps, warmup, device):
+    """Decode attention at one of the other attention-only configurations: K timed launches, CUDA events."""
+    import torch
+    from tests import helpers
+    peak, peak_kind = _peaks()
+    key, batch, context = WORKLOADS[name]
+    case = helpers.CONFIGS[key]
+    lay = helpers.layout_of(case)
+    cache, q, _ = build_cache(case, batch, context, device)
+    out = torch.empty((batch, case.nh, case.d), dtype=torch.float32, device=device)
+    step_bytes = lay.decode_algorithmic_bytes(context) * batch
+    # the page pools of these configurations fit in the L2: evict them between launches by writing a larger buffer
+    flush = torch.empty(192 << 20, dtype=torch.uint8, device=device) if cache.bytes_allocated() < (160 << 20) else None
+    for _ in range(max(3, warmup)):
+        cache.decode(q, out, max_seq_len=context)
+    torch.cuda.synchronize(device)
+    ms = []
+    for _ in range(steps):
+        if flush is not None:
+            flush.fill_(1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        cache.decode(q, out, max_seq_len=context)
+        e1.record()
+        torch.cuda.synchronize(device)
+        ms.append(e0.elapsed_time(e1))
+    med = statistics.median(ms)
+    value = step_bytes / (med * 1e-3) / 1e9
+    return {"metric": METRIC, "value": value, "unit": "GB/s", "ms_per_step": med, "tokens_per_s": batch / (med * 1e-3),
+            "config": {"workload": name, "batch": batch, "context": context, "algorithmic_bytes_per_step": step_bytes,
+                       "launch_plan": ctypes_plan(cache, batch, context),
+                       "l2": "L2 evicted before every launch (192 MB written)" if flush is not None else "inputs exceed the L2"},
+            "roofline": {"bound": "hbm (launch-latency bound at this size)" if step_bytes < (100 << 20) else "hbm",
+                         "achieved": value, "peak": peak, "unit": "GB/s", "frac": value / peak,
+                         "peak_source": f"{peak_kind} HBM copy bandwidth", "kernel": "decode_mma_kernel"}}
+
+
+def measure_secondary(args, device):
+    """The other parts of the path, each against its own HBM roofline (one GPU): the cache writer, the GEMV /
+    skinny GEMM of the generated runtime, the whole decode step at batch 1, and the two small attention-only
+    configurations. A part that fails is reported as such and does not take the headline down with it."""
+    import torch
+    out = {}
+    jobs = [("writer", lambda: measure_writer(args.steps, args.warmup, device)),
+            ("gemv_b1", lambda: measure_gemv(1, args.steps, args.warmup, device)),
+            ("gemv_b8", lambda: measure_gemv(8, args.steps, args.warmup, device)),
+            ("gemv_b64", lambda: measure_gemv(64, args.steps, args.warmup, device)),
+            ("decode_attn_tinyllama_b4_t512", lambda: measure_decode_config("tinyllama_decode_attn_b4_t512", args.steps, args.warmup, device)),
+            ("decode_attn_qwen05b_b64_t4096", lambda: measure_decode_config("qwen05b_decode_attn_b64_t4096", args.steps, args.warmup, device)),
+            ("decode_step_qwen25_14b_b1_t32768", lambda: measure_step(1, 32768, "p2p", min(args.steps, 10), args.warmup, device, 0, 0, 1, None))]
+    for name, fn in jobs:
+        try:
+            out[name] = fn()
+        except Exception as exc:   # noqa: BLE001
+            out[name] = {"failed": f"{type(exc).__name__}: {exc}"}
+        torch.cuda.synchronize(device)
+        torch.cuda.empty_cache()
+    return out
+
+
+def run_secondary(args):
+    """GEMV and cache-writer workloads on their own: one GPU, value = algorithmic bytes / CUDA-event time."""
+    import torch
     from jacq_b200 import _native
-    from jacq_b200.cache import gemv
     _native.lib()
     device = torch.device("cuda:0")
     torch.cuda.set_device(device)
-    peak, peak_kind = _peaks()
-    kind = SECONDARY[args.workload]
-    if kind == "gemv":
-        gbatch = int(args.workload.rsplit("_b", 1)[1])
-        hidden, ffn, qkv = 5120, 13824, 7168
-        shapes = [(qkv, hidden), (hidden, hidden), (2 * ffn, hidden), (hidden, ffn)]
-        layers = 8
-        gen = torch.Generator(device=device).manual_seed(11)
-        weights = [[(torch.randn((o, i), device=device, dtype=torch.float16, generator=gen) * 0.02) for o, i in shapes]
-                   for _ in range(layers)]
-        xs = {i: torch.randn((gbatch, i), device=device, dtype=torch.float16, generator=gen) for i in (hidden, ffn)}
-        ys = [[torch.empty((gbatch, o), device=device, dtype=torch.float16) for o, _ in shapes] for _ in range(layers)]
-        lib = _native.lib()
-        import ctypes
-        stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
-
-        def step():
-            for lw, ly in zip(weights, ys):
-                for w, y in zip(lw, ly):
-                    rc = lib.kivi_b200_gemv_f16(w.data_ptr(), xs[w.shape[1]].data_ptr(), y.data_ptr(), None,
-                                                w.shape[0], w.shape[1], gbatch, stream)
-                    assert rc == 0
-        step_bytes = layers * sum(o * i * 2 + gbatch * (o + i) * 2 for o, i in shapes)
-        launches = layers * len(shapes)
-        metric, kernel = "fp16 GEMV achieved HBM GB/s", ("gemv_kernel" if gbatch <= 4 else "skinny_gemm_kernel")
-        ms = _timed_steps(step, args.steps, args.warmup, device)
-        extra = {"shapes_out_in": shapes, "layers": layers, "batch": gbatch}
+    if SECONDARY[args.workload] == "gemv":
+        rec = measure_gemv(int(args.workload.rsplit("_b", 1)[1]), args.steps, args.warmup, device)
     else:
-        case = helpers.CONFIGS["mistral7b"]
-        lay = helpers.layout_of(case)
-        batch, chunk, start = 128, 512, 512
-        from jacq_b200.cache import KiviCache
-        pages = lay.old_pages(start + chunk * (args.steps + max(3, args.warmup) + 1)) + 1
-        cache = KiviCache(lay, batch * pages, batch, pages, device)
-        gen = torch.Generator(device=device).manual_seed(5)
-        cache.set_block_tables(torch.randperm(batch * pages, device=device, generator=gen).to(torch.int32)
-                               .reshape(batch, pages))
-        k = torch.randn((batch * chunk, case.nkv, case.d), device=device, dtype=torch.float16, generator=gen)
-        v = torch.randn((batch * chunk, case.nkv, case.d), device=device, dtype=torch.float16, generator=gen)
-        offs = torch.arange(batch + 1, device=device, dtype=torch.int32) * chunk
-        state = {"len": 0}
-
-        def step():
-            cache.write(k, v, offs, max_new_per_seq=chunk, max_start_seq_len=state["len"])
-            state["len"] += chunk
-        step()   # from empty: afterwards every step ages out exactly chunk / group groups per sequence
-        g, d, nkv, r, hg = case.g, case.d, case.nkv, case.r, lay.hd_groups
-        groups = chunk // g
-        per_head = (2 * chunk * d * 2                      # new K and V rows read (by the pack or the append)
-                    + groups * (g * d + (g // case.b) * d * 4 + g * hg * 4)   # codes, key params per page, value params
-                    + 2 * 2 * r * d * 2)                   # rows that stay fp16: read once, written once, K and V
-        step_bytes = batch * nkv * per_head
-        launches = 2
-        metric, kernel = "KIVI cache-writer achieved HBM GB/s", "pack_groups_kernel + scratch_update_kernel"
-        ms = _timed_steps(step, args.steps, args.warmup, device)
-        extra = {"batch": batch, "chunk_tokens": chunk, "tokens_per_s": batch * chunk / (statistics.mean(ms) * 1e-3)}
-    mean_ms = statistics.mean(ms)
-    value = step_bytes / (mean_ms * 1e-3) / 1e9
-    print(json.dumps({
-        "metric": metric, "value": value, "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup),
-        "ms_per_step": mean_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16/u4",
-        "data": "synthetic", "config": {"workload": args.workload, "algorithmic_bytes_per_step": step_bytes,
-                                        "l2": "working set exceeds the 126 MB L2", **extra},
-        "gpu_launches": launches * args.steps,
-        "roofline": {"bound": "hbm", "achieved": value, "peak": peak, "unit": "GB/s", "frac": value / peak,
-                     "traffic": None, "peak_source": f"{peak_kind} HBM copy bandwidth", "kernel": kernel},
-    }))
+        rec = measure_writer(args.steps, args.warmup, device)
+    print(json.dumps({**rec, "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup), "higher_is_better": True,
+                      "scaling": "weak", "vs_baseline": None, "dtype": "f16/u4", "data": "synthetic"}))
 
 
-def run_step(args):
-    """Whole decode step (config: Qwen2.5-14B shape) through jacq_b200.runtime.DecodeRuntime.
+def step_weights(cfg, device, rank, world):
+    """Random-init fp16 weights of the decode-step workloads, this rank's shard (same seed everywhere, so the
+    replicated tensors agree)."""
+    import torch
+    from jacq_b200.runtime import random_layer
+    gen = torch.Generator(device=device).manual_seed(1234)
+
+    def mat(rows, cols):
+        return (torch.randn((rows, cols), generator=gen, device=device, dtype=torch.float32) * 0.02).half()
+
+    return {"embed": mat(cfg.vocab, cfg.hidden),
+            "final_norm": (1.0 + 0.1 * torch.randn((cfg.hidden,), generator=gen, device=device)).half(),
+            "lm_head": mat(cfg.vocab // world, cfg.hidden),
+            "layers": [random_layer(cfg, gen, device, rank=rank, world=world) for _ in range(cfg.layers)]}, gen
+
+
+def measure_step(batch, context, comm, steps, warmup, device, rank, local_rank, world, group, weights=None, gen=None,
+                 profile_only=False):
+    """Whole decode step (Qwen2.5-14B shape) through jacq_b200.runtime.DecodeRuntime.
 
     value = tokens/s of the whole job (batch / step time, CUDA-graph replay, device-resident token
     ids); roofline = the bytes one rank must stream per step (its weight shard + the KV bytes of its
@@ -497,33 +748,16 @@ def run_step(args):
     read back into pinned host memory."""
     import torch
     import torch.distributed as dist
-    from jacq_b200 import _native
-    from jacq_b200.runtime import DecodeModelConfig, DecodeRuntime, random_layer
-    _native.lib()
-    rank, local_rank, world = _dist_env()
-    device = torch.device(f"cuda:{local_rank}")
-    torch.cuda.set_device(device)
-    group = None
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
-        group = dist.group.WORLD
+    from jacq_b200.runtime import DecodeModelConfig, DecodeRuntime
     cfg = DecodeModelConfig.qwen25_14b()
-    batch, context = STEP_WORKLOADS[args.workload]
-    warm = max(3, args.warmup)
-    total_steps = warm + 2 * args.steps + 2          # warm-up, device-timed steps, end-to-end steps
+    warm = max(3, warmup)
+    total_steps = warm + 2 * steps + 2          # warm-up, device-timed steps, end-to-end steps
     start = context - total_steps
-    gen = torch.Generator(device=device).manual_seed(1234)   # same seed on every rank: replicated tensors agree
-
-    def mat(rows, cols):
-        return (torch.randn((rows, cols), generator=gen, device=device, dtype=torch.float32) * 0.02).half()
-
-    weights = {"embed": mat(cfg.vocab, cfg.hidden),
-               "final_norm": (1.0 + 0.1 * torch.randn((cfg.hidden,), generator=gen, device=device)).half(),
-               "lm_head": mat(cfg.vocab // world, cfg.hidden),
-               "layers": [random_layer(cfg, gen, device, rank=rank, world=world) for _ in range(cfg.layers)]}
+    if weights is None:
+        weights, gen = step_weights(cfg, device, rank, world)
     tables = torch.randperm(batch * (-(-(context - cfg.residual) // cfg.block_size)), generator=gen, device=device)
     rt = DecodeRuntime(cfg, weights, batch=batch, max_seq_len=context, device=device, rank=rank, world=world,
-                       group=group, block_tables=tables.to(torch.int32).reshape(batch, -1), comm=args.comm)
+                       group=group, block_tables=tables.to(torch.int32).reshape(batch, -1), comm=comm)
     # synthetic context: fill layer 0 through the library's writer, then give every layer the same pages
     c0 = rt.caches[0]
     c0.set_block_tables(rt.block_tables)
@@ -547,92 +781,178 @@ def run_step(args):
     if world > 1:
         dist.all_reduce(torch.zeros(8, device=device, dtype=torch.float16))   # communicator up before the capture
     torch.cuda.synchronize(device)
-    if args.profile_only:
+    if profile_only:
         # eager steps inside an NVTX range: the command line ncu wraps (--nvtx --nvtx-include "kivi_step/")
         rt.step()
         torch.cuda.synchronize(device)
         torch.cuda.nvtx.range_push("kivi_step")
-        for _ in range(args.steps):
+        for _ in range(steps):
             rt.step()
         torch.cuda.synchronize(device)
         torch.cuda.nvtx.range_pop()
-        print(json.dumps({"profile_only": True, "workload": args.workload, "steps": args.steps,
-                          "launches_per_step": cfg.layers * 10 + 6}))
-        return
+        return {"profile_only": True, "steps": steps, "launches_per_step": cfg.layers * 10 + 6}
     rt.capture()
     for _ in range(warm):
         rt.step()
     torch.cuda.synchronize(device)
 
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize(device)
+    if sampler:
+        sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
+    for _ in range(steps):
         rt.step()
     e1.record()
     torch.cuda.synchronize(device)
+    clocks = sampler.stop() if sampler else None
     if world > 1:
         dist.barrier()
-    total_ms = e0.elapsed_time(e1)
-    clocks = sampler.stop() if rank == 0 else None
-    if world > 1:
-        t = torch.tensor([total_ms], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms = float(t.item())
-    ms_per_step = total_ms / args.steps
+    ms_per_step = _max_over_ranks(e0.elapsed_time(e1), device, world) / steps
 
     # end to end: token ids from pinned host memory in, next ids back out, every step
     tok_host = rt.tokens.cpu().pin_memory()
     out_host = torch.empty_like(tok_host).pin_memory()
     torch.cuda.synchronize(device)
     t0 = time.perf_counter()
-    for _ in range(args.steps):
+    for _ in range(steps):
         rt.tokens.copy_(tok_host, non_blocking=True)
         rt.step()
         out_host.copy_(rt.tokens, non_blocking=True)
         torch.cuda.synchronize(device)
         tok_host.copy_(out_host)
-    e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
-    if world > 1:
-        t = torch.tensor([e2e_ms], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
+    e2e_ms = _max_over_ranks((time.perf_counter() - t0) * 1e3 / steps, device, world)
     final_lens = rt.seq_lens.cpu().tolist()
     exchange_ok = rt.exchange_status() == 0
+    weight_bytes = cfg.weight_bytes(world)
+    kv_bytes = rt.kv_bytes_per_step(context)
     rt.close()
+    del rt
+    torch.cuda.empty_cache()
 
+    peak, peak_kind = _peaks()
+    rank_bytes = weight_bytes + kv_bytes
+    achieved = rank_bytes / (ms_per_step * 1e-3) / 1e9
+    launches_per_step = cfg.layers * 10 + 6
+    return {
+        "metric": "decode-step tokens/s", "value": batch / (ms_per_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
+        "steps": steps, "warmup": warm, "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f16/u4", "data": "synthetic",
+        "config": {"workload": f"qwen25_14b_decode_step_b{batch}_t{context}", "model_shape": cfg.name, "layers": cfg.layers,
+                   "batch": batch, "context": context, "block": cfg.block_size, "group": cfg.group_size, "residual": cfg.residual,
+                   "parallelism": f"tp{world} over kv heads, {comm} exchange" if world > 1 else "1 gpu",
+                   "weights": "random-init fp16 N(0, 0.02)", "step": "CUDA-graph replay of kivi_b200_decode_step",
+                   "l2": "29.5 GB of weights and the KV pages exceed the 126 MB L2",
+                   "final_seq_lens_ok": final_lens == [context - 2] * batch, "exchange_ok": exchange_ok},
+        "e2e": {"value": batch / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 4 * batch,
+                "d2h_bytes_per_step": 4 * batch, "ms_per_step": e2e_ms},
+        "gpu_launches": launches_per_step * (warm + 2 * steps),
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_source": f"{peak_kind} HBM copy bandwidth",
+                     "bytes_per_rank_per_step": {"weights": weight_bytes, "kv_cache": kv_bytes},
+                     "kernel": "whole step: gemv / skinny GEMM, decode_mma_kernel, writer, element-wise"},
+        "cpu_baseline": None,
+        "clocks": clocks,
+    }
+
+
+def tp_parity_check(device, rank, world, comm, batch):
+    """A short tensor-parallel run of a small model on all ranks, checked against the CPU step oracle (test
+    infrastructure, used here as the checker only): 70 steps across the first quantisation boundary, logits of
+    this rank's vocabulary slice within rtol = atol = 2e-2 and the exchange's status word clean."""
+    import torch
+    import torch.distributed as dist
+    from oracle import step_oracle as so
+    from jacq_b200.runtime import DecodeModelConfig, DecodeRuntime, shard_layer
+    s = so.StepShape(layers=2, hidden=512, nh=16, nkv=8, hd=64, ffn=1024, vocab=2048, rope_base=10000.0,
+                     norm_eps=1e-5, attn_bias=True, block=16, group=32, residual=32)
+    cfg = DecodeModelConfig("parity", s.layers, s.hidden, s.nh, s.nkv, s.hd, s.ffn, s.vocab, rope_base=s.rope_base,
+                            norm_eps=s.norm_eps, attn_bias=s.attn_bias, block_size=s.block, group_size=s.group,
+                            residual=s.residual)
+    w = so.random_weights(s, 21)
+    per_seq, steps = 8, 70
+    bt = np.random.default_rng(9).permutation(batch * per_seq).reshape(batch, per_seq).astype(np.int32)
+    oracle = so.StepOracle(s, w, bt, batch * per_seq, world=world)
+    vl = s.vocab // world
+    shard = {"embed": torch.from_numpy(w.embed), "final_norm": torch.from_numpy(w.final_norm),
+             "lm_head": torch.from_numpy(w.lm_head[rank * vl: (rank + 1) * vl]),
+             "layers": [shard_layer(cfg, {k: (None if v is None else torch.from_numpy(v)) for k, v in lw.items()},
+                                    rank, world) for lw in w.layers]}
+    rt = DecodeRuntime(cfg, shard, batch=batch, max_seq_len=per_seq * s.block + s.residual, device=device, rank=rank,
+                       world=world, group=dist.group.WORLD, block_tables=torch.from_numpy(bt), comm=comm)
+    tok = (np.arange(batch, dtype=np.int32) * 101 + 4) % s.vocab
+    worst, ok = 0.0, True
+    for i in range(steps):
+        if i == steps // 2:
+            rt.capture()
+        want_tok, want_logits = oracle.step(tok)
+        rt.step(torch.from_numpy(tok))
+        got = rt.logits.float().cpu().numpy()
+        want = want_logits.astype(np.float32)[:, rank * vl: (rank + 1) * vl]
+        err = np.abs(got - want)
+        worst = max(worst, float(err.max()))
+        ok = ok and bool((err <= 2e-2 + 2e-2 * np.abs(want)).all())
+        tok = want_tok.astype(np.int32)
+    ok = ok and rt.exchange_status() == 0 and bool((rt.seq_lens.cpu().numpy() == steps).all())
+    rt.close()
+    flag = torch.tensor([0.0 if ok else 1.0, worst], device=device, dtype=torch.float64)
+    dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+    return {"comm": comm, "batch": batch, "ranks": world, "steps": steps, "ok": bool(flag[0].item() == 0.0),
+            "max_abs_err_logits": float(flag[1].item()), "checked_against": "CPU step oracle, every rank its vocabulary slice"}
+
+
+def measure_tp_step(args, device, rank, local_rank, world):
+    """The one part of the path with an exchange, on the ranks of this run: KV-head tensor parallelism of the
+    Qwen2.5-14B-shaped decode step (strong scaling: the model is split, the batch is not), with the library's
+    peer-memory exchange and with NCCL hooks, batch 1 and 8, after a parity run of a small model on the same
+    ranks. NVLS is off and no multimem instruction is used."""
+    import torch
+    import torch.distributed as dist
+    from jacq_b200.runtime import DecodeModelConfig
+    out = {"parity": [], "runs": []}
+    try:
+        for comm, b in (("p2p", 3), ("p2p", 6), ("nccl", 3)):
+            out["parity"].append(tp_parity_check(device, rank, world, comm, b))
+        cfg = DecodeModelConfig.qwen25_14b()
+        weights, gen = step_weights(cfg, device, rank, world)
+        steps = min(args.steps, 10)
+        for batch in (1, 8):
+            for comm in ("p2p", "nccl"):
+                rec = measure_step(batch, 32768, comm, steps, args.warmup, device, rank, local_rank, world, dist.group.WORLD,
+                                   weights=weights, gen=gen)
+                out["runs"].append({"batch": batch, "comm": comm, "ms_per_step": rec["ms_per_step"], "tokens_per_s": rec["value"],
+                                    "e2e_ms_per_step": rec["e2e"]["ms_per_step"], "roofline_frac_of_rank_bytes": rec["roofline"]["frac"],
+                                    "bytes_per_rank_per_step": rec["roofline"]["bytes_per_rank_per_step"],
+                                    "exchange_ok": rec["config"]["exchange_ok"], "final_seq_lens_ok": rec["config"]["final_seq_lens_ok"]})
+    except Exception as exc:   # noqa: BLE001 - report, keep the headline
+        out["failed"] = f"{type(exc).__name__}: {exc}"
+    out["what"] = (f"Qwen2.5-14B-shaped decode step, 48 layers, context 32768, tp{world} over kv heads; all-reduce after o_proj "
+                   "and down_proj, arg-max gather; CUDA-graph replay; max over ranks")
+    return out
+
+
+def run_step(args):
+    """A decode-step workload on its own (`--workload qwen25_14b_decode_step_*`)."""
+    import torch
+    import torch.distributed as dist
+    from jacq_b200 import _native
+    _native.lib()
+    rank, local_rank, world = _dist_env()
+    device = torch.device(f"cuda:{local_rank}")
+    torch.cuda.set_device(device)
+    group = None
+    if world > 1:
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        dist.init_process_group("nccl", device_id=device)
+        group = dist.group.WORLD
+    batch, context = STEP_WORKLOADS[args.workload]
+    rec = measure_step(batch, context, args.comm, args.steps, args.warmup, device, rank, local_rank, world, group,
+                       profile_only=args.profile_only)
     if rank == 0:
-        peak, peak_kind = _peaks()
-        weight_bytes = cfg.weight_bytes(world)
-        kv_bytes = rt.kv_bytes_per_step(context)
-        rank_bytes = weight_bytes + kv_bytes
-        achieved = rank_bytes / (ms_per_step * 1e-3) / 1e9
-        launches_per_step = cfg.layers * 10 + 6
-        print(json.dumps({
-            "metric": "decode-step tokens/s", "value": batch / (ms_per_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
-            "steps": args.steps, "warmup": warm, "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f16/u4", "data": "synthetic",
-            "config": {"workload": args.workload, "model_shape": cfg.name, "layers": cfg.layers, "batch": batch,
-                       "context": context, "block": cfg.block_size, "group": cfg.group_size, "residual": cfg.residual,
-                       "parallelism": f"tp{world} over kv heads, {args.comm} exchange" if world > 1 else "1 gpu",
-                       "weights": "random-init fp16 N(0, 0.02)", "step": "CUDA-graph replay of kivi_b200_decode_step",
-                       "l2": "29.5 GB of weights and the KV pages exceed the 126 MB L2",
-                       "final_seq_lens_ok": final_lens == [context - 2] * batch, "exchange_ok": exchange_ok},
-            "e2e": {"value": batch / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 4 * batch,
-                    "d2h_bytes_per_step": 4 * batch, "ms_per_step": e2e_ms},
-            "gpu_launches": launches_per_step * (warm + 2 * args.steps),
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": None, "peak_source": f"{peak_kind} HBM copy bandwidth",
-                         "bytes_per_rank_per_step": {"weights": weight_bytes, "kv_cache": kv_bytes},
-                         "kernel": "whole step: gemv / skinny GEMM, decode_mma_kernel, writer, element-wise"},
-            "cpu_baseline": None,
-            "clocks": clocks,
-        }))
+        print(json.dumps(rec))
     if world > 1:
         # no destroy_process_group(): with NCCL collectives inside a captured graph it can block for minutes
         dist.barrier()
@@ -842,6 +1162,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", dest="cpu_baseline", action="store_false")
     ap.add_argument("--no-e2e-graph", dest="e2e_graph", action="store_false",
                     help="attention workloads: issue the end-to-end serving step as separate calls instead of one CUDA graph")
+    ap.add_argument("--no-extras", dest="extras", action="store_false",
+                    help="default workload: only the headline measurement (no secondary / tensor-parallel records)")
     ap.add_argument("--profile-only", action="store_true",
                     help="build the cache, run warmup+steps decode launches and exit (for ncu)")
     args = ap.parse_args()

@@ -135,6 +135,15 @@ int kivi_b200_decode(const kivi_geometry* geom, const kivi_cache* cache, const k
                      const int32_t* slot_ids, int batch, int max_seq_len, float* out,
                      void* workspace, size_t workspace_bytes, cudaStream_t stream);
 
+/* The same call with the result stored as fp16 (out f16 [batch, NH, D]): what a serving engine hands to the
+ * O projection, and half the bytes when the result leaves the device. Accumulation and normalisation are in
+ * fp32 as above; only the final store rounds. The reference's launch contract has fp32 output only
+ * (integrations/vllm_kivi/bindings.py:117), so this form has no counterpart there. */
+int kivi_b200_decode_f16(const kivi_geometry* geom, const kivi_cache* cache, const kivi_f16* q,
+                     const int32_t* block_tables, int max_blocks_per_seq, const int32_t* seq_lens,
+                     const int32_t* slot_ids, int batch, int max_seq_len, kivi_f16* out,
+                     void* workspace, size_t workspace_bytes, cudaStream_t stream);
+
 /* Sparse-retained decode for `batch` sequences (the reference's jac_launch_sparse_retained applied per
  * sequence: crates/jac-codegen-cuda/src/variants.rs:2620-2691, :2737-2742; tables built by the page-aware
  * allocator, integrations/vllm_kivi/source_patch.py:1839-1900). Row i of retained_block_tables is sequence
@@ -172,6 +181,26 @@ int kivi_b200_decode_noalloc(const kivi_geometry* geom, const kivi_cache* cache,
                              const int32_t* block_tables, int max_blocks_per_seq, const int32_t* seq_lens,
                              const int32_t* slot_ids, int batch, int max_seq_len, float* out,
                              cudaStream_t stream);
+
+/* How kivi_b200_decode would cut a launch of `batch` sequences of at most max_seq_len tokens into jobs (one
+ * CTA each), for callers and tests that want to see the plan: plan_out = {units1, k1, units2, k2}: the first
+ * units1 (sequence, kv head) units are cut into k1 parts each, the other units2 into k2 parts; parts of a cut
+ * unit leave partials in the workspace that a second kernel merges. Pure host arithmetic. No counterpart in
+ * the reference, which runs one warp per query head over the whole context. */
+int kivi_b200_decode_plan(const kivi_geometry* geom, int batch, int max_seq_len, int32_t plan_out[4]);
+
+/* What part `part` of `parts` of a sequence of seq_len tokens holds under that plan: items_out = {g0, g1, t0, t1},
+ * the key groups [g0, g1) and the 16-row tiles [t0, t1) of the fp16 residual. Over part = 0 .. parts - 1 these
+ * ranges tile the sequence's groups and tiles exactly once. The arithmetic the kernel itself runs, exported
+ * for tests. No counterpart in the reference. */
+int kivi_b200_decode_part_items(const kivi_geometry* geom, int seq_len, int part, int parts, int32_t items_out[4]);
+
+/* The tensor-core decode kernel waits on shared-memory barriers for its staged pages; every such wait is
+ * bounded. A CTA whose wait gave up drains its copies, counts itself here and leaves (the launch's output is
+ * then undefined). Writes the number of such CTAs since the library was loaded on the current device (0 in
+ * any healthy run) to *failures_out; synchronises the device. No counterpart in the reference, whose kernels
+ * have no asynchronous staging. */
+int kivi_b200_decode_wait_failures(uint32_t* failures_out);
 
 /* fp16 GEMV / skinny GEMM of the generated decode runtime: y[b, o] = sum_i W[o, i] * x[b, i],
  * W row-major [out_dim, in_dim], fp32 accumulation (reference: gemv(),

@@ -40,7 +40,7 @@ V1_SYMBOLS = (
 )
 V2_SYMBOLS = (
     "kivi_b200_abi_version", "kivi_b200_status_string", "kivi_b200_validate_geometry", "kivi_b200_cache_write",
-    "kivi_b200_decode_workspace_bytes", "kivi_b200_decode_workspace_init", "kivi_b200_decode", "kivi_b200_decode_noalloc", "kivi_b200_decode_sparse", "kivi_b200_gemv_f16", "kivi_b200_gemm_wait_failures",
+    "kivi_b200_decode_workspace_bytes", "kivi_b200_decode_workspace_init", "kivi_b200_decode", "kivi_b200_decode_f16", "kivi_b200_decode_noalloc", "kivi_b200_decode_sparse", "kivi_b200_gemv_f16", "kivi_b200_gemm_wait_failures", "kivi_b200_decode_wait_failures", "kivi_b200_decode_plan", "kivi_b200_decode_part_items",
     "kivi_b200_decode_step_workspace_bytes", "kivi_b200_decode_step", "kivi_b200_residual_rmsnorm",
     "kivi_b200_bias_rope", "kivi_b200_silu_mul", "kivi_b200_argmax",
     "kivi_b200_p2p_region_bytes", "kivi_b200_p2p_region_create", "kivi_b200_p2p_region_open",

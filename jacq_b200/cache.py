@@ -183,7 +183,8 @@ class KiviCache:
 
     def decode(self, q: torch.Tensor, out: torch.Tensor | None = None, *, max_seq_len: int,
                slot_ids: torch.Tensor | None = None, seq_lens: torch.Tensor | None = None) -> torch.Tensor:
-        """Decode attention for ``q [batch, NH, D]`` (fp16) -> ``out [batch, NH, D]`` (fp32)."""
+        """Decode attention for ``q [batch, NH, D]`` (fp16) -> ``out [batch, NH, D]``: fp32 as in the reference's
+        launch contract, or fp16 when an fp16 ``out`` is passed (the form the O projection consumes)."""
         g = self.layout.geometry
         if q.dtype != torch.float16:
             raise TypeError("Q must be torch.float16")
@@ -192,8 +193,8 @@ class KiviCache:
         batch = q.shape[0]
         if out is None:
             out = torch.empty(q.shape, dtype=torch.float32, device=self.device)
-        if out.dtype != torch.float32 or out.shape != q.shape or not out.is_contiguous():
-            raise TypeError("O must be a contiguous torch.float32 tensor shaped like Q")
+        if out.dtype not in (torch.float32, torch.float16) or out.shape != q.shape or not out.is_contiguous():
+            raise TypeError("O must be a contiguous torch.float32 (or float16) tensor shaped like Q")
         lens = self.seq_lens if seq_lens is None else seq_lens
         tables = self.block_tables
         if slot_ids is not None:
@@ -204,6 +205,8 @@ class KiviCache:
             raise TypeError("SEQ_LENS must be torch.int32")
         ws, ws_bytes = self.workspace(batch, max_seq_len)
         if self._sparse:
+            if out.dtype != torch.float32:
+                raise TypeError("the sparse-retained decode writes fp32 output only")
             mask = self.keep_mask if slot_ids is None else self.keep_mask.index_select(0, slot_ids.long())
             compact, counts = self.retained_tables(lens[:batch], tables[:batch], mask[:batch])
             rc = _native.lib().kivi_b200_decode_sparse(
@@ -212,9 +215,9 @@ class KiviCache:
                 _stream_ptr(self.device))
             _native.check(rc, "kivi_b200_decode_sparse")
             return out
-        rc = _native.lib().kivi_b200_decode(
-            ctypes.byref(self._geom), ctypes.byref(self._struct), _ptr(q), _ptr(tables), self.max_blocks_per_seq,
-            _ptr(lens), _ptr(slot_ids), batch, max_seq_len, _ptr(out), _ptr(ws), ws_bytes, _stream_ptr(self.device))
+        call = _native.lib().kivi_b200_decode if out.dtype == torch.float32 else _native.lib().kivi_b200_decode_f16
+        rc = call(ctypes.byref(self._geom), ctypes.byref(self._struct), _ptr(q), _ptr(tables), self.max_blocks_per_seq,
+                  _ptr(lens), _ptr(slot_ids), batch, max_seq_len, _ptr(out), _ptr(ws), ws_bytes, _stream_ptr(self.device))
         _native.check(rc, "kivi_b200_decode")
         return out
 

@@ -10,9 +10,20 @@
 namespace kivi {
 namespace {
 
-constexpr int kSmCount = 148;       // B200
 constexpr int kLongChunkTokens = 6144;
 constexpr int kMinChunkTokens = 256;
+
+// Multiprocessors of the current device (148 on a B200), asked once per device.
+int sm_count() {
+    static int cached[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (!cached[dev]) {
+        int n = 0;
+        cached[dev] = (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0) ? n : 148;
+    }
+    return cached[dev];
+}
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -64,13 +75,13 @@ SplitPlan plan_split(const Geom& g, int n, int max_old_tokens) {
     const long long units = (long long)n * g.nkv;
     // as many chunks as fill the resident CTA slots (three per SM) without exceeding them: a second, partial
     // wave costs more than the idle slots (the residual CTAs a split adds are tiny and do not count)
-    long long want = (3LL * kSmCount) / units;
+    const long long slots = 3LL * sm_count();
+    long long want = slots / units;
     if (want < 1) want = 1;
     // Long contexts: finer chunks are worth their partial results when they round the number of waves better
     // (256 units x 5 chunks = 2.9 waves of 444 slots instead of 256 CTAs on 444 slots), as long as a chunk stays
     // long enough to amortise a CTA's start and end (kLongChunkTokens; below it splitting measured slower).
     {
-        const long long slots = 3LL * kSmCount;
         auto efficiency = [&](long long w) {
             const long long ctas = units * w, waves = (ctas + slots - 1) / slots;
             return (double)ctas / (double)(waves * slots);
@@ -92,12 +103,71 @@ SplitPlan plan_split(const Geom& g, int n, int max_old_tokens) {
 constexpr size_t kWsAlign = 256;
 size_t align_up(size_t x) { return (x + kWsAlign - 1) / kWsAlign * kWsAlign; }
 
+// Tensor-core kernel: how the (sequence, kv head) units are cut into jobs. The model behind the choice, fitted
+// to measurements: three CTAs are resident on a multiprocessor and share it, so three equal jobs take one
+// "round" s together; CTAs are handed out in index order, so a multiprocessor's queue of j jobs runs as
+// floor(j / 3) full rounds and a last round of one or two jobs, which finish sooner than a full round but not in
+// proportion (a lone CTA reaches 0.6 of the multiprocessor's rate, two reach 0.87). A launch takes as long as the
+// longest queue, ceil(jobs / multiprocessors); a job costs a start-up plus its share of the unit; a launch that
+// cuts anything pays for the merge kernel. Candidates: every unit in k parts; or whole units for as many full
+// rounds as there are and the units left over in k2 parts each (the small jobs start last and even out the end).
+// Lengths live on the device, so the plan assumes every unit is as long as the longest the launch allows.
+constexpr int kJobFixedCost = 40;      // start-up of a CTA, in weight units of a 128-channel head (about 5 us)
+constexpr int kMergeCost = 60;         // the merge kernel behind a launch that cuts units
+constexpr double kCutMargin = 1.05;    // a cut has to promise this much before it is preferred to whole units
+constexpr int kMaxParts = 64;
+
+JobPlan plan_jobs(const Geom& g, int n, int max_old_tokens) {
+    const long long wg = g.g / 16;
+    const long long w = (long long)(max_old_tokens / g.g) * wg + (long long)((g.r + g.g + 15) / 16) * 4;
+    const long long units = (long long)n * g.nkv;
+    const long long sms = sm_count(), resident = decode_mma_ctas_per_sm();
+    const double fixed = (double)kJobFixedCost * 128 / g.d, merge = (double)kMergeCost * 128 / g.d;
+    long long kcap = w / (2 * wg);           // a part keeps at least two key groups' worth
+    if (kcap < 1) kcap = 1;
+    if (kcap > kMaxParts) kcap = kMaxParts;
+    JobPlan best = {0, 1, (int)units, 1};
+    // KIVI_DECODE_PARTS=k in the environment cuts every unit into k parts instead (for measurements)
+    static const int forced = [] { const char* e = getenv("KIVI_DECODE_PARTS"); return e ? atoi(e) : 0; }();
+    if (forced > 0) { best.k2 = forced < kcap ? forced : (int)kcap; return best; }
+    auto job = [&](long long k) { return fixed + (double)((w + k - 1) / k); };
+    // time of a queue of `jobs` equal jobs on one multiprocessor, in rounds
+    auto rounds_of = [&](long long jobs) {
+        const long long rest = jobs % resident;
+        const double last = rest == 0 ? 0.0 : (double)rest / resident / (rest == 1 ? 0.6 : (rest == 2 ? 0.87 : 1.0));
+        return (double)(jobs / resident) + last;
+    };
+    double best_t = rounds_of((units + sms - 1) / sms) * job(1);   // whole units
+    auto offer = [&](double t, long long u1, long long k1, long long u2, long long k2) {
+        if (t * kCutMargin < best_t) {
+            best_t = t * kCutMargin;
+            best.units1 = (int)u1; best.k1 = (int)k1; best.units2 = (int)u2; best.k2 = (int)k2;
+        }
+    };
+    for (long long k = 2; k <= kcap; ++k)                          // every unit in k parts
+        offer(rounds_of((units * k + sms - 1) / sms) * job(k) + merge, 0, 1, units, k);
+    const long long full = units / (sms * resident);                // whole units in full rounds, the rest cut finer
+    if (full >= 1 && units % (sms * resident) != 0) {
+        const long long whole = full * sms * resident, rest = units - whole;
+        for (long long k2 = 2; k2 <= kcap; ++k2)
+            offer((double)full * job(1) + rounds_of((rest * k2 + sms - 1) / sms) * job(k2) + merge, whole, 1, rest, k2);
+    }
+    return best;
+}
+
+// Workspace: the partials of whichever decode kernel the geometry runs on (both, sized for the larger, where a
+// dense launch takes the tensor-core kernel and a sparse one the generic kernel).
 struct WsLayout { size_t ml_off, o_off, total; };
-WsLayout ws_layout(const Geom& g, int n, const SplitPlan& sp) {
+WsLayout ws_layout(const Geom& g, int n, int max_old_tokens) {
     WsLayout w;
-    const size_t units = (size_t)n * g.nkv;
+    size_t parts = 0;
+    if (decode_mma_supports(g, -1)) parts = (size_t)plan_jobs(g, n, max_old_tokens).slots() * g.qpk;
+    if (!decode_mma_supports(g, 0)) {
+        const SplitPlan sp = plan_split(g, n, max_old_tokens);
+        const size_t chunk_parts = sp.max_chunks > 1 ? (size_t)n * g.nkv * sp.max_chunks * g.qpk : 0;
+        if (chunk_parts > parts) parts = chunk_parts;
+    }
     w.ml_off = 0;
-    const size_t parts = sp.max_chunks > 1 ? units * sp.max_chunks * g.qpk : 0;
     w.o_off = w.ml_off + align_up(parts * 2 * sizeof(float));
     w.total = w.o_off + align_up(parts * g.d * sizeof(float));
     if (w.total < kWsAlign) w.total = kWsAlign;   // never 0, which the size query returns for invalid arguments
@@ -107,7 +177,7 @@ WsLayout ws_layout(const Geom& g, int n, const SplitPlan& sp) {
 }  // namespace
 
 size_t decode_workspace_total(const Geom& g, int n, int max_old_tokens) {
-    return ws_layout(g, n, plan_split(g, n, max_old_tokens)).total;
+    return ws_layout(g, n, max_old_tokens).total;
 }
 
 int run_decode(const Geom& g, const CachePtrs& cache, const SeqAddressing& seq, const __half* q, float* out,
@@ -116,20 +186,35 @@ int run_decode(const Geom& g, const CachePtrs& cache, const SeqAddressing& seq, 
     DecodeParams p;
     p.geom = g; p.cache = cache; p.seq = seq; p.q = q; p.out = out; p.out_h = out_h; p.n = n;
     p.max_seq = max_seq_cap; p.retained_pages = retained_pages; p.retained_dev = retained_dev; p.status = nullptr;
-    const SplitPlan sp = plan_split(g, n, max_old_tokens);
-    const WsLayout wl = ws_layout(g, n, sp);
-    p.chunk_tokens = sp.chunk_tokens;
-    p.max_chunks = sp.max_chunks;
-    if (sp.max_chunks > 1) {
+    const bool tensor_path = decode_mma_supports(g, retained_dev ? 0 : retained_pages);
+    const WsLayout wl = ws_layout(g, n, max_old_tokens);
+    bool need_ws;
+    if (tensor_path) {
+        p.plan = plan_jobs(g, n, max_old_tokens);
+        p.chunk_tokens = 0; p.max_chunks = 1;
+        need_ws = p.plan.slots() > 0;
+    } else {
+        const SplitPlan sp = plan_split(g, n, max_old_tokens);
+        p.plan = JobPlan{0, 1, 0, 1};
+        p.chunk_tokens = sp.chunk_tokens;
+        p.max_chunks = sp.max_chunks;
+        need_ws = sp.max_chunks > 1;
+    }
+    if (need_ws) {
         if (!ws || ws_bytes < wl.total) return KIVI_ERR_WORKSPACE;
         if (!aligned16(ws)) return KIVI_ERR_ALIGNMENT;
     }
     unsigned char* base = static_cast<unsigned char*>(ws);
     p.ws_ml = base ? reinterpret_cast<float*>(base + wl.ml_off) : nullptr;
     p.ws_o = base ? reinterpret_cast<float*>(base + wl.o_off) : nullptr;
-    cudaError_t e = decode_mma_supports(g, retained_dev ? 0 : retained_pages) ? launch_decode_mma(p, stream)
-                                                           : launch_decode_generic(p, stream);
-    if (e == cudaSuccess) e = launch_decode_merge(p, stream);   // nothing to do unless the plan splits the context
+    cudaError_t e;
+    if (tensor_path) {
+        e = launch_decode_mma(p, stream);
+        if (e == cudaSuccess) e = launch_decode_part_merge(p, stream);   // nothing to do unless a unit was cut
+    } else {
+        e = launch_decode_generic(p, stream);
+        if (e == cudaSuccess) e = launch_decode_merge(p, stream);        // nothing to do unless the plan splits the context
+    }
     return e == cudaSuccess ? KIVI_OK : KIVI_ERR_CUDA;
 }
 
@@ -171,7 +256,7 @@ void* ref_workspace(const Geom& g, int n, size_t* bytes, cudaStream_t stream) {
         const Geom lanes[2] = {ref_geom(40, 8), ref_geom(20, 4)};
         for (const Geom& lane : lanes)
             for (int q = 1; q <= kRefMaxQueries; ++q) {
-                size_t t = ws_layout(lane, q, plan_split(lane, q, kRefLQ)).total;
+                size_t t = ws_layout(lane, q, kRefLQ).total;
                 if (t > need) need = t;
             }
         e = cudaMalloc(&g_ref_ws[dev], need);
@@ -291,7 +376,33 @@ extern "C" int kivi_b200_cache_write(const kivi_geometry* geom, const kivi_cache
 extern "C" size_t kivi_b200_decode_workspace_bytes(const kivi_geometry* geom, int batch, int max_seq_len) {
     if (check_geometry(geom) != KIVI_OK || batch <= 0 || max_seq_len < 0) return 0;
     const Geom g = make_geom(*geom);
-    return ws_layout(g, batch, plan_split(g, batch, split_old(max_seq_len, g.r, g.g))).total;
+    return ws_layout(g, batch, split_old(max_seq_len, g.r, g.g)).total;
+}
+
+extern "C" int kivi_b200_decode_plan(const kivi_geometry* geom, int batch, int max_seq_len, int32_t plan_out[4]) {
+    const int rc = check_geometry(geom);
+    if (rc != KIVI_OK) return rc;
+    if (!plan_out) return KIVI_ERR_NULL_POINTER;
+    if (batch <= 0 || max_seq_len < 0) return KIVI_ERR_RANGE;
+    const Geom g = make_geom(*geom);
+    if (!decode_mma_supports(g, -1)) { plan_out[0] = 0; plan_out[1] = 1; plan_out[2] = batch * g.nkv; plan_out[3] = 1; return KIVI_OK; }
+    const JobPlan pl = plan_jobs(g, batch, split_old(max_seq_len, g.r, g.g));
+    plan_out[0] = pl.units1; plan_out[1] = pl.k1; plan_out[2] = pl.units2; plan_out[3] = pl.k2;
+    return KIVI_OK;
+}
+
+extern "C" int kivi_b200_decode_part_items(const kivi_geometry* geom, int seq_len, int part, int parts, int32_t items_out[4]) {
+    const int rc = check_geometry(geom);
+    if (rc != KIVI_OK) return rc;
+    if (!items_out) return KIVI_ERR_NULL_POINTER;
+    if (seq_len < 0 || parts < 1 || part < 0 || part >= parts) return KIVI_ERR_RANGE;
+    const Geom g = make_geom(*geom);
+    if (g.g % 16) return KIVI_ERR_GEOMETRY;
+    const DecodeBounds b = decode_bounds(seq_len, g.r, g.g, -1, 0x3fffffff / g.b, g.b);
+    const UnitShape u = unit_shape_of(b.old_valid, b.res_valid, g.g);
+    const SegmentItems it = segment_items(u, g.g / 16, (int)share_begin(u.w, parts, part), (int)share_begin(u.w, parts, part + 1));
+    items_out[0] = it.g0; items_out[1] = it.g1; items_out[2] = it.t0; items_out[3] = it.t1;
+    return KIVI_OK;
 }
 
 extern "C" int kivi_b200_decode_workspace_init(void* workspace, size_t workspace_bytes, cudaStream_t stream) {
@@ -326,16 +437,16 @@ extern "C" int kivi_b200_decode_sparse(const kivi_geometry* geom, const kivi_cac
                       (int)max_old, -1, workspace, workspace_bytes, stream, retained_pages);
 }
 
-extern "C" int kivi_b200_decode(const kivi_geometry* geom, const kivi_cache* cache, const kivi_f16* q,
-                                const int32_t* block_tables, int max_blocks_per_seq, const int32_t* seq_lens,
-                                const int32_t* slot_ids, int batch, int max_seq_len, float* out, void* workspace,
-                                size_t workspace_bytes, cudaStream_t stream) {
+namespace {
+int decode_v2(const kivi_geometry* geom, const kivi_cache* cache, const kivi_f16* q, const int32_t* block_tables,
+              int max_blocks_per_seq, const int32_t* seq_lens, const int32_t* slot_ids, int batch, int max_seq_len,
+              float* out, kivi_f16* out_h, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
     int rc = check_geometry(geom);
     if (rc != KIVI_OK) return rc;
     rc = check_cache(cache);
     if (rc != KIVI_OK) return rc;
-    if (!q || !block_tables || !seq_lens || !out) return KIVI_ERR_NULL_POINTER;
-    if (!aligned16(q) || !aligned16(out)) return KIVI_ERR_ALIGNMENT;
+    if (!q || !block_tables || !seq_lens || (!out && !out_h)) return KIVI_ERR_NULL_POINTER;
+    if (!aligned16(q) || !aligned16(out) || !aligned16(out_h)) return KIVI_ERR_ALIGNMENT;
     if (batch < 0 || max_seq_len < 0 || max_seq_len > 0x3fffffff || max_blocks_per_seq < 0) return KIVI_ERR_RANGE;
     if (batch == 0) return KIVI_OK;
     if (!slot_ids && batch > cache->num_slots) return KIVI_ERR_RANGE;
@@ -348,8 +459,27 @@ extern "C" int kivi_b200_decode(const kivi_geometry* geom, const kivi_cache* cac
     a.slot_ids = slot_ids; a.slot_shared = 0;
     // max_seq_len also clamps a device-side length beyond the stated bound, so the launch plan and
     // the workspace stay valid whatever seq_lens holds.
-    return run_decode(g, cache_ptrs(*cache), a, reinterpret_cast<const __half*>(q), out, nullptr, batch, max_seq_len, max_old, -1,
-                      workspace, workspace_bytes, stream);
+    return run_decode(g, cache_ptrs(*cache), a, reinterpret_cast<const __half*>(q), out, reinterpret_cast<__half*>(out_h), batch,
+                      max_seq_len, max_old, -1, workspace, workspace_bytes, stream);
+}
+}  // namespace
+
+extern "C" int kivi_b200_decode(const kivi_geometry* geom, const kivi_cache* cache, const kivi_f16* q,
+                                const int32_t* block_tables, int max_blocks_per_seq, const int32_t* seq_lens,
+                                const int32_t* slot_ids, int batch, int max_seq_len, float* out, void* workspace,
+                                size_t workspace_bytes, cudaStream_t stream) {
+    if (!out) return KIVI_ERR_NULL_POINTER;
+    return decode_v2(geom, cache, q, block_tables, max_blocks_per_seq, seq_lens, slot_ids, batch, max_seq_len, out, nullptr,
+                     workspace, workspace_bytes, stream);
+}
+
+extern "C" int kivi_b200_decode_f16(const kivi_geometry* geom, const kivi_cache* cache, const kivi_f16* q,
+                                    const int32_t* block_tables, int max_blocks_per_seq, const int32_t* seq_lens,
+                                    const int32_t* slot_ids, int batch, int max_seq_len, kivi_f16* out, void* workspace,
+                                    size_t workspace_bytes, cudaStream_t stream) {
+    if (!out) return KIVI_ERR_NULL_POINTER;
+    return decode_v2(geom, cache, q, block_tables, max_blocks_per_seq, seq_lens, slot_ids, batch, max_seq_len, nullptr, out,
+                     workspace, workspace_bytes, stream);
 }
 
 // ------------------------------------------------------------------ decode without a workspace --
@@ -382,7 +512,7 @@ extern "C" int kivi_b200_decode_noalloc(const kivi_geometry* geom, const kivi_ca
     const int max_old = split_old(max_seq_len, g.r, g.g);
     if ((long long)max_old > (long long)max_blocks_per_seq * g.b) return KIVI_ERR_BLOCK_TABLE;
     // the launch plan decides how much scratch this call needs; refuse what the fixed array cannot hold
-    const WsLayout wl = ws_layout(g, batch, plan_split(g, batch, max_old));
+    const WsLayout wl = ws_layout(g, batch, max_old);
     if (wl.total > (size_t)KIVI_B200_NOALLOC_SCRATCH_BYTES) return KIVI_ERR_WORKSPACE;
 
     int dev = 0;

