@@ -160,98 +160,96 @@ def cpu_baseline(cache, q, case, context, nthreads, target_seconds=12.0):
 # ------------------------------------------------------------------------------------------------
 # clocks
 
+_POLLER = r"""
+import sys, time
+idx = int(sys.argv[1])
+sys.stdout = open(sys.argv[2], "w")
+try:
+    import pynvml as n
+    n.nvmlInit()
+    h = n.nvmlDeviceGetHandleByIndex(idx)
+    mx = n.nvmlDeviceGetMaxClockInfo(h, n.NVML_CLOCK_SM)
+    bits = {"hw_slowdown": n.nvmlClocksEventReasonHwSlowdown, "hw_thermal_slowdown": n.nvmlClocksEventReasonHwThermalSlowdown,
+            "sw_thermal_slowdown": n.nvmlClocksEventReasonSwThermalSlowdown, "sw_power_cap": n.nvmlClocksEventReasonSwPowerCap,
+            "hw_power_brake_slowdown": n.nvmlClocksEventReasonHwPowerBrakeSlowdown}
+    print("nvml", mx, " ".join(f"{k}={v}" for k, v in bits.items()), flush=True)
+    k, power = 0, 0.0
+    while True:
+        if k % 16 == 0:
+            power = n.nvmlDeviceGetPowerUsage(h) / 1000.0
+        print(f"{time.time():.6f} {n.nvmlDeviceGetClockInfo(h, n.NVML_CLOCK_SM)} {power:.1f} {n.nvmlDeviceGetCurrentClocksEventReasons(h)}")
+        k += 1
+        if k % 64 == 0:
+            sys.stdout.flush()
+        time.sleep(0.0002)
+except Exception as exc:
+    print("error", exc, flush=True)
+"""
+
+
 class ClockSampler:
-    """SM clock, power and throttle reasons of one GPU, read through NVML from a thread about every
-    millisecond while a timed region runs (reading only; nothing is set). A timed region of a few
-    milliseconds still gets several samples, which `nvidia-smi -lms` (100 ms at best) would not give;
-    where NVML cannot be loaded the sampler falls back to nvidia-smi."""
-    SMI_FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-                  "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-                  "clocks_event_reasons.sw_power_cap")
+    """SM clock, power and throttle reasons of one GPU, read through NVML (reading only; nothing is set) by a
+    child process a few thousand times a second for as long as the benchmark runs; every sample carries the host
+    clock, and a timed region asks for the samples that fall inside it. A separate process, because a polling
+    thread would contend with the launching thread for the interpreter lock; a few milliseconds of timed region
+    still get several samples, which `nvidia-smi -lms` (100 ms at best) would not give."""
 
     def __init__(self, gpu_index):
         self.gpu_index = gpu_index
-        self.samples, self.thread, self.proc, self.stop_flag = [], None, None, None
-        self.nvml = None
-        try:
-            import pynvml
-            pynvml.nvmlInit()
-            self.handle = pynvml.nvmlDeviceGetHandleByIndex(gpu_index)
-            self.nvml = pynvml
-        except Exception:   # noqa: BLE001 - any failure means "no NVML here"
-            self.nvml = None
-
-    def _loop(self):
-        n = self.nvml
-        while not self.stop_flag.is_set():
-            try:
-                self.samples.append((n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM),
-                                     n.nvmlDeviceGetPowerUsage(self.handle) / 1000.0,
-                                     n.nvmlDeviceGetCurrentClocksEventReasons(self.handle)))
-            except Exception:   # noqa: BLE001
-                break
-            time.sleep(0.0005)
+        self.proc, self.lines, self.path = None, None, None
 
     def start(self):
-        if self.nvml is not None:
-            import threading
-            self.samples = []
-            self.stop_flag = threading.Event()
-            self.thread = threading.Thread(target=self._loop, daemon=True)
-            self.thread.start()
-            return
+        import tempfile
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(self.gpu_index), f"--query-gpu={self.SMI_FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            fd, self.path = tempfile.mkstemp(prefix="kivi_clocks_", suffix=".txt")
+            os.close(fd)
+            self.proc = subprocess.Popen([sys.executable, "-c", _POLLER, str(self.gpu_index), self.path],
+                                         stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
+            time.sleep(0.5)   # NVML is up and polling before anything is timed
         except OSError:
             self.proc = None
 
     def stop(self):
-        if self.nvml is not None:
-            n = self.nvml
-            self.stop_flag.set()
-            self.thread.join(timeout=2)
-            if not self.samples:
-                return {"sm_mhz": None, "sm_max_mhz": None, "samples": 0, "reasons": ["no NVML sample"]}
-            bits = 0
-            for _, _, r in self.samples:
-                bits |= r
-            names = (("hw_slowdown", n.nvmlClocksEventReasonHwSlowdown), ("hw_thermal_slowdown", n.nvmlClocksEventReasonHwThermalSlowdown),
-                     ("sw_thermal_slowdown", n.nvmlClocksEventReasonSwThermalSlowdown), ("sw_power_cap", n.nvmlClocksEventReasonSwPowerCap),
-                     ("hw_power_brake_slowdown", n.nvmlClocksEventReasonHwPowerBrakeSlowdown))
-            try:
-                mx = n.nvmlDeviceGetMaxClockInfo(self.handle, n.NVML_CLOCK_SM)
-            except Exception:   # noqa: BLE001
-                mx = None
-            return {"sm_mhz": statistics.median(s[0] for s in self.samples), "sm_min_mhz": min(s[0] for s in self.samples),
-                    "sm_max_mhz": mx, "power_w_max": max(s[1] for s in self.samples), "samples": len(self.samples),
-                    "source": "NVML, one sample per ~0.6 ms during the timed region",
-                    "reasons": [name for name, bit in names if bits & bit]}
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+            self.lines = []
+            return
+        time.sleep(0.02)
         self.proc.terminate()
         try:
-            out, _ = self.proc.communicate(timeout=5)
+            self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-            out, _ = self.proc.communicate()
-        sm, mx, reasons = [], [], set()
-        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for line in out.splitlines():
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 7:
+            self.proc.wait()
+        try:
+            with open(self.path) as fh:
+                self.lines = fh.read().splitlines()
+            os.unlink(self.path)
+        except OSError:
+            self.lines = []
+        self.proc = None
+
+    def window(self, t0, t1):
+        """Statistics of the samples taken between host times t0 and t1 (call after stop())."""
+        if not self.lines or not self.lines[0].startswith("nvml"):
+            return {"sm_mhz": None, "sm_max_mhz": None, "samples": 0, "reasons": ["NVML unavailable: " + (self.lines[0] if self.lines else "no output")]}
+        head = self.lines[0].split()
+        sm_max = int(head[1])
+        names = dict((kv.split("=")[0], int(kv.split("=")[1])) for kv in head[2:])
+        sm, power, bits = [], [], 0
+        for line in self.lines[1:]:
+            parts = line.split()
+            if len(parts) != 4:
                 continue
-            try:
-                sm.append(float(parts[0]))
-                mx.append(float(parts[1]))
-            except ValueError:
-                continue
-            for name, val in zip(names, parts[3:7]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "source": "nvidia-smi -lms 100", "reasons": sorted(reasons)}
+            t = float(parts[0])
+            if t0 <= t <= t1:
+                sm.append(int(parts[1]))
+                power.append(float(parts[2]))
+                bits |= int(parts[3])
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": sm_max, "samples": 0, "reasons": ["no sample inside the region"]}
+        return {"sm_mhz": statistics.median(sm), "sm_min_mhz": min(sm), "sm_max_mhz": sm_max, "power_w_max": max(power),
+                "samples": len(sm), "source": "NVML polled by a child process, samples inside the timed region (host clock)",
+                "reasons": [name for name, bit in names.items() if bits & bit]}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -266,40 +264,38 @@ def _max_over_ranks(value, device, world):
     return float(t.item())
 
 
-def time_decode(cache, q, out, context, steps, warmup, device, rank, world, local_rank, sample_clocks=True):
+def time_decode(cache, q, out, context, steps, warmup, device, rank, world, local_rank):
     """W warm-up launches, then exactly K timed decode launches between a barrier + synchronize on both sides;
     CUDA events on the launching stream (one pair around the K steps, one event after every step). Returns
-    (ms of the K steps on this rank, per-step ms, clocks sampled during the K steps on rank 0)."""
+    (ms of the K steps on this rank, per-step ms, host-clock window of the timed region)."""
     import torch
     import torch.distributed as dist
     for _ in range(max(3, warmup)):
         cache.decode(q, out, max_seq_len=context)
     torch.cuda.synchronize(device)
-    sampler = ClockSampler(local_rank) if (rank == 0 and sample_clocks) else None
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize(device)
     marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
-    if sampler:
-        sampler.start()
+    t0 = time.time()
     marks[0].record()
     for k in range(steps):
         cache.decode(q, out, max_seq_len=context)
         marks[k + 1].record()
     torch.cuda.synchronize(device)
-    clocks = sampler.stop() if sampler else None
+    t1 = time.time()
     if world > 1:
         dist.barrier()
     per_step = [marks[k].elapsed_time(marks[k + 1]) for k in range(steps)]
-    return marks[0].elapsed_time(marks[steps]), per_step, clocks
+    return marks[0].elapsed_time(marks[steps]), per_step, (t0, t1)
 
 
 def sustained_decode(cache, q, out, context, device, local_rank, seconds=1.0):
     """The same launch back to back for about a second: what the kernel sustains once the GPU sits at its power
-    limit (the SM clock drops), reported beside the K-step figure with the clocks seen."""
+    limit (the SM clock drops), reported beside the K-step figure; returns the mean of the last 40 launches and
+    the host-clock window of the second half of the run."""
     import torch
-    sampler = ClockSampler(local_rank)
-    sampler.start()
+    start = time.time()
     t0, ms = time.perf_counter(), []
     while time.perf_counter() - t0 < seconds:
         marks = [torch.cuda.Event(enable_timing=True) for _ in range(41)]
@@ -309,7 +305,8 @@ def sustained_decode(cache, q, out, context, device, local_rank, seconds=1.0):
             marks[k + 1].record()
         torch.cuda.synchronize(device)
         ms = [marks[k].elapsed_time(marks[k + 1]) for k in range(40)]
-    return statistics.mean(ms), sampler.stop()
+    end = time.time()
+    return statistics.mean(ms), ((start + end) / 2, end)
 
 
 def run_b200(args):
@@ -347,17 +344,26 @@ def run_b200(args):
         return
 
     # ---- kernel-resident measurement: `value` and `roofline` --------------------------------
-    total_ms, per_step_ms, clocks = time_decode(cache, q, out, context, args.steps, args.warmup, device, rank, world,
-                                                local_rank)
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    total_ms, per_step_ms, timed_window = time_decode(cache, q, out, context, args.steps, args.warmup, device, rank, world,
+                                                      local_rank)
     total_ms = _max_over_ranks(total_ms, device, world)
     ms_per_step = total_ms / args.steps
     value = step_bytes * world / (ms_per_step * 1e-3) / 1e9
     plan = (ctypes_plan(cache, batch, context))
     sustained = None
+    clocks = None
     if rank == 0 and world == 1:
-        sus_ms, sus_clocks = sustained_decode(cache, q, out, context, device, local_rank)
+        sus_ms, sus_window = sustained_decode(cache, q, out, context, device, local_rank)
         sustained = {"value": step_bytes / (sus_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": sus_ms,
-                     "what": "the same launch back to back for 1 s (power-limited steady state)", "clocks": sus_clocks}
+                     "what": "the same launch back to back for 1 s (power-limited steady state); clocks over its second half"}
+    if sampler:
+        sampler.stop()
+        clocks = sampler.window(*timed_window)
+        if sustained is not None:
+            sustained["clocks"] = sampler.window(*sus_window)
 
     # ---- CPU baseline on a bounded sample (rank 0, one GPU only); doubles as a parity check ------
     base, parity = None, None
@@ -460,24 +466,34 @@ def measure_e2e(args, cache, q, case, lay, batch, context, device, rank, world, 
     import torch.distributed as dist
     e2e_steps = args.steps
     out16 = torch.empty((batch, case.nh, case.d), dtype=torch.float16, device=device)
-    q_host = q.cpu().pin_memory()
+    # One pinned staging buffer for everything a step sends to the device -- q, the new K and V rows, the
+    # sequence lengths before and after the write -- and one device buffer of the same layout: one H2D copy per step.
+    nq, nkv_rows = batch * case.nh * case.d, batch * case.nkv * case.d
+    halves = nq + 2 * nkv_rows
+    stage_bytes = halves * 2 + 2 * batch * 4
+    stage_host = torch.empty(stage_bytes, dtype=torch.uint8).pin_memory()
+    stage_dev = torch.empty(stage_bytes, dtype=torch.uint8, device=device)
+
+    def views(buf):
+        h = buf[: halves * 2].view(torch.float16)
+        lens = buf[halves * 2:].view(torch.int32).view(2, batch)      # row 0: before the write, row 1: after
+        return (h[:nq].view(batch, case.nh, case.d), h[nq: nq + nkv_rows].view(batch, case.nkv, case.d),
+                h[nq + nkv_rows:].view(batch, case.nkv, case.d), lens)
+
+    q_host, nk_host, nv_host, lens_host = views(stage_host)
+    q_dev, nk_dev, nv_dev, lens_dev = views(stage_dev)
     out_host = torch.empty(out16.shape, dtype=out16.dtype).pin_memory()
     gen = torch.Generator().manual_seed(7 + rank)
-    nk_host = torch.randn((batch, case.nkv, case.d), generator=gen).to(torch.float16).pin_memory()
-    nv_host = torch.randn((batch, case.nkv, case.d), generator=gen).to(torch.float16).pin_memory()
-    lens_host = torch.empty((2, batch), dtype=torch.int32).pin_memory()      # row 0: before the write, row 1: after
-    q_dev, nk_dev, nv_dev = torch.empty_like(q), torch.empty_like(nk_host, device=device), torch.empty_like(nv_host, device=device)
-    lens_dev = torch.empty((2, batch), dtype=torch.int32, device=device)
+    q_host.copy_(q.cpu())
+    nk_host.copy_(torch.randn((batch, case.nkv, case.d), generator=gen).to(torch.float16))
+    nv_host.copy_(torch.randn((batch, case.nkv, case.d), generator=gen).to(torch.float16))
     offs = torch.arange(batch + 1, device=device, dtype=torch.int32)
     state = {"len": context}
     # the bounds the launch plan needs are those of the last step of the run
     bound = context + e2e_steps + warm + 4
 
     def enqueue_step():
-        q_dev.copy_(q_host, non_blocking=True)
-        nk_dev.copy_(nk_host, non_blocking=True)
-        nv_dev.copy_(nv_host, non_blocking=True)
-        lens_dev.copy_(lens_host, non_blocking=True)
+        stage_dev.copy_(stage_host, non_blocking=True)
         cache.write(nk_dev, nv_dev, offs, max_new_per_seq=1, max_start_seq_len=bound, start_seq_lens=lens_dev[0], advance=False)
         cache.decode(q_dev, out16, max_seq_len=bound + 1, seq_lens=lens_dev[1])
         out_host.copy_(out16, non_blocking=True)
@@ -529,11 +545,11 @@ def measure_e2e(args, cache, q, case, lay, batch, context, device, rank, world, 
     if not torch.equal(check.cpu(), out_host):
         raise RuntimeError("bench: the end-to-end step's output differs from a decode of the same cache state")
     e2e_s = _max_over_ranks(e2e_s, device, world)
-    h2d = q_host.numel() * 2 + nk_host.numel() * 2 * 2 + lens_host.numel() * 4
+    h2d = stage_bytes
     d2h = out_host.numel() * 2
     return {"value": e2e_bytes * world / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
             "ms_per_step": e2e_s / e2e_steps * 1e3, "tokens_per_s": batch * world / (e2e_s / e2e_steps),
-            "what": "pinned q + new K/V rows + sequence lengths H2D, cache write (1 token/sequence), decode (fp16 out), O D2H"
+            "what": "one pinned staging buffer (q, new K/V rows, sequence lengths) H2D, cache write (1 token/sequence), decode (fp16 out), O D2H"
                     + ("; one CUDA graph launch per step" if graph is not None else "; eager calls")}
 
 
@@ -544,7 +560,7 @@ def measure_strong_scaling(args, cache, q, out, case, lay, batch, context, devic
     from jacq_b200 import sharding
     n = len(sharding.contiguous_shards(batch, world)[rank])
     total_ms, per_step, _ = time_decode(cache, q[:n], out[:n], context, args.steps, args.warmup, device, rank, world,
-                                        local_rank, sample_clocks=False)
+                                        local_rank)
     total_ms = _max_over_ranks(total_ms, device, world)
     ms = total_ms / args.steps
     value = lay.decode_algorithmic_bytes(context) * batch / (ms * 1e-3) / 1e9
@@ -696,7 +712,7 @@ def measure_secondary(args, device):
             ("gemv_b64", lambda: measure_gemv(64, args.steps, args.warmup, device)),
             ("decode_attn_tinyllama_b4_t512", lambda: measure_decode_config("tinyllama_decode_attn_b4_t512", args.steps, args.warmup, device)),
             ("decode_attn_qwen05b_b64_t4096", lambda: measure_decode_config("qwen05b_decode_attn_b64_t4096", args.steps, args.warmup, device)),
-            ("decode_step_qwen25_14b_b1_t32768", lambda: measure_step(1, 32768, "p2p", min(args.steps, 10), args.warmup, device, 0, 0, 1, None))]
+            ("decode_step_qwen25_14b_b1_t32768", lambda: measure_step(1, 32768, "p2p", min(args.steps, 10), args.warmup, device, 0, 0, 1, None, sample_clocks=False))]
     for name, fn in jobs:
         try:
             out[name] = fn()
@@ -739,7 +755,7 @@ def step_weights(cfg, device, rank, world):
 
 
 def measure_step(batch, context, comm, steps, warmup, device, rank, local_rank, world, group, weights=None, gen=None,
-                 profile_only=False):
+                 profile_only=False, sample_clocks=True):
     """Whole decode step (Qwen2.5-14B shape) through jacq_b200.runtime.DecodeRuntime.
 
     value = tokens/s of the whole job (batch / step time, CUDA-graph replay, device-resident token
@@ -796,19 +812,24 @@ def measure_step(batch, context, comm, steps, warmup, device, rank, local_rank, 
         rt.step()
     torch.cuda.synchronize(device)
 
-    sampler = ClockSampler(local_rank) if rank == 0 else None
+    sampler = ClockSampler(local_rank) if (rank == 0 and sample_clocks) else None
+    if sampler:
+        sampler.start()
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize(device)
-    if sampler:
-        sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    w0 = time.time()
     e0.record()
     for _ in range(steps):
         rt.step()
     e1.record()
     torch.cuda.synchronize(device)
-    clocks = sampler.stop() if sampler else None
+    w1 = time.time()
+    clocks = None
+    if sampler:
+        sampler.stop()
+        clocks = sampler.window(w0, w1)
     if world > 1:
         dist.barrier()
     ms_per_step = _max_over_ranks(e0.elapsed_time(e1), device, world) / steps
@@ -922,7 +943,7 @@ def measure_tp_step(args, device, rank, local_rank, world):
         for batch in (1, 8):
             for comm in ("p2p", "nccl"):
                 rec = measure_step(batch, 32768, comm, steps, args.warmup, device, rank, local_rank, world, dist.group.WORLD,
-                                   weights=weights, gen=gen)
+                                   weights=weights, gen=gen, sample_clocks=False)
                 out["runs"].append({"batch": batch, "comm": comm, "ms_per_step": rec["ms_per_step"], "tokens_per_s": rec["value"],
                                     "e2e_ms_per_step": rec["e2e"]["ms_per_step"], "roofline_frac_of_rank_bytes": rec["roofline"]["frac"],
                                     "bytes_per_rank_per_step": rec["roofline"]["bytes_per_rank_per_step"],

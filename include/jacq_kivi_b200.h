@@ -171,7 +171,9 @@ int kivi_b200_decode_sparse(const kivi_geometry* geom, const kivi_cache* cache, 
  *     with KIVI_ERR_WORKSPACE and nothing is launched (kivi_b200_decode_workspace_bytes tells the
  *     need in advance);
  *   - the first call on each device, made with that device current, looks the array's device
- *     address up; make that first call before any stream capture begins;
+ *     address up (once per device, safe against two threads calling first at the same time; the address
+ *     is kept until the process exits, so do not cudaDeviceReset between calls); make that first call
+ *     before any stream capture begins;
  *   - every call uses the same array: two calls whose kernels can overlap on the GPU (different
  *     streams, different host threads) race on it. Calls on one stream are safe back to back;
  *     nothing in the array has to be cleared between them (a call reads only partials it wrote).
@@ -194,6 +196,16 @@ int kivi_b200_decode_plan(const kivi_geometry* geom, int batch, int max_seq_len,
  * ranges tile the sequence's groups and tiles exactly once. The arithmetic the kernel itself runs, exported
  * for tests. No counterpart in the reference. */
 int kivi_b200_decode_part_items(const kivi_geometry* geom, int seq_len, int part, int parts, int32_t items_out[4]);
+
+/* Page ids (block tables) and slot ids are read from device memory and become addresses. The v2 calls hold them
+ * against kivi_cache.num_blocks / num_slots inside the kernels: the writer leaves a sequence untouched when its
+ * slot or one of the pages the write would pack into lies outside the pool; the decode reads page / slot 0
+ * instead (that sequence's output is then meaningless) -- nothing outside the pools is accessed either way.
+ * These report how many such sequences (writer) and ids (decode) were met since the library was loaded on the
+ * current device; 0 in any healthy run. The reference checks neither (its signatures carry no pool sizes, and
+ * the reference-lane symbols here cannot check for the same reason). Synchronise the device. */
+int kivi_b200_writer_rejected_indices(uint32_t* count_out);
+int kivi_b200_decode_rejected_indices(uint32_t* count_out);
 
 /* The tensor-core decode kernel waits on shared-memory barriers for its staged pages; every such wait is
  * bounded. A CTA whose wait gave up drains its copies, counts itself here and leaves (the launch's output is
@@ -302,8 +314,10 @@ typedef struct kivi_step_state {
  * kivi_b200_p2p_region_create(), hands the returned handle to the other ranks (any host channel),
  * opens theirs with kivi_b200_p2p_region_open() and passes the tp_size pointers, own region at
  * index tp_rank, in rank order. A rank pushes its partial projection into its slot in every
- * region with plain peer stores and raises a flag there; the kernel that consumes the sum (residual
- * add + RMSNorm) waits for the tp_size flags and adds the slots up in rank order in fp32, so every
+ * region with plain peer stores of 8-byte words, each carrying 32 bits of data and the 32-bit sequence
+ * number of the exchange, so a word is entirely old or entirely new and there is no separate flag; the
+ * kernel that consumes the sum (residual add + RMSNorm) polls the words of the tp_size slots until they
+ * carry the current number and adds them up in rank order in fp32, so every
  * rank gets the same bits and the reduction has no launch of its own. Waits are bounded: a rank
  * that never delivers ends the wait after about a second and sets its bit in the region's status
  * word (kivi_b200_p2p_status), the step's result is then undefined but nothing hangs. All ranks

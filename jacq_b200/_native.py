@@ -96,6 +96,8 @@ SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "kivi_b200_gemv_f16": (c_int, [_P, _P, _P, _P, c_int, c_int, c_int, _P]),
     "kivi_b200_gemm_wait_failures": (c_int, [ctypes.POINTER(c_uint32)]),
     "kivi_b200_decode_wait_failures": (c_int, [ctypes.POINTER(c_uint32)]),
+    "kivi_b200_writer_rejected_indices": (c_int, [ctypes.POINTER(c_uint32)]),
+    "kivi_b200_decode_rejected_indices": (c_int, [ctypes.POINTER(c_uint32)]),
     "kivi_b200_decode_part_items": (c_int, [ctypes.POINTER(KiviGeometry), c_int, c_int, c_int, ctypes.POINTER(c_int32)]),
     "kivi_b200_decode_plan": (c_int, [ctypes.POINTER(KiviGeometry), c_int, c_int, ctypes.POINTER(c_int32)]),
     "kivi_b200_decode_step_workspace_bytes": (c_size_t, [ctypes.POINTER(KiviStepConfig), c_int, c_int]),

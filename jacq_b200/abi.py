@@ -40,7 +40,7 @@ V1_SYMBOLS = (
 )
 V2_SYMBOLS = (
     "kivi_b200_abi_version", "kivi_b200_status_string", "kivi_b200_validate_geometry", "kivi_b200_cache_write",
-    "kivi_b200_decode_workspace_bytes", "kivi_b200_decode_workspace_init", "kivi_b200_decode", "kivi_b200_decode_f16", "kivi_b200_decode_noalloc", "kivi_b200_decode_sparse", "kivi_b200_gemv_f16", "kivi_b200_gemm_wait_failures", "kivi_b200_decode_wait_failures", "kivi_b200_decode_plan", "kivi_b200_decode_part_items",
+    "kivi_b200_decode_workspace_bytes", "kivi_b200_decode_workspace_init", "kivi_b200_decode", "kivi_b200_decode_f16", "kivi_b200_decode_noalloc", "kivi_b200_decode_sparse", "kivi_b200_gemv_f16", "kivi_b200_gemm_wait_failures", "kivi_b200_decode_wait_failures", "kivi_b200_writer_rejected_indices", "kivi_b200_decode_rejected_indices", "kivi_b200_decode_plan", "kivi_b200_decode_part_items",
     "kivi_b200_decode_step_workspace_bytes", "kivi_b200_decode_step", "kivi_b200_residual_rmsnorm",
     "kivi_b200_bias_rope", "kivi_b200_silu_mul", "kivi_b200_argmax",
     "kivi_b200_p2p_region_bytes", "kivi_b200_p2p_region_create", "kivi_b200_p2p_region_open",
@@ -114,11 +114,13 @@ def kernel_interface_v2(layout: KiviPageLayout, max_seq_len: int) -> dict[str, o
 
 
 def check_vllm_version(version: str, source_head: str | None = None) -> None:
-    core = version.split("+", 1)[0].split(".")
-    on_line = len(core) >= 3 and core[:3] == ["0", "8", "5"] and all(not s[:1].isdigit() for s in core[3:])
-    if not on_line:
+    """Accept the pinned 0.8.5 release line only: `0.8.5`, `0.8.5.postN`, `.devN`, any `+local` tag; refuse
+    look-alikes such as 0.8.50 or 0.8.5.1. With `source_head`, also require the pinned commit."""
+    release = version.partition("+")[0].split(".")
+    suffixes_ok = all(not part[:1].isdigit() for part in release[3:])
+    if release[:3] != ["0", "8", "5"] or not suffixes_ok:
         raise UnsupportedAbiError(f"vLLM {version} is not the supported {SUPPORTED_VLLM_VERSION} line")
-    if source_head is not None and source_head != SUPPORTED_VLLM_SOURCE_HEAD:
+    if source_head not in (None, SUPPORTED_VLLM_SOURCE_HEAD):
         raise UnsupportedAbiError(
             f"vLLM source head {source_head[:12]}... is not the pinned {SUPPORTED_VLLM_SOURCE_HEAD[:12]}...")
 
@@ -130,9 +132,10 @@ def check_cuda_arch(arch: str) -> None:
 
 def check_geometry(geometry: KiviModelGeometry) -> None:
     """v1 symbols only: the geometry they were compiled for."""
-    want = supported_geometry()
-    for attr in ("num_attention_heads", "num_kv_heads", "head_dim"):
-        if getattr(geometry, attr) != getattr(want, attr):
-            raise UnsupportedAbiError(
-                f"model geometry {attr}={getattr(geometry, attr)} does not match the v1 lane "
-                f"({want.name}: {attr}={getattr(want, attr)}); use the v2 calls")
+    lane = supported_geometry()
+    wrong = [(a, getattr(geometry, a), getattr(lane, a)) for a in ("num_attention_heads", "num_kv_heads", "head_dim")
+             if getattr(geometry, a) != getattr(lane, a)]
+    if wrong:
+        attr, got, want = wrong[0]
+        raise UnsupportedAbiError(f"model geometry {attr}={got} does not match the v1 lane ({lane.name}: {attr}={want}); "
+                                  "use the v2 calls")

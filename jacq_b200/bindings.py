@@ -8,7 +8,8 @@ cover several pages and the scratch holds ``residual + group`` rows.
 """
 from __future__ import annotations
 
-from dataclasses import asdict, dataclass
+import math
+from dataclasses import dataclass
 
 from jacq_b200.layout import KiviModelGeometry, KiviPageLayout
 
@@ -21,29 +22,35 @@ CACHE_TENSORS = JAC_LAUNCH_ORDER[2:10]
 
 @dataclass(frozen=True)
 class TensorBinding:
+    """One argument of the launch: name, dtype, shape (an entry may be a symbol instead of a number), element size
+    and what it holds. The per-layer counts are "dynamic" as soon as one dimension is symbolic."""
     name: str
     dtype: str
     shape: tuple[int | str, ...]
     bytes_per_element: int
     role: str
 
+    def _static_numel(self) -> int | None:
+        if any(isinstance(dim, str) for dim in self.shape):
+            return None
+        return math.prod(self.shape)
+
     @property
     def numel_per_layer(self) -> int | str:
-        n = 1
-        for dim in self.shape:
-            if isinstance(dim, str):
-                return "dynamic"
-            n *= dim
-        return n
+        n = self._static_numel()
+        return "dynamic" if n is None else n
 
     @property
     def bytes_per_layer(self) -> int | str:
-        n = self.numel_per_layer
-        return n if isinstance(n, str) else n * self.bytes_per_element
+        n = self._static_numel()
+        return "dynamic" if n is None else n * self.bytes_per_element
 
     def to_dict(self) -> dict[str, object]:
-        return {**asdict(self), "shape": list(self.shape), "numel_per_layer": self.numel_per_layer,
-                "bytes_per_layer": self.bytes_per_layer}
+        out: dict[str, object] = {"name": self.name, "dtype": self.dtype, "shape": list(self.shape),
+                                  "bytes_per_element": self.bytes_per_element, "role": self.role}
+        out["numel_per_layer"] = self.numel_per_layer
+        out["bytes_per_layer"] = self.bytes_per_layer
+        return out
 
 
 @dataclass(frozen=True)
@@ -122,17 +129,14 @@ class KiviDecodeBindingAbi:
         return 2 * g.num_kv_heads * self.layout.residual_tokens * g.head_dim * g.dtype_bytes
 
     def to_report(self) -> dict[str, object]:
-        return {
-            "seq_len": self.seq_len,
-            "old_tokens": self.old_tokens,
-            "old_pages": self.old_pages,
-            "physical_blocks_reported": self.physical_blocks,
-            "block_table_len": self.block_table_len,
-            "jac_launch_order": self.jac_launch_order(),
-            "tensor_bindings": [b.to_dict() for b in self.tensor_bindings()],
-            "old_page_bytes_per_layer": self.old_page_bytes_per_layer(),
-            "residual_bytes_per_sequence_layer": self.residual_bytes_per_sequence_layer(),
-        }
+        """JSON-serialisable summary (keys as in the reference's report, bindings.py:131-143)."""
+        report: dict[str, object] = {name: getattr(self, name) for name in ("seq_len", "old_tokens", "old_pages", "block_table_len")}
+        report["physical_blocks_reported"] = self.physical_blocks
+        report["jac_launch_order"] = self.jac_launch_order()
+        report["tensor_bindings"] = [binding.to_dict() for binding in self.tensor_bindings()]
+        for name in ("old_page_bytes_per_layer", "residual_bytes_per_sequence_layer"):
+            report[name] = getattr(self, name)()
+        return report
 
 
 def default_qwen32b_binding_abi(seq_len: int = 4096) -> KiviDecodeBindingAbi:

@@ -3,6 +3,7 @@
 // replaces are in include/jacq_kivi_b200.h.
 #include <cstdio>
 #include <cstdlib>
+#include <mutex>
 
 #include "decode_merge.cuh"
 #include "kivi_common.cuh"
@@ -62,6 +63,7 @@ CachePtrs cache_ptrs(const kivi_cache& c) {
     o.v_zero = reinterpret_cast<__half*>(c.v_zero_pages);
     o.k_scratch = reinterpret_cast<__half*>(c.k_residual_scratch);
     o.v_scratch = reinterpret_cast<__half*>(c.v_residual_scratch);
+    o.num_blocks = c.num_blocks; o.num_slots = c.num_slots;
     return o;
 }
 
@@ -280,6 +282,7 @@ CachePtrs ref_cache(const unsigned char* kc, const kivi_f16* ks, const kivi_f16*
     c.v_zero = reinterpret_cast<__half*>(const_cast<kivi_f16*>(vz));
     c.k_scratch = reinterpret_cast<__half*>(const_cast<kivi_f16*>(kr));
     c.v_scratch = reinterpret_cast<__half*>(const_cast<kivi_f16*>(vr));
+    c.num_blocks = c.num_slots = 0x7fffffff;   // the reference's signatures state no pool sizes
     return c;
 }
 
@@ -490,9 +493,11 @@ extern "C" int kivi_b200_decode_f16(const kivi_geometry* geom, const kivi_cache*
 static __device__ __align__(256) unsigned char g_noalloc_scratch[KIVI_B200_NOALLOC_SCRATCH_BYTES];
 
 namespace {
-// Device address of g_noalloc_scratch, looked up once per device. In host code the array's name is
-// only a handle for the runtime, not an address a kernel could use.
+// Device address of g_noalloc_scratch, looked up once per device (std::call_once: two host threads may make
+// their first call at the same time). In host code the array's name is only a handle for the runtime, not
+// an address a kernel could use.
 void* g_noalloc_ptr[kivi::kMaxDevices];
+std::once_flag g_noalloc_once[kivi::kMaxDevices];
 }  // namespace
 
 extern "C" int kivi_b200_decode_noalloc(const kivi_geometry* geom, const kivi_cache* cache, const kivi_f16* q,
@@ -517,13 +522,13 @@ extern "C" int kivi_b200_decode_noalloc(const kivi_geometry* geom, const kivi_ca
 
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return KIVI_ERR_CUDA;
-    if (!g_noalloc_ptr[dev]) {
-        // first call on this device (with it current): resolve the array's device address
+    // first call on this device (with it current): resolve the array's device address
+    std::call_once(g_noalloc_once[dev], [dev] {
         void* ptr = nullptr;
-        if (cudaGetSymbolAddress(&ptr, g_noalloc_scratch) != cudaSuccess || !ptr) return KIVI_ERR_CUDA;
-        g_noalloc_ptr[dev] = ptr;
-    }
+        if (cudaGetSymbolAddress(&ptr, g_noalloc_scratch) == cudaSuccess) g_noalloc_ptr[dev] = ptr;
+    });
     void* scratch = g_noalloc_ptr[dev];
+    if (!scratch) return KIVI_ERR_CUDA;
     // nothing in the array has to start from a known value: a launch reads only the partials it wrote itself
     SeqAddressing a;
     a.seq_lens = seq_lens; a.seq_len_scalar = 0;
@@ -613,6 +618,7 @@ extern "C" void kivi_b200_cache_write_launch(unsigned char* K_CODE_PAGES, kivi_f
                                              const kivi_f16* NEW_K, const kivi_f16* NEW_V, const int64_t* SLOT_MAPPING,
                                              const int* BLOCK_TABLE, int seq_len, int NKV_RUNTIME, cudaStream_t stream) {
     (void)SLOT_MAPPING;  // validated by the caller, never used for addressing (source_patch.py:1675)
+    if (NKV_RUNTIME < 1) { fprintf(stderr, "NKV_RUNTIME out of range for kivi_cache_write_launch: %d\n", NKV_RUNTIME); exit(1); }
     ref_write(NKV_RUNTIME, KIVI_V1_CACHE, NEW_K, NEW_V, BLOCK_TABLE, seq_len - 1, 1, stream);
 }
 extern "C" void kivi_b200_cache_write_batched_launch(unsigned char* K_CODE_PAGES, kivi_f16* K_SCALE_PAGES,
@@ -625,6 +631,7 @@ extern "C" void kivi_b200_cache_write_batched_launch(unsigned char* K_CODE_PAGES
                                                      cudaStream_t stream) {
     (void)SLOT_MAPPING;
     if (NUM_NEW < 1) return;
+    if (NKV_RUNTIME < 1) { fprintf(stderr, "NKV_RUNTIME out of range for kivi_cache_write_batched_launch: %d\n", NKV_RUNTIME); exit(1); }
     ref_write(NKV_RUNTIME, KIVI_V1_CACHE, NEW_K, NEW_V, BLOCK_TABLE, START_SEQ_LEN, NUM_NEW, stream);
 }
 

@@ -46,6 +46,9 @@ struct DynamicShape {
     static constexpr bool in_registers = false;
 };
 
+// Sequences whose write was refused because a slot or page id lay outside the pools (since the library was loaded).
+__device__ unsigned int g_writer_rejected;
+
 struct SeqWrite {
     int start, num_new, end, prev_old, next_old, new_row0, slot;
     const int* bt;
@@ -68,6 +71,18 @@ __device__ __forceinline__ SeqWrite seq_write(const WriteParams& p, int i) {
     s.next_old = split_old(s.end, p.geom.r, p.geom.g);
     s.slot = slot_of(p.seq, i);
     s.bt = p.seq.block_tables + (size_t)i * p.seq.bt_stride;
+    // Ids from device memory become addresses: the slot and every page this write packs into must lie in the
+    // pools. A sequence that fails is left untouched by all of its CTAs (they all see the same ids) and counted.
+    // The threads of the CTA share the page ids between them (every thread of the CTA calls this function).
+    bool ok = index_in_pool(s.slot, p.cache.num_slots);
+    const int page0 = s.prev_old / p.geom.b, page1 = s.next_old / p.geom.b;
+    for (int lp = page0 + (int)threadIdx.x; lp < page1; lp += (int)blockDim.x)
+        ok = ok && lp < p.seq.bt_width && index_in_pool(s.bt[lp], p.cache.num_blocks);
+    ok = __syncthreads_and(ok ? 1 : 0) != 0;
+    if (!ok) {
+        if (threadIdx.x == 0 && blockIdx.x == 0 && s.num_new > 0) atomicAdd(&g_writer_rejected, 1u);
+        s.num_new = 0; s.end = s.start; s.next_old = s.prev_old; s.slot = 0;
+    }
     return s;
 }
 
@@ -848,3 +863,8 @@ cudaError_t launch_cache_write(const WriteParams& p, int max_new_per_seq, cudaSt
 }
 
 }  // namespace kivi
+
+extern "C" int kivi_b200_writer_rejected_indices(uint32_t* count) {
+    if (!count) return KIVI_ERR_NULL_POINTER;
+    return cudaMemcpyFromSymbol(count, kivi::g_writer_rejected, sizeof(uint32_t)) == cudaSuccess ? KIVI_OK : KIVI_ERR_CUDA;
+}

@@ -15,6 +15,7 @@ namespace kivi {
 namespace {
 
 constexpr int kMaxBytesPerLane = 4;  // head_dim <= 256
+__device__ unsigned int g_generic_rejected;   // page / slot ids outside the pools, replaced by id 0
 
 __global__ void __launch_bounds__(256) decode_generic_kernel(const DecodeParams p) {
     const Geom& g = p.geom;
@@ -31,7 +32,8 @@ __global__ void __launch_bounds__(256) decode_generic_kernel(const DecodeParams 
     const bool with_residual = work.with_residual;
 
     const int* bt = p.seq.block_tables + (size_t)i * p.seq.bt_stride;
-    const int slot = slot_of(p.seq, i);
+    int slot = slot_of(p.seq, i);
+    if (!index_in_pool(slot, p.cache.num_slots)) { slot = 0; if (threadIdx.x == 0) atomicAdd(&g_generic_rejected, 1u); }
     const int bytes_per_row = g.d / 2;
     const float score_scale = rsqrtf((float)g.d) * 1.4426950408889634f;
 
@@ -56,7 +58,8 @@ __global__ void __launch_bounds__(256) decode_generic_kernel(const DecodeParams 
 
         for (int s = t0; s < t1; ++s) {
             const int lp = s / g.b, off = s - lp * g.b;
-            const int page = bt[lp];
+            int page = bt[lp];
+            if (!index_in_pool(page, p.cache.num_blocks)) { page = 0; if (lane == 0 && off == 0) atomicAdd(&g_generic_rejected, 1u); }
             const size_t head_base = (size_t)page * g.nkv + kv;
             if (page != cur_page) {
                 cur_page = page;
@@ -170,6 +173,10 @@ __global__ void __launch_bounds__(256) decode_generic_kernel(const DecodeParams 
 }
 
 }  // namespace
+
+cudaError_t decode_generic_rejected(unsigned int* count) {
+    return cudaMemcpyFromSymbol(count, g_generic_rejected, sizeof(unsigned int));
+}
 
 cudaError_t launch_decode_generic(const DecodeParams& p, cudaStream_t stream) {
     if (p.n <= 0) return cudaSuccess;

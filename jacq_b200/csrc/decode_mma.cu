@@ -7,20 +7,26 @@
 // one warp per query head and re-reads every K/V byte once per query head of the group; here one
 // CTA serves all query heads of a kv head, so each byte is read once.
 //
-// Work split: grid (context chunk, kv head, sequence). A CTA's key groups go round-robin to its
-// warps; each warp keeps its own online-softmax state, the states are merged in shared memory at
-// the end, and across chunks by the last CTA to arrive. The last chunk also takes the residual
-// rows, in 16-row tiles.
+// Work split: one CTA per job. A job is a (sequence, kv head) unit or, where the host's launch plan cuts units,
+// one of the k parts of a unit (JobPlan in kivi_common.cuh; the plan and the measurements behind it are in
+// api.cu). A part owns a run of the unit's key groups and/or of the 16-row tiles of its fp16 residual, chosen by
+// weight so that parts move equal bytes (decode_merge.cuh). A CTA's key groups go round-robin to its warps, its
+// residual tiles to the least loaded warps; each warp keeps its own online-softmax state and the states are
+// merged in shared memory at the end. A whole unit then writes its output; a part leaves a partial
+// (maximum, sum, accumulator) in the workspace and a second, small kernel (decode_merge.cu) combines the
+// parts of every cut unit. No CTA ever waits for another.
 //
 // Data movement: every warp owns a small ring of shared-memory slots of 64 tokens each (codes of
 // K and V, the value scale/zero of those tokens, and with the first slot of a group its key
-// scale/zero). Code pages arrive by 1-D bulk asynchronous copies (cp.async.bulk, the TMA engine
-// without a tensor map: a page is contiguous per kv head); the small parameter arrays and the fp16
-// residual rows arrive by 16-byte cp.async, one warp instruction for a whole slot. Both complete on
-// the slot's mbarrier. A warp fills its own slots and is the only one to wait on them: after
-// draining a slot it issues the copies of the slot-count-th next one into it, so there is no
-// "empty" barrier and no cross-warp synchronisation until the final merge, every warp keeps
-// several slots in flight, and no registers are spent on staging.
+// scale/zero). Everything arrives by 16-byte cp.async, one warp instruction per 512 contiguous bytes of a
+// page (1-D bulk copies were measured slower here: a page is only 1 KB per kv head, and every bulk copy
+// costs about ten issue slots of address and uniform-register work), completing on the slot's mbarrier.
+// Value codes are stored with their 16-byte columns swizzled so that ldmatrix reads them without bank
+// conflicts. A warp fills its own slots and is the only one to wait on them: after draining a slot it
+// issues the copies of the slot-count-th next one into it, so there is no "empty" barrier and no
+// cross-warp synchronisation until the final merge, every warp keeps several slots in flight, and no
+// registers are spent on staging. Every wait is bounded; a CTA whose wait ran out drains its copies, counts
+// itself (kivi_b200_decode_wait_failures) and leaves.
 //
 // Arithmetic on codes: a 32-bit word holds 8 channels of one token. Masking a word with
 // 0x000f000f / 0x00f000f0 leaves two nibbles in fp16 *subnormal* position: the pair (n_i, n_i+4)
@@ -31,8 +37,9 @@
 //          to even out the two nibble positions) and the zero-point term is one extra MMA set.
 //          Channels are contracted, so the odd pairing (i, i+4) only permutes the contraction.
 //   PV:    sum_s p_s (vs_s n_sd + vz_s) = sum_s (p_s vs_s) n_sd + sum_s p_s vz_s. Tokens are
-//          contracted, so a byte-permute first interleaves the same word of two tokens; the
-//          2^-24 / 2^-20 factors land on output channels and are undone in the epilogue.
+//          contracted, so the A fragment wants the same 16-bit word of two consecutive tokens side by side:
+//          ldmatrix.trans over the token rows delivers exactly that; the 2^-24 / 2^-20 factors land on
+//          output channels and are undone in the epilogue.
 // MMA shape m16n8k16 (fp16 in, fp32 accumulate): M = 16 tokens (QK^T) or 16 channels (PV),
 // N = 8 query heads of the group (up to 8 used), so the tensor work wasted on padding is at most
 // 2x for a group of 4. The score tile comes out token-major and is turned head-major for PV by
@@ -56,6 +63,8 @@ constexpr int kSubMax = KIVI_SUB;        // tokens per ring slot (never more tha
 constexpr int kBarBytes = 512;           // room for 64 mbarriers
 // Bounded waits that ran out, over the life of the process (kivi_b200_decode_wait_failures reads it).
 __device__ unsigned int g_decode_wait_failures;
+// Page or slot ids outside the pools that this kernel met and replaced by id 0 (kivi_b200_decode_rejected_indices).
+__device__ unsigned int g_decode_rejected;
 constexpr int kMaxSlotsPerWarp = 4;
 constexpr int kBarArrivals = 33;         // lane 0's expect_tx arrive + one cp.async arrive per lane
 constexpr float kLog2e = 1.4426950408889634f;
@@ -216,7 +225,8 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
     const uint32_t v_stage_off = (uint32_t)((lane & ~(C::VCOLS - 1)) | ((lane & (C::VCOLS - 1)) ^ ((lane >> 3) & (C::VCOLS - 1)))) * 16u;
     const uint32_t page_stride32 = (uint32_t)page_stride;
     const int* bt = p.seq.block_tables + (size_t)i * p.seq.bt_stride;
-    const int slot = slot_of(p.seq, i);
+    int slot = slot_of(p.seq, i);
+    if (!index_in_pool(slot, p.cache.num_slots)) { slot = 0; if (threadIdx.x == 0) atomicAdd(&g_decode_rejected, 1u); }
     const uint8_t* kc_lane = p.cache.k_code + (size_t)kv * page_code_bytes + lane * 16;
     const uint8_t* vc_lane = p.cache.v_code + (size_t)kv * page_code_bytes + lane * 16;
     const __half* k_res = p.cache.k_scratch + ((size_t)slot * g.nkv + kv) * g.scratch_rows * D;
@@ -256,7 +266,8 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
             const int tokbase = i_grp * G + i_sub * kSub;
             const int lp = tokbase >> logb;
             // the slot's page ids: lanes 0..PB-1 fetch them, shuffles hand them round
-            const int my_page = lane < PB ? bt[lp + lane] : 0;
+            int my_page = lane < PB ? bt[lp + lane] : 0;
+            if (!index_in_pool(my_page, p.cache.num_blocks)) { my_page = 0; atomicAdd(&g_decode_rejected, 1u); }
             uint32_t pg[PB];
 #pragma unroll
             for (int j = 0; j < PB; ++j) pg[j] = (uint32_t)__shfl_sync(0xffffffffu, my_page, j);
@@ -728,6 +739,15 @@ cudaError_t launch_decode_mma(const DecodeParams& p, cudaStream_t stream) {
 extern "C" int kivi_b200_decode_wait_failures(uint32_t* count) {
     if (!count) return KIVI_ERR_NULL_POINTER;
     return cudaMemcpyFromSymbol(count, kivi::g_decode_wait_failures, sizeof(unsigned int)) == cudaSuccess ? KIVI_OK : KIVI_ERR_CUDA;
+}
+
+extern "C" int kivi_b200_decode_rejected_indices(uint32_t* count) {
+    if (!count) return KIVI_ERR_NULL_POINTER;
+    unsigned int mine = 0, generic = 0;
+    if (cudaMemcpyFromSymbol(&mine, kivi::g_decode_rejected, sizeof(unsigned int)) != cudaSuccess) return KIVI_ERR_CUDA;
+    if (kivi::decode_generic_rejected(&generic) != cudaSuccess) return KIVI_ERR_CUDA;
+    *count = mine + generic;
+    return KIVI_OK;
 }
 
 #ifdef KIVI_DECODE_TRACE

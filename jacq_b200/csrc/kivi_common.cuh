@@ -48,7 +48,16 @@ struct CachePtrs {
     uint8_t* k_code; __half* k_scale; __half* k_zero;
     uint8_t* v_code; __half* v_scale; __half* v_zero;
     __half* k_scratch; __half* v_scratch;
+    // Pages in the pools and scratch slots, where the caller stated them (ABI v2); INT_MAX for the reference-lane
+    // symbols, whose signatures carry no sizes. Page ids and slot ids read from device memory are held against them.
+    int num_blocks, num_slots;
 };
+
+// A page or slot id read from device memory is used as an address only when it lies inside the pool. A block
+// table entry that is stale or garbage would otherwise become an out-of-bounds access; ids that fail are counted
+// (kivi_b200_rejected_indices) and the access is skipped (writer: the whole sequence's write) or redirected to
+// id 0 (decode: the output of that sequence is then meaningless, but nothing outside the pool is touched).
+__host__ __device__ inline bool index_in_pool(int id, int pool_size) { return (unsigned)id < (unsigned)pool_size; }
 
 // How a launch finds each sequence's length, block-table row and scratch slot. The v1 symbols
 // pass host scalars and one shared table; the v2 calls pass device arrays.
@@ -340,6 +349,7 @@ int run_decode(const Geom& g, const CachePtrs& cache, const SeqAddressing& seq, 
                size_t ws_bytes, cudaStream_t stream, const int* retained_dev = nullptr);
 size_t decode_workspace_total(const Geom& g, int n, int max_old_tokens);
 cudaError_t launch_decode_generic(const DecodeParams& p, cudaStream_t stream);
+cudaError_t decode_generic_rejected(unsigned int* count);
 cudaError_t launch_decode_mma(const DecodeParams& p, cudaStream_t stream);
 bool decode_mma_supports(const Geom& g, int retained_pages);
 int decode_mma_ctas_per_sm();

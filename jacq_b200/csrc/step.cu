@@ -341,6 +341,7 @@ CachePtrs to_ptrs(const kivi_cache& c) {
     o.v_zero = reinterpret_cast<__half*>(c.v_zero_pages);
     o.k_scratch = reinterpret_cast<__half*>(c.k_residual_scratch);
     o.v_scratch = reinterpret_cast<__half*>(c.v_residual_scratch);
+    o.num_blocks = c.num_blocks; o.num_slots = c.num_slots;
     return o;
 }
 

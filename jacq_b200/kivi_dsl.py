@@ -32,34 +32,65 @@ CACHE_WRITE_KERNEL_ENV = "JAC_KIVI_CACHE_WRITE_KERNEL"
 _GEOMETRIES = {(40, 8): "", (20, 4): "_tp2_local"}
 
 
+_WRITER_ALIASES = {"hand_cuda": ("hand_cuda", "hand", "cuda", "legacy"), "jac_dsl": ("jac_dsl", "jac", "dsl")}
+_CODE_TENSORS = ("K_CODE_PAGES", "V_CODE_PAGES")
+
+
 def cache_write_kernel_source() -> str:
     """Which single-token writer entry point serves: ``hand_cuda`` (default) or ``jac_dsl``.
 
-    Same selector and fail-closed parsing as the reference (source_patch.py:67-85). Both names
-    resolve to the same B200 kernels here; the selector picks the C symbol
-    (``kivi_b200_cache_write_launch`` vs ``jac_launch_cache_write``)."""
+    The environment variable, its accepted spellings and the fail-closed error are the reference's
+    (source_patch.py:67-85). Both names resolve to the same B200 kernels here; the selector picks the
+    C symbol (``kivi_b200_cache_write_launch`` vs ``jac_launch_cache_write``)."""
     raw = os.environ.get(CACHE_WRITE_KERNEL_ENV, "hand_cuda")
-    normalized = raw.strip().lower().replace("-", "_")
-    if normalized in ("hand_cuda", "hand", "cuda", "legacy"):
-        return "hand_cuda"
-    if normalized in ("jac_dsl", "jac", "dsl"):
-        return "jac_dsl"
+    key = raw.strip().lower().replace("-", "_")
+    for canonical, spellings in _WRITER_ALIASES.items():
+        if key in spellings:
+            return canonical
     raise ValueError(f"{CACHE_WRITE_KERNEL_ENV} must be hand_cuda or jac_dsl, got {raw!r}")
 
 
 def validate_kivi_cache_bundle(cache: Mapping[str, Any]) -> None:
+    """Kind tag, presence and dtype of the eight cache tensors (the checks of source_patch.py:210-226, in
+    the same order, with the same exception types and messages)."""
     if cache.get("kind") != KIVI_CACHE_KIND:
         raise TypeError("expected GPUModelRunner int4_kivi_dsl_paged cache bundle")
-    missing = [name for name in _CACHE_TENSORS if name not in cache]
-    if missing:
-        raise KeyError(f"KIVI cache bundle missing tensors: {missing}")
-    for name in ("K_CODE_PAGES", "V_CODE_PAGES"):
-        if cache[name].dtype != torch.uint8:
-            raise TypeError(f"{name} must be torch.uint8 packed int4")
-    for name in ("K_SCALE_PAGES", "K_ZERO_PAGES", "V_SCALE_PAGES", "V_ZERO_PAGES", "K_RESIDUAL_SCRATCH",
-                 "V_RESIDUAL_SCRATCH"):
-        if cache[name].dtype != torch.float16:
-            raise TypeError(f"{name} must be torch.float16")
+    absent = [name for name in _CACHE_TENSORS if name not in cache]
+    if absent:
+        raise KeyError(f"KIVI cache bundle missing tensors: {absent}")
+    for wanted, names, suffix in ((torch.uint8, _CODE_TENSORS, "torch.uint8 packed int4"),
+                                  (torch.float16, tuple(n for n in _CACHE_TENSORS if n not in _CODE_TENSORS), "torch.float16")):
+        for name in names:
+            if cache[name].dtype != wanted:
+                raise TypeError(f"{name} must be {suffix}")
+
+
+def _require_dtype(tensor: torch.Tensor, dtype: torch.dtype, message: str) -> None:
+    if tensor.dtype != dtype:
+        raise TypeError(message)
+
+
+def _check_decode_io(q: torch.Tensor, table: torch.Tensor, out: torch.Tensor, table_name: str) -> None:
+    _require_dtype(table, torch.int32, f"{table_name} must be torch.int32")
+    _require_dtype(q, torch.float16, "Q must be torch.float16")
+    _require_dtype(out, torch.float32, "O must be torch.float32")
+
+
+def _check_write_io(key: torch.Tensor, value: torch.Tensor, slot_mapping: torch.Tensor, block_table: torch.Tensor) -> None:
+    if not (key.dtype == value.dtype == torch.float16):
+        raise TypeError("KIVI cache write expects fp16 key/value tensors")
+    _require_dtype(slot_mapping, torch.int64, "KIVI cache write expects int64 slot_mapping")
+    _require_dtype(block_table, torch.int32, "KIVI cache write expects int32 block_table")
+
+
+def _check_launch_order(cache: Mapping[str, Any]) -> None:
+    if tuple(cache.get("jac_launch_order", ())) != JAC_LAUNCH_ORDER:
+        raise RuntimeError("int4_kivi cache bundle has stale jac_launch_order")
+
+
+def _check_seq_len(seq_len: int) -> None:
+    if not 1 <= seq_len <= MAX_SEQ_LEN:
+        raise ValueError("SEQ_LEN must be in [1, 4096] for the first KIVI DSL lane")
 
 
 def make_cache_bundle(num_blocks: int, *, num_kv_heads: int = 8, device: torch.device | str = "cuda",
@@ -158,20 +189,14 @@ class KiviDslLaunchBinding:
     out: torch.Tensor
 
     def jac_launch_args(self) -> tuple[Any, ...]:
+        """The arguments in launch order, after the bundle, dtype, length and one-device checks."""
         validate_kivi_cache_bundle(self.cache)
-        if tuple(self.cache.get("jac_launch_order", ())) != JAC_LAUNCH_ORDER:
-            raise RuntimeError("int4_kivi cache bundle has stale jac_launch_order")
-        if self.block_table.dtype != torch.int32:
-            raise TypeError("BLOCK_TABLE must be torch.int32")
-        if self.q.dtype != torch.float16:
-            raise TypeError("Q must be torch.float16")
-        if self.out.dtype != torch.float32:
-            raise TypeError("O must be torch.float32")
-        if self.seq_len < 1 or self.seq_len > MAX_SEQ_LEN:
-            raise ValueError("SEQ_LEN must be in [1, 4096] for the first KIVI DSL lane")
-        tensors = (self.q, self.block_table) + tuple(self.cache[name] for name in _CACHE_TENSORS) + (self.out,)
-        _one_device(tensors, "KIVI jac_launch", require_cuda=False)
-        return tensors[:-1] + (self.seq_len, self.out)
+        _check_launch_order(self.cache)
+        _check_decode_io(self.q, self.block_table, self.out, "BLOCK_TABLE")
+        _check_seq_len(self.seq_len)
+        pools = tuple(self.cache[name] for name in _CACHE_TENSORS)
+        _one_device((self.q, self.block_table, self.out) + pools, "KIVI jac_launch", require_cuda=False)
+        return (self.q, self.block_table) + pools + (self.seq_len, self.out)
 
 
 def launch_kivi_dsl_decode(q: torch.Tensor, block_table: torch.Tensor, cache: Mapping[str, Any], out: torch.Tensor,
@@ -197,16 +222,9 @@ def launch_kivi_dsl_decode_batched(q: torch.Tensor, seq_lens: torch.Tensor, bloc
     (reference: source_patch.py:412-485 -> ``jac_launch_batched``). Like the reference this reads
     SEQ_LENS back to the host to bound the values before launching."""
     validate_kivi_cache_bundle(cache)
-    if tuple(cache.get("jac_launch_order", ())) != JAC_LAUNCH_ORDER:
-        raise RuntimeError("int4_kivi cache bundle has stale jac_launch_order")
-    if block_table.dtype != torch.int32:
-        raise TypeError("BLOCK_TABLE must be torch.int32")
-    if q.dtype != torch.float16:
-        raise TypeError("Q must be torch.float16")
-    if out.dtype != torch.float32:
-        raise TypeError("O must be torch.float32")
-    if seq_lens.dtype != torch.int32:
-        raise TypeError("SEQ_LENS must be torch.int32")
+    _check_launch_order(cache)
+    _check_decode_io(q, block_table, out, "BLOCK_TABLE")
+    _require_dtype(seq_lens, torch.int32, "SEQ_LENS must be torch.int32")
     if num_queries < 1 or num_queries > MAX_QUERIES:
         raise ValueError(f"NUM_QUERIES must be in [1, {MAX_QUERIES}]")
     lens = [int(v) for v in seq_lens.detach().cpu().tolist()]
@@ -232,18 +250,12 @@ def launch_kivi_dsl_decode_sparse_retained(q: torch.Tensor, retained_block_table
     ``jac_launch_sparse_retained``); the serving telemetry the reference writes around the call is
     not part of the kernel path and is left to the caller."""
     validate_kivi_cache_bundle(cache)
-    if retained_block_table.dtype != torch.int32:
-        raise TypeError("RETAINED_BLOCK_TABLE must be torch.int32")
-    if q.dtype != torch.float16:
-        raise TypeError("Q must be torch.float16")
-    if out.dtype != torch.float32:
-        raise TypeError("O must be torch.float32")
+    _check_decode_io(q, retained_block_table, out, "RETAINED_BLOCK_TABLE")
     if retained_block_table.numel() != OLD_BLOCKS:
         raise ValueError(f"RETAINED_BLOCK_TABLE must have {OLD_BLOCKS} entries")
     if num_retained_pages < 0 or num_retained_pages > OLD_BLOCKS:
         raise ValueError("NUM_RETAINED_PAGES must be in [0, OLD_BLOCKS]")
-    if seq_len < 1 or seq_len > MAX_SEQ_LEN:
-        raise ValueError("SEQ_LEN must be in [1, 4096] for the first KIVI DSL lane")
+    _check_seq_len(seq_len)
     nkv, suffix = _check_cache_shapes(cache)
     _one_device((q, retained_block_table, out) + tuple(cache[n] for n in _CACHE_TENSORS), "KIVI sparse jac_launch")
     fn = getattr(_native.lib(), "jac_launch_sparse_retained" + suffix)
@@ -256,20 +268,13 @@ def require_kivi_cache_write(key: torch.Tensor, value: torch.Tensor, slot_mappin
     """Write one token's K/V; ``seq_len`` is the length after it (reference:
     source_patch.py:228-291 -> ``kivi_cache_write_dsl`` / ``kivi_cache_write_jac_dsl``)."""
     validate_kivi_cache_bundle(cache)
-    if key.dtype != torch.float16 or value.dtype != torch.float16:
-        raise TypeError("KIVI cache write expects fp16 key/value tensors")
-    if slot_mapping.dtype != torch.int64:
-        raise TypeError("KIVI cache write expects int64 slot_mapping")
-    if block_table.dtype != torch.int32:
-        raise TypeError("KIVI cache write expects int32 block_table")
-    residual = cache["K_RESIDUAL_SCRATCH"]
-    expected = tuple(residual.shape[0:1]) + tuple(residual.shape[2:3])
-    new_k = key.reshape(-1, residual.shape[-1]).contiguous()
-    new_v = value.reshape(-1, residual.shape[-1]).contiguous()
-    if tuple(new_k.shape) != expected:
-        raise RuntimeError("KIVI key tensor does not match residual [num_kv_heads, head_size]")
-    if tuple(new_v.shape) != expected:
-        raise RuntimeError("KIVI value tensor does not match residual [num_kv_heads, head_size]")
+    _check_write_io(key, value, slot_mapping, block_table)
+    heads, _, head_size = cache["K_RESIDUAL_SCRATCH"].shape
+    new_k = key.reshape(-1, head_size).contiguous()
+    new_v = value.reshape(-1, head_size).contiguous()
+    for label, rows in (("key", new_k), ("value", new_v)):
+        if tuple(rows.shape) != (heads, head_size):
+            raise RuntimeError(f"KIVI {label} tensor does not match residual [num_kv_heads, head_size]")
     tensors = tuple(cache[name] for name in _CACHE_TENSORS) + (new_k, new_v, slot_mapping, block_table)
     dev = _one_device(tensors, "KIVI cache-write")
     nkv, _ = _check_cache_shapes(cache)
@@ -292,12 +297,7 @@ def require_kivi_cache_write_batched(key: torch.Tensor, value: torch.Tensor, slo
     pre-split with ``plan_batched_write``; this writer also takes a chunk that crosses several
     age-out boundaries, as long as it fits the call's bound of 160 rows."""
     validate_kivi_cache_bundle(cache)
-    if key.dtype != torch.float16 or value.dtype != torch.float16:
-        raise TypeError("KIVI cache write expects fp16 key/value tensors")
-    if slot_mapping.dtype != torch.int64:
-        raise TypeError("KIVI cache write expects int64 slot_mapping")
-    if block_table.dtype != torch.int32:
-        raise TypeError("KIVI cache write expects int32 block_table")
+    _check_write_io(key, value, slot_mapping, block_table)
     if num_new < 1 or num_new > RESIDUAL + BLOCK_SIZE:
         raise ValueError(f"NUM_NEW must be in [1, {RESIDUAL + BLOCK_SIZE}]")
     if start_seq_len < 0 or start_seq_len + num_new > MAX_SEQ_LEN:
@@ -322,11 +322,22 @@ def _split_old_tokens_batched(seq_len: int, residual: int, block_size: int) -> i
 
 @dataclass(frozen=True)
 class KiviWriteSubChunk:
+    """One piece of a planned chunk (field names are the reference's, source_patch.py:488-501): the piece appends
+    ``num_new`` rows at scratch row ``scratch_start``; when it fills the scratch, ``age_out_page`` is the logical
+    page (key group) that is quantised and ``post_shift_residual_len`` the rows left afterwards."""
     start_seq_len: int
     num_new: int
     scratch_start: int
     age_out_page: int | None
     post_shift_residual_len: int | None
+
+    @property
+    def crosses_boundary(self) -> bool:
+        return self.age_out_page is not None
+
+    @property
+    def end_seq_len(self) -> int:
+        return self.start_seq_len + self.num_new
 
 
 def plan_batched_write(start_seq_len: int, num_new_tokens: int, residual: int = 128,

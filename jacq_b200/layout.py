@@ -53,21 +53,21 @@ class KiviPageLayout:
 
     # ---- validation -------------------------------------------------------------------------
     def validate_for_vllm_lane(self) -> None:
-        """The reference lane's rules (layout.py:51-69 of the reference), unchanged."""
-        if self.nbits != 4:
-            raise ValueError(f"first KIVI lane is int4 only, got nbits={self.nbits}")
-        if self.block_size != self.group_size:
-            raise ValueError(
-                "KIVI key grouping must not straddle vLLM pages in the first serving lane; "
-                f"require block_size==group_size, got {self.block_size}!={self.group_size}")
-        if self.block_size != 32:
-            raise ValueError(f"first vLLM KIVI lane requires block_size=32, got {self.block_size}")
-        if self.geometry.head_dim % self.group_size:
-            raise ValueError(
-                f"head_dim={self.geometry.head_dim} must be divisible by group_size={self.group_size}")
-        if self.residual_tokens % self.block_size:
-            raise ValueError(
-                f"residual_tokens={self.residual_tokens} must be page-aligned for the first lane")
+        """The reference lane's rules (layout.py:51-69 of the reference), with its messages."""
+        d = self.geometry.head_dim
+        rules = (
+            (self.nbits == 4, f"first KIVI lane is int4 only, got nbits={self.nbits}"),
+            (self.block_size == self.group_size,
+             "KIVI key grouping must not straddle vLLM pages in the first serving lane; "
+             f"require block_size==group_size, got {self.block_size}!={self.group_size}"),
+            (self.block_size == 32, f"first vLLM KIVI lane requires block_size=32, got {self.block_size}"),
+            (d % self.group_size == 0, f"head_dim={d} must be divisible by group_size={self.group_size}"),
+            (self.residual_tokens % self.block_size == 0,
+             f"residual_tokens={self.residual_tokens} must be page-aligned for the first lane"),
+        )
+        for holds, message in rules:
+            if not holds:
+                raise ValueError(message)
 
     def validate_for_b200_lane(self) -> None:
         """Rules of the generalised layout the B200 library implements (ABI v2)."""
@@ -172,21 +172,18 @@ class KiviPageLayout:
         return g.num_kv_heads * per_head + math.ceil(t_old / self.block_size) * 4
 
     def to_abi_dict(self, seq_len: int = 4096) -> dict[str, object]:
+        """The layout as the ABI report carries it (keys of the reference's report, layout.py:134-154, plus the
+        decode bytes)."""
         self.validate_for_b200_lane()
-        return {
-            "geometry": asdict(self.geometry),
-            "block_size": self.block_size,
-            "group_size": self.group_size,
-            "nbits": self.nbits,
-            "residual_tokens": self.residual_tokens,
-            "fp16_page_bytes_per_layer": self.fp16_page_bytes_per_layer,
-            "quantized_page_bytes_per_layer": self.quantized_page_bytes_per_layer,
-            "key_code_bytes": self.code_page_bytes_per_component,
-            "value_code_bytes": self.code_page_bytes_per_component,
-            "key_scale_zero_bytes": self.key_param_page_bytes,
-            "value_scale_zero_bytes": self.value_param_page_bytes,
-            "residual_pages": self.residual_pages,
-            "effective_bytes_per_token_all_layers_at_seq_len": self.effective_bytes_per_token_all_layers(seq_len),
-            "capacity_ratio_vs_fp16_at_seq_len": self.capacity_ratio_vs_fp16(seq_len),
-            "decode_algorithmic_bytes_at_seq_len": self.decode_algorithmic_bytes(seq_len),
-        }
+        out: dict[str, object] = {"geometry": asdict(self.geometry)}
+        for name in ("block_size", "group_size", "nbits", "residual_tokens", "fp16_page_bytes_per_layer",
+                     "quantized_page_bytes_per_layer"):
+            out[name] = getattr(self, name)
+        out["key_code_bytes"] = out["value_code_bytes"] = self.code_page_bytes_per_component
+        out["key_scale_zero_bytes"] = self.key_param_page_bytes
+        out["value_scale_zero_bytes"] = self.value_param_page_bytes
+        out["residual_pages"] = self.residual_pages
+        out["effective_bytes_per_token_all_layers_at_seq_len"] = self.effective_bytes_per_token_all_layers(seq_len)
+        out["capacity_ratio_vs_fp16_at_seq_len"] = self.capacity_ratio_vs_fp16(seq_len)
+        out["decode_algorithmic_bytes_at_seq_len"] = self.decode_algorithmic_bytes(seq_len)
+        return out

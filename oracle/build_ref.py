@@ -84,8 +84,18 @@ def build(reference: Path) -> Path | None:
     return lib
 
 
+def find_reference() -> Path | None:
+    """The reference checkout: $JACQ_REFERENCE, else a directory named `reference` beside this repository."""
+    for cand in (os.environ.get("JACQ_REFERENCE"), HERE.parent.parent / "reference"):
+        if cand and (Path(cand) / SNAP).is_dir():
+            return Path(cand)
+    return None
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("JACQ_REFERENCE", "/root/reference"))
-    out = build(Path(ap.parse_args().reference))
-    print(out if out else "skipped")
+    ap.add_argument("--reference", default=None, help="reference checkout (default: $JACQ_REFERENCE or ../reference)")
+    chosen = ap.parse_args().reference
+    ref = Path(chosen) if chosen else find_reference()
+    out = build(ref) if ref else None
+    print(out if out else "skipped: no reference checkout found")

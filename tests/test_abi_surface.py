@@ -148,3 +148,21 @@ def test_v2_interface_and_host_only_calls(native_lib):
     # argument validation happens on the host, before anything is launched
     assert native_lib.kivi_b200_gemv_f16(None, None, None, None, 8, 8, 1, None) == 1
     assert native_lib.kivi_b200_decode(ctypes.byref(g), None, None, None, 0, None, None, 1, 1, None, None, 0, None) == 1
+
+
+def test_v1_writer_symbols_refuse_a_non_positive_head_count(native_lib):
+    """NKV_RUNTIME <= 0 is refused with a message and exit(1) before anything is computed from it (the reference
+    would report an invalid launch configuration, integrations/vllm_kivi/source_patch.py:1661-1697). Run in a
+    child process, since the v1 contract is print-and-exit; no GPU is touched."""
+    import sys
+    code = (
+        "import ctypes, sys\n"
+        f"lib = ctypes.CDLL({str(_native.LIB_PATH)!r})\n"
+        "null = ctypes.c_void_p(0)\n"
+        "args = [null] * 12 + [ctypes.c_int(200), ctypes.c_int(int(sys.argv[1])), null]\n"
+        "lib.kivi_b200_cache_write_launch(*args)\n"
+        "print('returned')\n")
+    for nkv in (0, -3):
+        proc = subprocess.run([sys.executable, "-c", code, str(nkv)], capture_output=True, text=True, timeout=120)
+        assert proc.returncode == 1, (proc.returncode, proc.stdout, proc.stderr)
+        assert "NKV_RUNTIME out of range" in proc.stderr and "returned" not in proc.stdout

@@ -108,3 +108,12 @@ def test_noalloc_decode_refuses_what_the_fixed_array_cannot_hold(native_lib):
         batch, max_len, ctypes.c_void_p(out.data_ptr()), None)
     assert rc == 5 and _native.STATUS_NAMES[rc] == "KIVI_ERR_WORKSPACE"
     assert b"workspace" in native_lib.kivi_b200_status_string(rc)
+
+
+def test_zz_no_bounded_wait_gave_up_in_this_process(native_lib):
+    """Every wait inside the kernels is bounded and counts itself when it gives up. After everything this
+    process ran (the whole suite when it is run in one go) both counters must read zero."""
+    for fn in (native_lib.kivi_b200_decode_wait_failures, native_lib.kivi_b200_gemm_wait_failures):
+        out = ctypes.c_uint32(123)
+        assert fn(ctypes.byref(out)) == 0
+        assert out.value == 0, fn.__name__
