@@ -1139,7 +1139,7 @@ def run_reference(args):
     geom = helpers.oracle_geometry(case)
     lay = helpers.layout_of(case)
     nthreads = os.cpu_count() or 1
-    n = min(batch, max(1, nthreads // 8))
+    n = min(batch, max(1, nthreads))      # one sequence per host thread and step: about half a second of CPU work
     pages = lay.old_pages(context) + 1
     tables = helpers.shuffled_block_tables(n, pages, n * pages)
     oc = ko.OracleCache(geom, n * pages, n)
@@ -1149,7 +1149,7 @@ def run_reference(args):
     qh = helpers.make_q(case, n)
     lens = np.full(n, context, np.int32)
     step_bytes = lay.decode_algorithmic_bytes(context) * n
-    warm = min(args.warmup, 1)
+    warm = args.warmup
     for _ in range(warm):
         ko.decode_batch(oc, qh, tables, lens, mode=0, nthreads=nthreads)
     t0 = time.perf_counter()
