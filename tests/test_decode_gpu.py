@@ -255,3 +255,22 @@ def test_v2_sparse_retained_per_sequence(native_lib, name):
         compact[: len(keep)] = tables[i, keep]
         want = ko.decode(oc, q[i], compact, int(t), slot=i, mode=0, num_retained_pages=len(keep))
         _check(got[i], want, f"{name} sequence {i} ({len(keep)} of {dense_pages} pages kept)")
+
+
+@pytest.mark.parametrize("name,batch", [("mistral7b", 3), ("tinyllama", 4)])
+def test_v2_decode_fp16_output_is_the_rounded_fp32_output(native_lib, name, batch):
+    """kivi_b200_decode_f16 runs the same kernels and rounds only the final store: its output equals the fp32
+    output rounded to fp16, for a launch that is cut into parts (merge kernel) as well as for whole units."""
+    from tests.gpu_utils import DEV, f16_tensor, upload
+    case = helpers.CONFIGS[name]
+    seq_lens = np.full(batch, case.context, np.int32)
+    geom, oc, tables, slots = _build_oracle_cache(case, seq_lens)
+    q = f16_tensor(helpers.make_q(case, batch))
+    cache = upload(oc, case, tables.shape[1])
+    cache.set_block_tables(torch.from_numpy(tables))
+    cache.seq_lens.copy_(torch.from_numpy(seq_lens))
+    out32 = cache.decode(q, max_seq_len=case.context)
+    out16 = cache.decode(q, torch.empty(q.shape, dtype=torch.float16, device=DEV), max_seq_len=case.context)
+    torch.cuda.synchronize()
+    assert out16.dtype == torch.float16
+    assert torch.equal(out16, out32.to(torch.float16))
