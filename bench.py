@@ -395,8 +395,8 @@ def run_b200(args):
         peak, peak_kind = _peaks()
         kernel_ms = statistics.mean(per_step_ms)
         achieved = step_bytes / (kernel_ms * 1e-3) / 1e9
-        # DRAM bytes per launch: one ncu capture of this kernel on 48 sequences of the same shape read 446.99 MB and
-        # wrote 3.93 MB against 447.58 MB of algorithmic bytes; traffic grows with the sequences, so that ratio is
+        # DRAM bytes per launch: one ncu capture of this kernel on 48 sequences of the same shape read 447.02 MB and
+        # wrote 3.91 MB against 447.58 MB of algorithmic bytes; traffic grows with the sequences, so that ratio is
         # applied to this launch
         traffic, traffic_source = None, None
         if key == "mistral7b" and context == 8192:
@@ -447,7 +447,7 @@ def run_b200(args):
 
 
 # DRAM bytes over algorithmic bytes of decode_mma_kernel, from the ncu capture of the 48-sequence case
-TRAFFIC_RATIO_B48 = (446.99 + 3.93) / 447.58
+TRAFFIC_RATIO_B48 = (447.02 + 3.91) / 447.58
 
 
 def ctypes_plan(cache, batch, context):

@@ -9,10 +9,6 @@
 #include "kivi_common.cuh"
 
 namespace kivi {
-namespace {
-
-constexpr int kLongChunkTokens = 6144;
-constexpr int kMinChunkTokens = 256;
 
 // Multiprocessors of the current device (148 on a B200), asked once per device.
 int sm_count() {
@@ -25,6 +21,11 @@ int sm_count() {
     }
     return cached[dev];
 }
+
+namespace {
+
+constexpr int kLongChunkTokens = 6144;
+constexpr int kMinChunkTokens = 256;
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 

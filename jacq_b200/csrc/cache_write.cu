@@ -242,9 +242,35 @@ __device__ __forceinline__ float4 group_params(float mn, float mx) {
     return make_float4(mn, scale, __frcp_rn(scale), 0.0f);
 }
 
+// The loads of pack_group_regs as asynchronous copies into a shared-memory tile: thread tid's k-th word lands at
+// tile[k * kThreads + tid], so a thread later reads back only what it requested itself (cp.async.wait_all, no
+// barrier). Lets a CTA that packs several groups request the next tile while it works on the current one.
+template <class Shape>
+__device__ __forceinline__ void prefetch_group_regs(const WriteParams& p, const SeqWrite& s, int h, int j, bool values,
+                                                    uint4* tile) {
+    constexpr int D = Shape::d, G = Shape::g;
+    constexpr int WPR = D / 8, RPP = kThreads / WPR, NK = G / RPP;
+    const int nkv = p.geom.nkv;
+    const int pos0 = s.prev_old + j * G;
+    const int tid = threadIdx.x, w = tid % WPR, r = tid / WPR;
+    const __half* scratch = values ? p.cache.v_scratch : p.cache.k_scratch;
+    const __half* fresh = values ? p.new_v : p.new_k;
+    const int pos = pos0 + r;
+    const uint4* from_scratch = reinterpret_cast<const uint4*>(
+        scratch + (((size_t)s.slot * nkv + h) * p.geom.scratch_rows + (pos - s.prev_old)) * D) + w;
+    const uint4* from_fresh = reinterpret_cast<const uint4*>(
+        fresh + ((long long)(s.new_row0 + pos - s.start) * nkv + h) * D) + w;
+    const size_t fresh_step = (size_t)RPP * nkv * WPR;
+#pragma unroll
+    for (int k = 0; k < NK; ++k) {
+        cp_async16(tile + k * kThreads + tid, pos + RPP * k < s.start ? from_scratch + k * RPP * WPR : from_fresh);
+        from_fresh += fresh_step;
+    }
+}
+
 template <class Shape>
 __device__ __forceinline__ void pack_group_regs(const WriteParams& p, const SeqWrite& s, int h, int j, bool values,
-                                                unsigned char* smem_raw) {
+                                                unsigned char* smem_raw, uint4* prefetched = nullptr, int next_j = -1) {
     constexpr int D = Shape::d, G = Shape::g, B = Shape::b;
     constexpr int WPR = D / 8, RPP = kThreads / WPR, NK = G / RPP;
     static_assert(kThreads % WPR == 0 && G % RPP == 0 && NK >= 1 && NK <= 8, "shape not covered by the register tile");
@@ -256,7 +282,13 @@ __device__ __forceinline__ void pack_group_regs(const WriteParams& p, const SeqW
 
     // ---- the tile: word w of rows r + RPP k, from the old scratch rows or the new rows
     uint4 x[NK];
-    {
+    if (prefetched) {
+        // the tile was requested earlier with prefetch_group_regs (same thread, same words): take it from there
+#pragma unroll
+        for (int k = 0; k < NK; ++k) x[k] = prefetched[k * kThreads + tid];
+        // ... and ask for the next group's tile into the same words (each thread overwrites only what it has just read)
+        if (next_j >= 0) prefetch_group_regs<Shape>(p, s, h, next_j, values, prefetched);
+    } else {
         const __half* scratch = values ? p.cache.v_scratch : p.cache.k_scratch;
         const __half* fresh = values ? p.new_v : p.new_k;
         const int pos = pos0 + r;
@@ -609,17 +641,37 @@ __device__ __forceinline__ void pack_group(const WriteParams& p, const Shape& g,
 // keys and values of a group are quantised independently (per channel / per token): one CTA each, so a
 // tile's worth of shared memory per CTA and twice the loads in flight per SM
 template <class Shape>
-__global__ void __launch_bounds__(kThreads, Shape::in_registers ? 3 : 1) pack_groups_kernel(const WriteParams p) {
+__global__ void __launch_bounds__(kThreads, Shape::in_registers ? 3 : 1) pack_groups_kernel(const WriteParams p, int per_cta) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const Shape g(p.geom);
-    const int i = blockIdx.z, h = blockIdx.y, j = blockIdx.x >> 1;
+    const int i = blockIdx.z, h = blockIdx.y, lane_j = blockIdx.x >> 1, lanes = gridDim.x >> 1;
     const bool values = blockIdx.x & 1;
     pdl_trigger();
     pdl_wait();   // new rows, lengths and tables may come from the kernel before this one
     const SeqWrite s = seq_write(p, i);
     const int ngroups = (s.next_old - s.prev_old) / g.g;
-    if (j >= ngroups) return;
-    pack_group(p, g, s, h, j, values, smem_raw);
+    if constexpr (Shape::in_registers) {
+        // A CTA takes a run of `per_cta` consecutive groups of its tensor (keys | values): the next group's rows are
+        // on their way (asynchronous copies into a shared-memory tile) while the current one is packed.
+        const int j0 = lane_j * per_cta, j1 = min(ngroups, j0 + per_cta);
+        if (j0 >= j1) return;
+        // shared memory: the prefetched tile first, then what pack_group_regs needs for itself
+        uint4* tile = reinterpret_cast<uint4*>(smem_raw);
+        unsigned char* work = smem_raw + (size_t)Shape::g * Shape::d * sizeof(__half);
+        prefetch_group_regs<Shape>(p, s, h, j0, values, tile);
+        for (int j = j0; j < j1; ++j) {
+            cp_async_wait_all();
+            // pack_group_regs copies the tile into registers first and then requests the next one
+            pack_group_regs<Shape>(p, s, h, j, values, work, tile, j + 1 < j1 ? j + 1 : -1);
+            __syncthreads();   // its shared-memory parameters are reused by the next group
+        }
+    } else {
+        (void)per_cta;
+        for (int j = lane_j; j < ngroups; j += lanes) {
+            pack_group(p, g, s, h, j, values, smem_raw);
+            __syncthreads();
+        }
+    }
 }
 
 // Move-to-front of the rows of (sequence s, kv head h) that stay in the scratch, then append of the new
@@ -748,20 +800,21 @@ size_t pack_smem_bytes(const Geom& g) {
 }
 
 template <class Shape>
-cudaError_t launch_pack(const WriteParams& p, dim3 grid, cudaStream_t stream) {
-    const size_t smem = pack_smem_bytes<Shape>(p.geom);
+cudaError_t launch_pack(const WriteParams& p, dim3 grid, int per_cta, cudaStream_t stream) {
+    size_t smem = pack_smem_bytes<Shape>(p.geom);
+    if constexpr (Shape::in_registers) smem += (size_t)Shape::g * Shape::d * sizeof(__half);   // the prefetched tile
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(pack_groups_kernel<Shape>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
-    return launch_pdl(pack_groups_kernel<Shape>, grid, dim3(kThreads), smem, stream, p);
+    return launch_pdl(pack_groups_kernel<Shape>, grid, dim3(kThreads), smem, stream, p, per_cta);
 }
 
 template <int D, int G>
-cudaError_t launch_pack_for_block(const WriteParams& p, dim3 grid, cudaStream_t stream, bool* done) {
+cudaError_t launch_pack_for_block(const WriteParams& p, dim3 grid, int per_cta, cudaStream_t stream, bool* done) {
     *done = true;
-    if (p.geom.b == 16) return launch_pack<StaticShape<D, G, 16>>(p, grid, stream);
-    if (p.geom.b == 32) return launch_pack<StaticShape<D, G, 32>>(p, grid, stream);
+    if (p.geom.b == 16) return launch_pack<StaticShape<D, G, 16>>(p, grid, per_cta, stream);
+    if (p.geom.b == 32) return launch_pack<StaticShape<D, G, 32>>(p, grid, per_cta, stream);
     *done = false;
     return cudaSuccess;
 }
@@ -844,21 +897,28 @@ cudaError_t launch_cache_write(const WriteParams& p, int max_new_per_seq, cudaSt
         if (e != cudaSuccess) return e;
         return done ? cudaSuccess : launch_append_shape<DynamicShape>(p, stream);
     }
+    // Quantise the groups that age out, then move / append the scratch rows (a second kernel: folding the scratch
+    // update into the first CTA of every (sequence, kv head, tensor) was measured slower, 3.5 against 3.7 TB/s --
+    // the copy then waits inside a CTA that has packing to do instead of running at the copy rate on its own).
+    // Compile-time shapes: a CTA takes a run of about four consecutive groups of one tensor (keys | values), so that
+    // the next group's rows travel while the current one is packed.
     const int max_groups = max_new_per_seq / g.g + 1;
-    const dim3 grid(2 * max_groups, g.nkv, p.n);   // (group, keys | values)
+    static const int wanted = [] { const char* e = getenv("KIVI_PACK_GROUPS_PER_CTA"); return e ? atoi(e) : 4; }();
+    const int per_cta = wanted < 1 ? 1 : (wanted > max_groups ? max_groups : wanted);
+    const int lanes = (max_groups + per_cta - 1) / per_cta;
     bool done = false;
     cudaError_t e = cudaSuccess;
-    if (g.d == 128 && g.g == 128) e = launch_pack_for_block<128, 128>(p, grid, stream, &done);
-    else if (g.d == 128 && g.g == 64) e = launch_pack_for_block<128, 64>(p, grid, stream, &done);
-    else if (g.d == 128 && g.g == 32) e = launch_pack_for_block<128, 32>(p, grid, stream, &done);
-    else if (g.d == 64 && g.g == 128) e = launch_pack_for_block<64, 128>(p, grid, stream, &done);
-    else if (g.d == 64 && g.g == 64) e = launch_pack_for_block<64, 64>(p, grid, stream, &done);
-    else if (g.d == 64 && g.g == 32) e = launch_pack_for_block<64, 32>(p, grid, stream, &done);
+    const dim3 run_grid(2 * lanes, g.nkv, p.n);   // (run of groups, keys | values)
+    if (g.d == 128 && g.g == 128) e = launch_pack_for_block<128, 128>(p, run_grid, per_cta, stream, &done);
+    else if (g.d == 128 && g.g == 64) e = launch_pack_for_block<128, 64>(p, run_grid, per_cta, stream, &done);
+    else if (g.d == 128 && g.g == 32) e = launch_pack_for_block<128, 32>(p, run_grid, per_cta, stream, &done);
+    else if (g.d == 64 && g.g == 128) e = launch_pack_for_block<64, 128>(p, run_grid, per_cta, stream, &done);
+    else if (g.d == 64 && g.g == 64) e = launch_pack_for_block<64, 64>(p, run_grid, per_cta, stream, &done);
+    else if (g.d == 64 && g.g == 32) e = launch_pack_for_block<64, 32>(p, run_grid, per_cta, stream, &done);
     if (e != cudaSuccess) return e;
-    if (!done) {
-        e = launch_pack<DynamicShape>(p, grid, stream);
-        if (e != cudaSuccess) return e;
-    }
+    // any other geometry: one CTA per (group, tensor)
+    if (!done) e = launch_pack<DynamicShape>(p, dim3(2 * max_groups, g.nkv, p.n), 1, stream);
+    if (e != cudaSuccess) return e;
     return launch_pdl(scratch_update_kernel, dim3(g.nkv, p.n), dim3(kThreads), 0, stream, p);
 }
 

@@ -65,7 +65,7 @@ constexpr int kBarBytes = 512;           // room for 64 mbarriers
 __device__ unsigned int g_decode_wait_failures;
 // Page or slot ids outside the pools that this kernel met and replaced by id 0 (kivi_b200_decode_rejected_indices).
 __device__ unsigned int g_decode_rejected;
-constexpr int kMaxSlotsPerWarp = 4;
+constexpr int kMaxSlotsPerWarp = 8;    // small slots (32-token groups of 64 channels) need this many in flight to cover the latency
 constexpr int kBarArrivals = 33;         // lane 0's expect_tx arrive + one cp.async arrive per lane
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleSlack = 8.0f;    // log2 units
@@ -261,7 +261,6 @@ __global__ void __launch_bounds__(W * 32, CTAS) decode_mma_kernel(const DecodePa
         if (i_item >= my_items) return;
         const uint32_t st = ring32 + (uint32_t)i_slot * C::SLOT;
         const uint32_t bar = bars32 + (uint32_t)i_slot * 8u;
-        fence_proxy_async();
         if (i_item < my_quant) {
             const int tokbase = i_grp * G + i_sub * kSub;
             const int lp = tokbase >> logb;

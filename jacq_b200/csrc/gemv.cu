@@ -183,11 +183,11 @@ cudaError_t launch_bt(const __half* w, const GemvPrologue& pro, __half* y16, flo
         cudaError_t e = cudaFuncSetAttribute(gemv_kernel<BT, PRO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
     }
-    // Enough CTAs to fill the 148 SMs, never more warps than row pairs; all of them
+    // Enough CTAs to fill the multiprocessors, never more warps than row pairs; all of them
     // resident at once, so a kernel launched behind this one can start as soon as they have.
     const int warps_needed = PRO == kGemvAddNormSiluOut ? out_dim : (out_dim + kRowsPerWarp - 1) / kRowsPerWarp;
     int blocks = (warps_needed + kGemvThreads / 32 - 1) / (kGemvThreads / 32);
-    if (blocks > 148 * kGemvCtasPerSm) blocks = 148 * kGemvCtasPerSm;
+    if (blocks > sm_count() * kGemvCtasPerSm) blocks = sm_count() * kGemvCtasPerSm;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(blocks, 1, 1);
     cfg.blockDim = dim3(kGemvThreads, 1, 1);
@@ -656,7 +656,7 @@ SkinnyPlan plan_skinny(int out_dim, int in_dim, int batch, int ctas_per_sm = kSg
     p.nt = (batch + 7) / 8;
     p.row_blocks = (out_dim + kSgRows - 1) / kSgRows;
     const int chunks = in_dim / kSgK;
-    int splits = ctas_per_sm * 148 / p.row_blocks;               // at most one wave of resident CTAs
+    int splits = ctas_per_sm * sm_count() / p.row_blocks;               // at most one wave of resident CTAs
     const int max_splits = chunks / 8 > 0 ? chunks / 8 : 1;      // at least 8 chunks (512 elements) per CTA
     if (splits > max_splits) splits = max_splits;
     if (splits > split_cap) splits = split_cap;

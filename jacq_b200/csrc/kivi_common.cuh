@@ -338,6 +338,9 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// Multiprocessors of the current device, asked once per device (api.cu).
+int sm_count();
+
 // Host-side launchers implemented in the .cu files.
 cudaError_t launch_cache_write(const WriteParams& p, int max_new_per_seq, cudaStream_t stream);
 struct RopeParams;     // step_math.cuh
