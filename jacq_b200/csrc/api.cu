@@ -110,12 +110,12 @@ size_t align_up(size_t x) { return (x + kWsAlign - 1) / kWsAlign * kWsAlign; }
 // to measurements: three CTAs are resident on a multiprocessor and share it, so three equal jobs take one
 // "round" s together; CTAs are handed out in index order, so a multiprocessor's queue of j jobs runs as
 // floor(j / 3) full rounds and a last round of one or two jobs, which finish sooner than a full round but not in
-// proportion (a lone CTA reaches 0.6 of the multiprocessor's rate, two reach 0.87). A launch takes as long as the
+// proportion (a lone CTA reaches 0.6 of the multiprocessor's rate -- 0.5 with key groups shorter than 128 tokens --, two reach 0.87). A launch takes as long as the
 // longest queue, ceil(jobs / multiprocessors); a job costs a start-up plus its share of the unit; a launch that
 // cuts anything pays for the merge kernel. Candidates: every unit in k parts; or whole units for as many full
 // rounds as there are and the units left over in k2 parts each (the small jobs start last and even out the end).
 // Lengths live on the device, so the plan assumes every unit is as long as the longest the launch allows.
-constexpr int kJobFixedCost = 40;      // start-up of a CTA, in weight units of a 128-channel head (about 5 us)
+constexpr int kJobFixedCost = 40;      // start-up of a CTA, in weight units of a 128-channel head with 128-token groups (about 7 us)
 constexpr int kMergeCost = 60;         // the merge kernel behind a launch that cuts units
 constexpr double kCutMargin = 1.05;    // a cut has to promise this much before it is preferred to whole units
 constexpr int kMaxParts = 64;
@@ -125,7 +125,13 @@ JobPlan plan_jobs(const Geom& g, int n, int max_old_tokens) {
     const long long w = (long long)(max_old_tokens / g.g) * wg + (long long)((g.r + g.g + 15) / 16) * 4;
     const long long units = (long long)n * g.nkv;
     const long long sms = sm_count(), resident = decode_mma_ctas_per_sm();
-    const double fixed = (double)kJobFixedCost * 128 / g.d, merge = (double)kMergeCost * 128 / g.d;
+    // The two costs are times, and the time of a weight unit depends on the geometry: a 64-channel head takes
+    // about 0.6 of a 128-channel one, and short key groups cost more per token (per group the query is rescaled and the zero-point term formed: about 4.7 tiles' worth). Fitted on
+    // head 128 / group 128 (0.17 us per unit) and head 64 / group 32 (0.22 us per unit).
+    const double unit_us = (g.d >= 128 ? 0.107 : 0.064) * (1.0 + 4.74 / (double)wg);
+    const double fixed = kJobFixedCost * 0.17 / unit_us, merge = kMergeCost * 0.17 / unit_us;
+    // a CTA alone on a multiprocessor: short groups leave a lone warp per scheduler waiting on itself more often
+    const double lone_rate = wg >= 8 ? 0.6 : 0.5;
     long long kcap = w / (2 * wg);           // a part keeps at least two key groups' worth
     if (kcap < 1) kcap = 1;
     if (kcap > kMaxParts) kcap = kMaxParts;
@@ -137,7 +143,7 @@ JobPlan plan_jobs(const Geom& g, int n, int max_old_tokens) {
     // time of a queue of `jobs` equal jobs on one multiprocessor, in rounds
     auto rounds_of = [&](long long jobs) {
         const long long rest = jobs % resident;
-        const double last = rest == 0 ? 0.0 : (double)rest / resident / (rest == 1 ? 0.6 : (rest == 2 ? 0.87 : 1.0));
+        const double last = rest == 0 ? 0.0 : (double)rest / resident / (rest == 1 ? lone_rate : (rest == 2 ? 0.87 : 1.0));
         return (double)(jobs / resident) + last;
     };
     double best_t = rounds_of((units + sms - 1) / sms) * job(1);   // whole units
