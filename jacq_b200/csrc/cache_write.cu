@@ -827,7 +827,12 @@ __global__ void __launch_bounds__(kThreads, Shape::in_registers ? 3 : 1) pack_gr
                     cp_async16_32(c.tile32 + k * kThreads * 16,
                                   c.fresh_w + (unsigned long long)(uint32_t)(rel0 + C::RPP * k) * c.fresh_row_bytes);
         };
-        if (j0 < j1) request_tile(c, j0);
+        // the block-table entries of a group are read when its codes are stored; asked for one group ahead, they
+        // are in the L1 by then
+        auto touch_pages = [&](int j) {
+            asm volatile("prefetch.global.L1 [%0];" ::"l"(c.pages + j * Shape::pages_per_group));
+        };
+        if (j0 < j1) { request_tile(c, j0); touch_pages(j0); }
         else request_staying_rows();
         for (int j = j0; j < j1; ++j) {
             cp_async_wait_all();
@@ -836,7 +841,7 @@ __global__ void __launch_bounds__(kThreads, Shape::in_registers ? 3 : 1) pack_gr
             uint4 x[C::NK];
 #pragma unroll
             for (int k = 0; k < C::NK; ++k) x[k] = lds128(c.tile32 + k * kThreads * 16);
-            if (j + 1 < j1) request_tile(c, j + 1);
+            if (j + 1 < j1) { request_tile(c, j + 1); touch_pages(j + 1); }
             else request_staying_rows();
             pack_tile<Shape>(p, c, h, j, values, x, work);
         }

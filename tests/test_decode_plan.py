@@ -53,6 +53,19 @@ def test_known_plans_on_148_multiprocessors(native_lib):
     assert (u1, k1, u2) == (0, 1, 8) and 18 <= k2 <= 56
 
 
+def test_short_groups_and_narrow_heads_are_cut_too(native_lib):
+    """Head 64 / group 32 (the two small configurations): a weight unit takes longer there and a lone CTA gets less
+    of its multiprocessor, so launches that leave multiprocessors idle or with one CTA are cut; full ones are not."""
+    qwen = _geom(14, 2, 64, 16, 32, 32)
+    assert _plan(native_lib, qwen, 64, 4096) == (0, 1, 128, 3)      # 128 units -> 384 jobs: one round of three everywhere
+    assert _plan(native_lib, qwen, 128, 4096) == (0, 1, 256, 1)     # two per multiprocessor already
+    u1, k1, u2, k2 = _plan(native_lib, qwen, 16, 4096)
+    assert (u1, k1, u2) == (0, 1, 32) and 4 <= k2 <= 13             # 32 units: at least a job per multiprocessor
+    tiny = _geom(32, 4, 64, 16, 32, 32)
+    assert _plan(native_lib, tiny, 4, 512) == (0, 1, 16, 1)         # 512 tokens: nothing to gain from a merge launch
+    assert _plan(native_lib, tiny, 32, 2048) == (0, 1, 128, 1)
+
+
 @pytest.mark.parametrize("g,r", [(128, 128), (32, 32), (64, 128), (32, 128)])
 def test_parts_tile_the_groups_and_residual_tiles_exactly_once(native_lib, g, r):
     geom = _geom(8, 2, 128, 16, g, r)
