@@ -124,10 +124,9 @@ __device__ __forceinline__ P2pView p2p_view(const P2pGather& g) {
     return v;
 }
 
-// Data words 2 i and 2 i + 1 of rank r's payload (one 16-byte load of two 8-byte words).
-__device__ __forceinline__ uint2 p2p_read2(P2pView& v, int r, size_t i) {
-    const unsigned char* p = v.slots + (size_t)r * v.slot_bytes + i * 16;
-    uint4 w = ld_volatile16(p);
+// Data words 2 i and 2 i + 1 of rank r's payload (one 16-byte load of two 8-byte words). `w` is a first look at
+// them, possibly from before they arrived: polled again until both carry the exchange's sequence number.
+__device__ __forceinline__ uint2 p2p_settle2(P2pView& v, int r, const unsigned char* p, uint4 w) {
     unsigned spins = 0;
     while ((w.y != v.seq || w.w != v.seq) && spins < v.spin_limit) {
         __nanosleep(40);
@@ -140,22 +139,44 @@ __device__ __forceinline__ uint2 p2p_read2(P2pView& v, int r, size_t i) {
     }
     return make_uint2(w.x, w.z);
 }
+__device__ __forceinline__ uint2 p2p_read2(P2pView& v, int r, size_t i) {
+    const unsigned char* p = v.slots + (size_t)r * v.slot_bytes + i * 16;
+    return p2p_settle2(v, r, p, ld_volatile16(p));
+}
 
 // Sum over ranks of eight fp16 values (data words 4 vec .. 4 vec + 3 of every payload): fp32, rank
-// order, one rounding.
+// order, one rounding. The loads of two ranks go out together before any of them is looked at: a load
+// that bypasses the L1 takes the better part of a microsecond, and one after the other (two per rank) they were
+// most of what an exchange cost -- 20 round trips per thread on four ranks, 40 on eight. (Four ranks together made
+// the projection kernels, which call this from their prologue with weights already prefetched into registers, spill.)
+template <int kTogether = 2>   // ranks whose words are requested together (two 16-byte loads, 8 registers, each)
 __device__ __forceinline__ uint4 p2p_sum8(P2pView& v, size_t vec) {
     float acc[8];
 #pragma unroll
     for (int k = 0; k < 8; ++k) acc[k] = 0.0f;
-    for (int r = 0; r < v.tp; ++r) {
-        const uint2 a = p2p_read2(v, r, 2 * vec), b = p2p_read2(v, r, 2 * vec + 1);
-        const unsigned w[4] = {a.x, a.y, b.x, b.y};
+    const unsigned char* base = v.slots + vec * 32;
+    for (int r0 = 0; r0 < v.tp; r0 += kTogether) {
+        uint4 first[kTogether][2];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[k]));
-            acc[2 * k] += f.x;
-            acc[2 * k + 1] += f.y;
-        }
+        for (int k = 0; k < kTogether; ++k)
+            if (r0 + k < v.tp) {
+                const unsigned char* p = base + (size_t)(r0 + k) * v.slot_bytes;
+                first[k][0] = ld_volatile16(p);
+                first[k][1] = ld_volatile16(p + 16);
+            }
+#pragma unroll
+        for (int k = 0; k < kTogether; ++k)
+            if (r0 + k < v.tp) {
+                const unsigned char* p = base + (size_t)(r0 + k) * v.slot_bytes;
+                const uint2 a = p2p_settle2(v, r0 + k, p, first[k][0]), b = p2p_settle2(v, r0 + k, p + 16, first[k][1]);
+                const unsigned w[4] = {a.x, a.y, b.x, b.y};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[e]));
+                    acc[2 * e] += f.x;
+                    acc[2 * e + 1] += f.y;
+                }
+            }
     }
     uint4 o;
     __half* oh = reinterpret_cast<__half*>(&o);

@@ -44,7 +44,7 @@ __global__ void __launch_bounds__(kNormThreads) residual_rmsnorm_kernel(
     const int vecs = hidden >> 3;
     for (int v = tid; v < vecs; v += kNormThreads) {
         uint4 a = xs[v];
-        if (gathered) a = hadd8(a, p2p_sum8(view, (size_t)blockIdx.x * vecs + v));
+        if (gathered) a = hadd8(a, p2p_sum8<4>(view, (size_t)blockIdx.x * vecs + v));   // nothing else lives in registers here
         else if (ds) a = hadd8(a, ds[v]);
         if (xo) xo[v] = a;
         row[v] = a;
