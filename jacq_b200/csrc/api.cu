@@ -247,12 +247,21 @@ Geom ref_geom(int nh, int nkv) {
     exit(1);
 }
 
-// Workspace of the v1 decode symbols. Their signatures carry no workspace, so the library keeps
-// one per device, sized for the largest v1 launch (160 queries) and allocated with cudaMalloc on
-// the first v1 decode call on that device (that first call must not be inside a stream capture).
+// Workspace of the v1 decode symbols. Their signatures carry no workspace and the reference's entry points
+// never allocate, so the partial results of a cut launch live in a fixed array of the library's device image
+// (every GPU that loads the library carries it; all v1 calls on a device share it, like the reference's calls
+// share nothing they would have to). Its size covers the largest v1 launch (160 queries, 4096 tokens) on a B200's
+// 148 multiprocessors; on a device whose launch plan would need more, the first call falls back to cudaMalloc.
 constexpr int kMaxDevices = 64;
+constexpr size_t kRefWorkspaceBytes = 2560u << 10;
+}  // namespace
+}  // namespace kivi
+static __device__ __align__(256) unsigned char g_ref_workspace[kivi::kRefWorkspaceBytes];
+namespace kivi {
+namespace {
 void* g_ref_ws[kMaxDevices];
 size_t g_ref_ws_bytes[kMaxDevices];
+std::once_flag g_ref_ws_once[kMaxDevices];
 
 void* ref_workspace(const Geom& g, int n, size_t* bytes, cudaStream_t stream) {
     int dev = 0;
@@ -260,7 +269,7 @@ void* ref_workspace(const Geom& g, int n, size_t* bytes, cudaStream_t stream) {
     if (e != cudaSuccess) die("cudaGetDevice", e);
     if (dev < 0 || dev >= kMaxDevices) { fprintf(stderr, "device index %d out of range\n", dev); exit(1); }
     (void)g; (void)n;
-    if (!g_ref_ws[dev]) {
+    std::call_once(g_ref_ws_once[dev], [dev, stream] {
         size_t need = 0;
         const Geom lanes[2] = {ref_geom(40, 8), ref_geom(20, 4)};
         for (const Geom& lane : lanes)
@@ -268,12 +277,18 @@ void* ref_workspace(const Geom& g, int n, size_t* bytes, cudaStream_t stream) {
                 size_t t = ws_layout(lane, q, kRefLQ).total;
                 if (t > need) need = t;
             }
-        e = cudaMalloc(&g_ref_ws[dev], need);
-        if (e != cudaSuccess) die("cudaMalloc(v1 decode workspace)", e);
-        e = cudaMemsetAsync(g_ref_ws[dev], 0, need, stream);
-        if (e != cudaSuccess) die("cudaMemsetAsync(v1 decode workspace)", e);
+        void* ptr = nullptr;
+        if (need <= kRefWorkspaceBytes && cudaGetSymbolAddress(&ptr, g_ref_workspace) == cudaSuccess && ptr) {
+            g_ref_ws[dev] = ptr;
+            g_ref_ws_bytes[dev] = kRefWorkspaceBytes;
+            return;
+        }
+        cudaError_t err = cudaMalloc(&g_ref_ws[dev], need);
+        if (err != cudaSuccess) die("cudaMalloc(v1 decode workspace)", err);
+        err = cudaMemsetAsync(g_ref_ws[dev], 0, need, stream);
+        if (err != cudaSuccess) die("cudaMemsetAsync(v1 decode workspace)", err);
         g_ref_ws_bytes[dev] = need;
-    }
+    });
     *bytes = g_ref_ws_bytes[dev];
     return g_ref_ws[dev];
 }
