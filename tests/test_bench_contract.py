@@ -33,6 +33,19 @@ def test_reference_arm_prints_the_shared_contract_line():
     assert e2e == {"value": line["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
 
 
+def test_reference_arm_under_torchrun_prints_once():
+    """Launched one process per GPU like the product arm: rank 0 alone does the work and prints, the others leave."""
+    proc = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                           "--master-addr", "127.0.0.1", "--master-port", "29631", str(ROOT / "bench.py"), "--impl",
+                           "reference", "--gpus", "2", "--steps", "1", "--warmup", "1"],
+                          cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    lines = [ln for ln in proc.stdout.splitlines() if ln.startswith("{")]
+    assert len(lines) == 1
+    line = json.loads(lines[0])
+    assert line["impl"] == "reference" and line["n_gpus"] == 2 and line["value"] > 0
+
+
 @pytest.mark.skipif(torch.cuda.is_available(), reason="only meaningful where no GPU is present")
 def test_product_arm_has_no_cpu_fallback():
     proc = _run("--steps", "1", "--warmup", "1", "--no-extras", "--no-cpu-baseline", timeout=300)
