@@ -724,6 +724,85 @@ def measure_decode_config(name, steps, warmup, device):
                          "peak_source": f"{peak_kind} HBM copy bandwidth", "kernel": "decode_mma_kernel"}}
 
 
+def measure_ragged(steps, warmup, device):
+    """The ragged stress shape as a throughput case: 256 sequences whose lengths are drawn uniformly from 1..32768
+    (32 query / 8 kv heads, head size 128, page 16, group 128), fully shuffled block tables, the cache built by
+    interleaved 512-token chunk writes (a sequence drops out of the batch when it is full). One step = one decode
+    launch over all 256 sequences; bytes = the sum of every sequence's own algorithmic bytes."""
+    import torch
+    from tests import helpers
+    from jacq_b200.cache import KiviCache
+    peak, peak_kind = _peaks()
+    case = helpers.CONFIGS["mistral7b"]
+    lay = helpers.layout_of(case)
+    batch, longest, chunk = 256, 32768, 512
+    rng = np.random.default_rng(20261125)
+    lens = rng.integers(1, longest + 1, size=batch).astype(np.int64)
+    pages = lay.old_pages(longest) + 1
+    cache = KiviCache(lay, batch * pages, batch, pages, device)
+    gen = torch.Generator(device=device).manual_seed(9)
+    cache.set_block_tables(torch.randperm(batch * pages, device=device, generator=gen).to(torch.int32)
+                           .reshape(batch, pages))
+    # all chunks' rows first (16 GB), then the 64 write calls back to back between two events: the host stays
+    # ahead of the device, so the time is the writer's and not the call overhead's
+    written, calls = 0, []
+    for start in range(0, longest, chunk):
+        counts = np.clip(lens - start, 0, chunk)
+        total = int(counts.sum())
+        if total == 0:
+            break
+        k = torch.randn((total, case.nkv, case.d), device=device, dtype=torch.float16, generator=gen)
+        v = torch.randn((total, case.nkv, case.d), device=device, dtype=torch.float16, generator=gen)
+        offs = torch.from_numpy(np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)).to(device)
+        calls.append((k, v, offs, start))
+        written += total
+    # the writer's kernels are loaded by a first call elsewhere (a 2-sequence cache of the same geometry): the first
+    # launch of a kernel in a process costs milliseconds of module loading
+    small = KiviCache(lay, 2 * (2 * chunk // case.b + 1), 2, 2 * chunk // case.b + 1, device)
+    small.set_block_tables(torch.arange(2 * (2 * chunk // case.b + 1), device=device, dtype=torch.int32).reshape(2, -1))
+    for first in (0, chunk):
+        small.write(calls[0][0][: 2 * chunk], calls[0][1][: 2 * chunk],
+                    torch.tensor([0, chunk, 2 * chunk], device=device, dtype=torch.int32), max_new_per_seq=chunk,
+                    max_start_seq_len=first)
+    del small
+    torch.cuda.synchronize(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for k, v, offs, start in calls:
+        cache.write(k, v, offs, max_new_per_seq=chunk, max_start_seq_len=start)
+    e1.record()
+    torch.cuda.synchronize(device)
+    write_ms = e0.elapsed_time(e1)
+    ncalls = len(calls)
+    del calls, k, v
+    torch.cuda.empty_cache()
+    if cache.seq_lens.cpu().numpy().tolist() != lens.tolist():
+        raise RuntimeError("bench: the ragged cache's lengths differ from the lengths written")
+    q = torch.randn((batch, case.nh, case.d), device=device, dtype=torch.float16, generator=gen)
+    out = torch.empty((batch, case.nh, case.d), dtype=torch.float32, device=device)
+    step_bytes = int(sum(lay.decode_algorithmic_bytes(int(t)) for t in lens))
+
+    def step():
+        cache.decode(q, out, max_seq_len=longest)
+    ms = statistics.mean(_timed_steps(step, steps, warmup, device))
+    if not bool(torch.isfinite(out).all()):
+        raise RuntimeError("bench: the ragged decode produced a non-finite output")
+    value = step_bytes / (ms * 1e-3) / 1e9
+    return {"metric": METRIC, "value": value, "unit": "GB/s", "ms_per_step": ms, "tokens_per_s": batch / (ms * 1e-3),
+            "config": {"workload": "ragged_decode_attn_b256_t1_32768", "batch": batch, "context": "uniform 1..32768",
+                       "context_tokens_total": int(lens.sum()), "algorithmic_bytes_per_step": step_bytes,
+                       "launch_plan": ctypes_plan(cache, batch, longest),
+                       "cache_build": {"tokens": written, "write_calls": ncalls, "ms": write_ms,
+                                       "tokens_per_s": written / (write_ms * 1e-3),
+                                       "new_rows_gbs": written * case.nkv * case.d * 4 / (write_ms * 1e-3) / 1e9,
+                                       "what": "interleaved ragged 512-token chunk writes, all calls back to back "
+                                               "between two events; GB/s of the new K and V rows alone"},
+                       "l2": "inputs exceed the L2"},
+            "gpu_launches": steps,
+            "roofline": {"bound": "hbm", "achieved": value, "peak": peak, "unit": "GB/s", "frac": value / peak,
+                         "peak_source": f"{peak_kind} HBM copy bandwidth", "kernel": "decode_mma_kernel"}}
+
+
 def measure_secondary(args, device):
     """The other parts of the path, each against its own HBM roofline (one GPU): the cache writer, the GEMV /
     skinny GEMM of the generated runtime, the whole decode step at batch 1, and the two small attention-only
@@ -736,6 +815,7 @@ def measure_secondary(args, device):
             ("gemv_b64", lambda: measure_gemv(64, args.steps, args.warmup, device)),
             ("decode_attn_tinyllama_b4_t512", lambda: measure_decode_config("tinyllama_decode_attn_b4_t512", args.steps, args.warmup, device)),
             ("decode_attn_qwen05b_b64_t4096", lambda: measure_decode_config("qwen05b_decode_attn_b64_t4096", args.steps, args.warmup, device)),
+            ("decode_attn_ragged_b256_t1_32768", lambda: measure_ragged(args.steps, args.warmup, device)),
             ("decode_step_qwen25_14b_b1_t32768", lambda: measure_step(1, 32768, "p2p", min(args.steps, 10), args.warmup, device, 0, 0, 1, None, sample_clocks=False))]
     for name, fn in jobs:
         try:
